@@ -1,0 +1,182 @@
+/*
+ * msaq_b200.h -- C ABI of the B200 (sm_100a) MSAQ-signed decode path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*, i.e. a cudaStream_t), launches on that stream, allocates
+ * nothing, never synchronises the host, and returns MSAQ_OK or a negative
+ * error code; msaq_last_error() gives the message of the calling thread's last
+ * failure.  Scratch memory is a caller-owned workspace whose size the matching
+ * *_workspace() query returns.
+ *
+ * Packed data layout (unchanged from the reference, ms_lib/pack.py:101-137 and
+ * :479-504).  BLOCK = 32, nb = K/32 (or D/32), wbits = 8-u,
+ * UB = 32*wbits/8, SB = ceil((32/gs)*u/8):
+ *   weights   scale_exp int8 [nb,OUT]
+ *             row-major    upper u8 [nb,UB,OUT]   shared u8 [nb,SB,OUT]
+ *             column-major upper u8 [nb,OUT,UB]   shared u8 [nb,OUT,SB]
+ *   KV cache  scale_exp int8 [B*Hkv,nb,Lcap]
+ *             upper u8 [B*Hkv,nb,Lcap,UB]   shared u8 [B*Hkv,nb,Lcap,SB]
+ * Inside a block, upper code k sits at bits [k*wbits,(k+1)*wbits) and the shared
+ * code of group g = k/gs at bits [g*u,(g+1)*u) of the little-endian byte run,
+ * both two's complement; value = (up*2^u + sh) * 2^scale_exp.
+ *
+ * Supported: u in {2,3,4}; gs in {2,4,8,16,32}; D a power of two in [32,256].
+ */
+#ifndef MSAQ_B200_H
+#define MSAQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MSAQ_OK               0
+#define MSAQ_ERR_ARG         -1   /* null pointer, bad size, misaligned pointer   */
+#define MSAQ_ERR_UNSUPPORTED -2   /* (u, gs, D) outside the supported set         */
+#define MSAQ_ERR_WORKSPACE   -3   /* workspace missing or too small               */
+#define MSAQ_ERR_CUDA        -4   /* a CUDA runtime call or a launch failed       */
+#define MSAQ_ERR_DEVICE      -5   /* the current device is not an sm_100 part     */
+
+/* Library version (major*1000 + minor). */
+int msaq_version(void);
+/* Message of the calling thread's most recent error ("" if none). */
+const char* msaq_last_error(void);
+/* Number of kernels this library has launched in the calling process. */
+unsigned long long msaq_launch_count(void);
+
+/* ------------------------------------------------------------------ GEMV -- */
+
+/* Bytes of workspace the three GEMV entry points need for these sizes. */
+size_t msaq_wonly_gemv_workspace(int64_t M, int64_t OUT, int64_t NB, int u, int gs);
+
+/*
+ * y[OUT] = x[K] . dequant(W)^T on ROW-MAJOR planes.  x, y bf16; fp32 accumulate.
+ * Replaces op `msaq::wonly_gemv` (csrc/pybind.cpp:199-200, host
+ * csrc/w_gemv.cu:1410-1454).  y_f32 (optional, may be NULL) also receives the
+ * result before the bf16 rounding.
+ */
+int msaq_wonly_gemv(const void* x, const int8_t* scale_exp, const uint8_t* upper,
+                    const uint8_t* shared, void* y, float* y_f32,
+                    int64_t OUT, int64_t NB, int u, int gs,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Same product on COLUMN-MAJOR planes (upper_cm / shared_cm).
+ * Replaces op `msaq::wonly_gemv_wide` (csrc/pybind.cpp:201-202, host
+ * csrc/w_gemv.cu:1457-1510).
+ */
+int msaq_wonly_gemv_wide(const void* x, const int8_t* scale_exp, const uint8_t* upper_cm,
+                         const uint8_t* shared_cm, void* y, float* y_f32,
+                         int64_t OUT, int64_t NB, int u, int gs,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Y[M,OUT] = X[M,K] . dequant(W)^T on column-major planes, any M >= 1.
+ * Replaces op `msaq::wonly_gemv_batched` (csrc/pybind.cpp:205-206, host
+ * csrc/w_gemv.cu:1514-1570).
+ */
+int msaq_wonly_gemv_batched(const void* X, const int8_t* scale_exp, const uint8_t* upper_cm,
+                            const uint8_t* shared_cm, void* Y, float* Y_f32,
+                            int64_t M, int64_t OUT, int64_t NB, int u, int gs,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
+/* -------------------------------------------------------- KV cache write -- */
+
+/*
+ * Quantise one new token X[H,D] (bf16) into slot `pos` of the cache planes
+ * (key stride Lcap), in place.  Replaces op `msaq::kv_append`
+ * (csrc/pybind.cpp:236-237, host csrc/kv_attention.cu:2326-2339).
+ */
+int msaq_kv_append(const void* X, int8_t* scale_exp, uint8_t* upper, uint8_t* shared,
+                   int64_t H, int64_t D, int64_t NB, int64_t pos, int64_t Lcap,
+                   int u, int gs, void* stream);
+
+/*
+ * Same, after rotating each head row by the orthonormal Hadamard matrix H_D:
+ * an fp32 butterfly (stages h = 1,2,..,D/2; lo' = lo+hi, hi' = lo-hi) times
+ * float(1/sqrt(D)).  Replaces op `msaq::kv_append_rot`
+ * (csrc/pybind.cpp:238-239, host csrc/kv_attention.cu:2343-2356).
+ */
+int msaq_kv_append_rot(const void* X, int8_t* scale_exp, uint8_t* upper, uint8_t* shared,
+                       int64_t H, int64_t D, int64_t NB, int64_t pos, int64_t Lcap,
+                       int u, int gs, void* stream);
+
+/*
+ * Batched append with one position per sequence: X[B*Hkv,D]; row r belongs to
+ * sequence r / Hkv and is written at slot pos[r / Hkv] (int32, device memory).
+ * rotate != 0 applies the Hadamard rotation first.  The reference has one
+ * scalar position for the whole batch (csrc/kv_attention.cu:2326-2328); this
+ * is the per-sequence form of the same two ops.
+ */
+int msaq_kv_append_varlen(const void* X, int8_t* scale_exp, uint8_t* upper, uint8_t* shared,
+                          int64_t B, int64_t Hkv, int64_t D, int64_t NB, const int32_t* pos,
+                          int64_t Lcap, int u, int gs, int rotate, void* stream);
+
+/*
+ * Prefill pack: X[H,L,D] (bf16) -> slots [key0, key0+L) of planes with key
+ * stride Lcap (Lcap = L, key0 = 0 gives the reference's freshly allocated
+ * planes).  rotate != 0 applies the Hadamard rotation to every row first.
+ * Replaces op `msaq::kv_write` (csrc/pybind.cpp:235, host
+ * csrc/kv_attention.cu:2302-2321).
+ */
+int msaq_kv_write(const void* X, int8_t* scale_exp, uint8_t* upper, uint8_t* shared,
+                  int64_t H, int64_t L, int64_t D, int64_t NB, int64_t key0, int64_t Lcap,
+                  int u, int gs, int rotate, void* stream);
+
+/*
+ * out[N,D] = bf16( H_D-rotation of x[N,D] ), bf16 in and out.
+ * Replaces op `msaq::hadamard_rotate` (csrc/pybind.cpp:286, csrc/rotate.cu:40-86).
+ */
+int msaq_hadamard_rotate(const void* x, void* out, int64_t N, int64_t D, void* stream);
+
+/*
+ * Offline weight packing on the device: W[OUT,K] (bf16 if w_is_bf16 else fp32)
+ * -> all five planes.  Any of the plane pointers may be NULL to skip it.
+ * Device twin of ms_lib/pack.py:101-137 (`pack_weight`).
+ */
+int msaq_pack_weight(const void* W, int w_is_bf16, int8_t* scale_exp, uint8_t* upper,
+                     uint8_t* shared, uint8_t* upper_cm, uint8_t* shared_cm,
+                     int64_t OUT, int64_t K, int u, int gs, void* stream);
+
+/* ------------------------------------------------------ KV flash-decode -- */
+
+/* Bytes of workspace the decode entry points need (split-KV partials). */
+size_t msaq_kv_decode_workspace(int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D);
+
+/*
+ * Single-sequence decode attention: q[H,D] bf16 -> out[H,D] bf16;
+ * out[h] = softmax(q[h].K^T / sqrt(D)) . V over keys [0,Lk) of kv head
+ * h / (H/Hkv).  Never rotates q.  Replaces op `msaq::kv_decode_attention`
+ * (csrc/pybind.cpp:266-269, host csrc/kv_attention.cu:1875-2049).
+ */
+int msaq_kv_decode_attention(const void* q,
+                             const int8_t* ks, const uint8_t* ku, const uint8_t* kh,
+                             const int8_t* vs, const uint8_t* vu, const uint8_t* vh,
+                             void* out, float* out_f32,
+                             int64_t H, int64_t Hkv, int64_t Lk, int64_t D, int64_t NB,
+                             int u, int gs, int64_t Lcap,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Batched decode attention: q[B,H,D], planes [B,Hkv,NB,Lcap,*] -> out[B,H,D].
+ * qrot != 0 rotates each query row by H_D in the prologue (the op reads this
+ * from the MS_KV_QROT environment variable, csrc/kv_attention.cu:2082-2083).
+ * seq_lens (optional int32[B], device) gives per-sequence key counts <= Lk;
+ * NULL means every sequence attends Lk keys, as in the reference.
+ * Replaces op `msaq::kv_decode_attention_batched` (csrc/pybind.cpp:270-273,
+ * host csrc/kv_attention.cu:2055-2122).
+ */
+int msaq_kv_decode_attention_batched(const void* q,
+                                     const int8_t* ks, const uint8_t* ku, const uint8_t* kh,
+                                     const int8_t* vs, const uint8_t* vu, const uint8_t* vh,
+                                     void* out, float* out_f32, const int32_t* seq_lens,
+                                     int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D,
+                                     int64_t NB, int u, int gs, int64_t Lcap, int qrot,
+                                     void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MSAQ_B200_H */

@@ -1,0 +1,68 @@
+// Error plumbing, launch accounting and device queries shared by the entry points.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "msaq_common.cuh"
+
+namespace msaq {
+
+namespace {
+thread_local char g_err[512] = "";
+std::atomic<unsigned long long> g_launches{0};
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int check_launch(const char* what) {
+    const cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) {
+        cudaGetLastError();   // clear the non-sticky launch-configuration error
+        return fail(MSAQ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    }
+    return MSAQ_OK;
+}
+
+void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
+
+// Per-device cache; filled on first use by whichever thread gets there (the
+// values are idempotent, so a benign double fill is harmless).
+namespace {
+constexpr int MAX_DEV = 64;
+std::atomic<int> g_sm[MAX_DEV];
+std::atomic<int> g_cc[MAX_DEV];
+
+int current_device_attr(std::atomic<int>* cache, cudaDeviceAttr attr) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return 0;
+    int v = cache[dev].load(std::memory_order_relaxed);
+    if (v == 0) {
+        if (cudaDeviceGetAttribute(&v, attr, dev) != cudaSuccess) return 0;
+        cache[dev].store(v, std::memory_order_relaxed);
+    }
+    return v;
+}
+}  // namespace
+
+int sm_count() {
+    const int n = current_device_attr(g_sm, cudaDevAttrMultiProcessorCount);
+    return n > 0 ? n : 148;
+}
+
+int require_sm100() {
+    const int major = current_device_attr(g_cc, cudaDevAttrComputeCapabilityMajor);
+    if (major != 10) return fail(MSAQ_ERR_DEVICE, "current device has compute capability major %d; this library is built for sm_100a only", major);
+    return MSAQ_OK;
+}
+
+}  // namespace msaq
+
+extern "C" int msaq_version(void) { return 1000; }
+extern "C" const char* msaq_last_error(void) { return msaq::g_err; }
+extern "C" unsigned long long msaq_launch_count(void) { return msaq::g_launches.load(std::memory_order_relaxed); }

@@ -1,0 +1,100 @@
+// Host side of the KV flash-decode entry points: argument checks, the split-KV
+// plan, kernel selection.  Replaces the launchers at
+// csrc/kv_attention.cu:1875-2122 of the reference.
+#include "kv_decode_generic.cuh"
+
+namespace msaq {
+namespace {
+
+struct KvPlan {
+    int S;          // key tiles per (sequence, head)
+    int key_tile;   // keys per tile (multiple of the chunk)
+};
+
+KvPlan plan_generic(int64_t B, int64_t H, int64_t Lk) {
+    KvPlan p;
+    const int64_t heads = B * H;
+    int64_t want = (3LL * sm_count() + heads - 1) / heads;
+    const int64_t max_tiles = (Lk + KVG_CHUNK - 1) / KVG_CHUNK;
+    if (want > max_tiles) want = max_tiles;
+    if (want < 1) want = 1;
+    int64_t tile = (Lk + want - 1) / want;
+    tile = (tile + KVG_CHUNK - 1) / KVG_CHUNK * KVG_CHUNK;
+    p.key_tile = (int)tile;
+    p.S = (int)((Lk + tile - 1) / tile);
+    return p;
+}
+
+int decode_dispatch(const void* q, KvPlanes kp, KvPlanes vp, void* out, float* out_f32, const int32_t* seq_lens,
+                    int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D, int64_t NB, int u, int gs,
+                    int64_t Lcap, int qrot, void* ws, size_t ws_bytes, void* stream) {
+    Fmt f;
+    if (!make_fmt(u, gs, &f)) return fail(MSAQ_ERR_UNSUPPORTED, "unsupported format u=%d gs=%d", u, gs);
+    if (!q || !kp.s || !kp.u || !kp.h || !vp.s || !vp.u || !vp.h || !out) return fail(MSAQ_ERR_ARG, "null pointer");
+    if (B <= 0 || H <= 0 || Hkv <= 0 || Lk <= 0) return fail(MSAQ_ERR_ARG, "B, H, Hkv and Lk must be positive");
+    if (H % Hkv) return fail(MSAQ_ERR_ARG, "H (%lld) must be a multiple of Hkv (%lld)", (long long)H, (long long)Hkv);
+    if (D != 32 && D != 64 && D != 128 && D != 256)
+        return fail(MSAQ_ERR_UNSUPPORTED, "head_dim %lld: must be 32, 64, 128 or 256", (long long)D);
+    if (NB * BLOCK != D) return fail(MSAQ_ERR_ARG, "NB (%lld) must equal D/32 (D=%lld)", (long long)NB, (long long)D);
+    if (Lcap < 0) Lcap = Lk;
+    if (Lcap < Lk) return fail(MSAQ_ERR_ARG, "Lcap (%lld) is smaller than Lk (%lld)", (long long)Lcap, (long long)Lk);
+    if (Lk > INT32_MAX || Lcap > INT32_MAX || B > 65535 || H > INT32_MAX)
+        return fail(MSAQ_ERR_ARG, "size exceeds the supported range");
+    if ((reinterpret_cast<uintptr_t>(kp.u) | reinterpret_cast<uintptr_t>(vp.u)) & 3)
+        return fail(MSAQ_ERR_ARG, "upper planes must be 4-byte aligned");
+    if (int rc = require_sm100()) return rc;
+    const size_t need = msaq_kv_decode_workspace(B, H, Hkv, Lk, D);
+    if (!ws || ws_bytes < need)
+        return fail(MSAQ_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", need, ws ? ws_bytes : (size_t)0);
+
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const KvPlan p = plan_generic(B, H, Lk);
+    const float sm_scale = (float)(1.0 / sqrt((double)D));
+    float* partial = static_cast<float*>(ws);
+    const __nv_bfloat16* qq = static_cast<const __nv_bfloat16*>(q);
+    dim3 grid((unsigned)H, (unsigned)p.S, (unsigned)B);
+    const size_t smem = ((size_t)D + KVG_CHUNK) * sizeof(float);
+#define MSAQ_GO(U) kv_decode_generic_kernel<U><<<grid, KVG_THREADS, smem, st>>>( \
+        qq, kp, vp, partial, seq_lens, (int)H, (int)Hkv, (int)Lk, (int)Lcap, (int)D, (int)NB, f, p.key_tile, p.S, \
+        sm_scale, qrot)
+    if (u == 4) MSAQ_GO(4); else if (u == 3) MSAQ_GO(3); else MSAQ_GO(2);
+#undef MSAQ_GO
+    count_launch();
+    if (int rc = check_launch("kv_decode_generic")) return rc;
+    kv_decode_combine_kernel<<<dim3((unsigned)H, (unsigned)B), 128, 0, st>>>(
+        partial, static_cast<__nv_bfloat16*>(out), out_f32, (int)H, (int)D, p.S);
+    count_launch();
+    return check_launch("kv_decode_combine");
+}
+
+}  // namespace
+}  // namespace msaq
+
+using namespace msaq;
+
+extern "C" size_t msaq_kv_decode_workspace(int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D) {
+    (void)Hkv;
+    if (B <= 0 || H <= 0 || Lk <= 0 || D <= 0) return 0;
+    const KvPlan p = plan_generic(B, H, Lk);
+    const size_t bytes = (size_t)B * H * p.S * kv_partial_stride((int)D) * sizeof(float);
+    return (bytes + 255) & ~(size_t)255;
+}
+
+extern "C" int msaq_kv_decode_attention(const void* q, const int8_t* ks, const uint8_t* ku, const uint8_t* kh,
+                                        const int8_t* vs, const uint8_t* vu, const uint8_t* vh, void* out,
+                                        float* out_f32, int64_t H, int64_t Hkv, int64_t Lk, int64_t D, int64_t NB,
+                                        int u, int gs, int64_t Lcap, void* workspace, size_t workspace_bytes,
+                                        void* stream) {
+    return decode_dispatch(q, KvPlanes{ks, ku, kh}, KvPlanes{vs, vu, vh}, out, out_f32, nullptr, 1, H, Hkv, Lk, D, NB,
+                           u, gs, Lcap, 0, workspace, workspace_bytes, stream);
+}
+
+extern "C" int msaq_kv_decode_attention_batched(const void* q, const int8_t* ks, const uint8_t* ku, const uint8_t* kh,
+                                                const int8_t* vs, const uint8_t* vu, const uint8_t* vh, void* out,
+                                                float* out_f32, const int32_t* seq_lens, int64_t B, int64_t H,
+                                                int64_t Hkv, int64_t Lk, int64_t D, int64_t NB, int u, int gs,
+                                                int64_t Lcap, int qrot, void* workspace, size_t workspace_bytes,
+                                                void* stream) {
+    return decode_dispatch(q, KvPlanes{ks, ku, kh}, KvPlanes{vs, vu, vh}, out, out_f32, seq_lens, B, H, Hkv, Lk, D, NB,
+                           u, gs, Lcap, qrot, workspace, workspace_bytes, stream);
+}

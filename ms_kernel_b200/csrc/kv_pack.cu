@@ -1,0 +1,210 @@
+// Quantise-and-pack kernels: KV append / append-with-rotation / prefill write,
+// the standalone Hadamard rotation, and the offline weight packer.
+//
+// One warp owns one row of D values (D = 32*EPL): it loads the row, optionally
+// runs the Hadamard butterfly in registers, parks the fp32 row in shared
+// memory, and lanes 0..NB-1 each quantise one 32-block in float64 and store it.
+// Behaviour replaced: csrc/kv_attention.cu:1766-1870 (kv_write / kv_append /
+// kv_append_rot kernels) and csrc/rotate.cu:40-69 of the reference.
+#include "msaq_common.cuh"
+
+namespace msaq {
+namespace {
+
+constexpr int ROWS_PER_CTA = 4;   // warps per block, one row each
+
+struct RowMap {
+    int64_t rows;            // total rows = heads * rows_per_head
+    int64_t rows_per_head;   // 1 for append, L for prefill write
+    int64_t key0;            // first slot (append: pos)
+    int64_t Lcap;            // key stride of the planes
+    const int32_t* pos;      // optional per-sequence slot (varlen append)
+    int64_t heads_per_seq;   // Hkv, used with pos
+};
+
+template <int EPL, bool ROT>
+__global__ void __launch_bounds__(ROWS_PER_CTA * 32)
+quantize_rows_kernel(const __nv_bfloat16* __restrict__ X, int8_t* __restrict__ scale_exp,
+                     uint8_t* __restrict__ upper, uint8_t* __restrict__ shared,
+                     RowMap map, Fmt f) {
+    constexpr int D = 32 * EPL, NB = EPL;
+    __shared__ float rowbuf[ROWS_PER_CTA][D];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * ROWS_PER_CTA + warp;
+    if (row >= map.rows) return;
+
+    float v[EPL];
+    const __nv_bfloat16* src = X + row * D + lane * EPL;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) v[i] = __bfloat162float(src[i]);
+    if (ROT) {
+        fwht_warp<EPL>(v, lane);
+        const float inv = (float)(1.0 / sqrt((double)D));
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) v[i] = v[i] * inv;
+    }
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) rowbuf[warp][lane * EPL + i] = v[i];
+    __syncwarp();
+
+    if (lane < NB) {
+        const int64_t head = row / map.rows_per_head;
+        int64_t key = map.key0 + row % map.rows_per_head;
+        if (map.pos) key = map.pos[head / map.heads_per_seq];
+        const int64_t slot = (head * NB + lane) * map.Lcap + key;
+        store_block(&rowbuf[warp][lane * BLOCK], f, scale_exp, upper, shared, slot);
+    }
+}
+
+template <int EPL>
+__global__ void __launch_bounds__(ROWS_PER_CTA * 32)
+hadamard_rotate_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int64_t N) {
+    constexpr int D = 32 * EPL;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * ROWS_PER_CTA + warp;
+    if (row >= N) return;
+    float v[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) v[i] = __bfloat162float(x[row * D + lane * EPL + i]);
+    fwht_warp<EPL>(v, lane);
+    const float inv = (float)(1.0 / sqrt((double)D));
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) out[row * D + lane * EPL + i] = __float2bfloat16_rn(v[i] * inv);
+}
+
+// One thread per (output row o, block): quantise 32 weights and scatter the
+// bytes into whichever planes were requested.
+__global__ void __launch_bounds__(128)
+pack_weight_kernel(const void* __restrict__ W, int w_is_bf16, int8_t* __restrict__ scale_exp,
+                   uint8_t* __restrict__ upper, uint8_t* __restrict__ shared,
+                   uint8_t* __restrict__ upper_cm, uint8_t* __restrict__ shared_cm,
+                   int64_t OUT, int64_t nb, Fmt f) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= OUT * nb) return;
+    const int64_t blk = t / OUT, o = t % OUT;      // consecutive threads -> consecutive columns
+    float x[BLOCK];
+    const int64_t base = o * nb * BLOCK + blk * BLOCK;
+    if (w_is_bf16) {
+        const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(W) + base;
+#pragma unroll
+        for (int k = 0; k < BLOCK; ++k) x[k] = __bfloat162float(w[k]);
+    } else {
+        const float* w = static_cast<const float*>(W) + base;
+#pragma unroll
+        for (int k = 0; k < BLOCK; ++k) x[k] = w[k];
+    }
+    int up[BLOCK], sh[16];
+    const int e = quantize_block(x, f, up, sh);
+    uint32_t uw[7], sw[3];
+    pack_codes(up, BLOCK, f.wbits, uw, 7);
+    pack_codes(sh, f.ng, f.u, sw, 3);
+    if (scale_exp) scale_exp[blk * OUT + o] = (int8_t)e;
+    for (int i = 0; i < f.UB; ++i) {
+        const uint8_t b = (uint8_t)(uw[i >> 2] >> ((i & 3) * 8));
+        if (upper) upper[(blk * f.UB + i) * OUT + o] = b;
+        if (upper_cm) upper_cm[(blk * OUT + o) * f.UB + i] = b;
+    }
+    for (int i = 0; i < f.SB; ++i) {
+        const uint8_t b = (uint8_t)(sw[i >> 2] >> ((i & 3) * 8));
+        if (shared) shared[(blk * f.SB + i) * OUT + o] = b;
+        if (shared_cm) shared_cm[(blk * OUT + o) * f.SB + i] = b;
+    }
+}
+
+template <bool ROT>
+int launch_rows(const void* X, int8_t* se, uint8_t* up, uint8_t* sh, const RowMap& map, int64_t D,
+                const Fmt& f, cudaStream_t st) {
+    if (map.rows == 0) return MSAQ_OK;
+    const unsigned grid = (unsigned)((map.rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA);
+    const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
+    switch (D) {
+        case 32:  quantize_rows_kernel<1, ROT><<<grid, ROWS_PER_CTA * 32, 0, st>>>(x, se, up, sh, map, f); break;
+        case 64:  quantize_rows_kernel<2, ROT><<<grid, ROWS_PER_CTA * 32, 0, st>>>(x, se, up, sh, map, f); break;
+        case 128: quantize_rows_kernel<4, ROT><<<grid, ROWS_PER_CTA * 32, 0, st>>>(x, se, up, sh, map, f); break;
+        case 256: quantize_rows_kernel<8, ROT><<<grid, ROWS_PER_CTA * 32, 0, st>>>(x, se, up, sh, map, f); break;
+        default: return fail(MSAQ_ERR_UNSUPPORTED, "head_dim %lld: must be 32, 64, 128 or 256", (long long)D);
+    }
+    count_launch();
+    return check_launch("quantize_rows");
+}
+
+int quantize_rows(const void* X, int8_t* se, uint8_t* up, uint8_t* sh, const RowMap& map, int64_t D,
+                  int64_t NB, int u, int gs, bool rot, void* stream) {
+    Fmt f;
+    if (!make_fmt(u, gs, &f)) return fail(MSAQ_ERR_UNSUPPORTED, "unsupported format u=%d gs=%d", u, gs);
+    if (!X || !se || !up || !sh) return fail(MSAQ_ERR_ARG, "null pointer");
+    if (NB * BLOCK != D) return fail(MSAQ_ERR_ARG, "NB (%lld) must equal D/32 (D=%lld)", (long long)NB, (long long)D);
+    if (map.rows < 0 || map.Lcap <= 0) return fail(MSAQ_ERR_ARG, "bad row count or capacity");
+    if (!map.pos && (map.key0 < 0 || map.key0 + map.rows_per_head > map.Lcap))
+        return fail(MSAQ_ERR_ARG, "slots [%lld, %lld) exceed the cache capacity %lld", (long long)map.key0,
+                    (long long)(map.key0 + map.rows_per_head), (long long)map.Lcap);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return rot ? launch_rows<true>(X, se, up, sh, map, D, f, st) : launch_rows<false>(X, se, up, sh, map, D, f, st);
+}
+
+}  // namespace
+}  // namespace msaq
+
+using namespace msaq;
+
+extern "C" int msaq_kv_append(const void* X, int8_t* scale_exp, uint8_t* upper, uint8_t* shared, int64_t H,
+                              int64_t D, int64_t NB, int64_t pos, int64_t Lcap, int u, int gs, void* stream) {
+    RowMap m{H, 1, pos, Lcap, nullptr, 1};
+    return quantize_rows(X, scale_exp, upper, shared, m, D, NB, u, gs, false, stream);
+}
+
+extern "C" int msaq_kv_append_rot(const void* X, int8_t* scale_exp, uint8_t* upper, uint8_t* shared, int64_t H,
+                                  int64_t D, int64_t NB, int64_t pos, int64_t Lcap, int u, int gs, void* stream) {
+    RowMap m{H, 1, pos, Lcap, nullptr, 1};
+    return quantize_rows(X, scale_exp, upper, shared, m, D, NB, u, gs, true, stream);
+}
+
+extern "C" int msaq_kv_append_varlen(const void* X, int8_t* scale_exp, uint8_t* upper, uint8_t* shared, int64_t B,
+                                     int64_t Hkv, int64_t D, int64_t NB, const int32_t* pos, int64_t Lcap, int u,
+                                     int gs, int rotate, void* stream) {
+    if (!pos) return fail(MSAQ_ERR_ARG, "pos is null");
+    if (Hkv <= 0) return fail(MSAQ_ERR_ARG, "Hkv must be positive");
+    RowMap m{B * Hkv, 1, 0, Lcap, pos, Hkv};
+    return quantize_rows(X, scale_exp, upper, shared, m, D, NB, u, gs, rotate != 0, stream);
+}
+
+extern "C" int msaq_kv_write(const void* X, int8_t* scale_exp, uint8_t* upper, uint8_t* shared, int64_t H, int64_t L,
+                             int64_t D, int64_t NB, int64_t key0, int64_t Lcap, int u, int gs, int rotate,
+                             void* stream) {
+    if (L < 0 || H < 0) return fail(MSAQ_ERR_ARG, "negative size");
+    if (L == 0) return MSAQ_OK;
+    RowMap m{H * L, L, key0, Lcap, nullptr, 1};
+    return quantize_rows(X, scale_exp, upper, shared, m, D, NB, u, gs, rotate != 0, stream);
+}
+
+extern "C" int msaq_hadamard_rotate(const void* x, void* out, int64_t N, int64_t D, void* stream) {
+    if (!x || !out) return fail(MSAQ_ERR_ARG, "null pointer");
+    if (N <= 0) return N == 0 ? MSAQ_OK : fail(MSAQ_ERR_ARG, "negative row count");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned grid = (unsigned)((N + ROWS_PER_CTA - 1) / ROWS_PER_CTA);
+    const __nv_bfloat16* xi = static_cast<const __nv_bfloat16*>(x);
+    __nv_bfloat16* xo = static_cast<__nv_bfloat16*>(out);
+    switch (D) {
+        case 32:  hadamard_rotate_kernel<1><<<grid, ROWS_PER_CTA * 32, 0, st>>>(xi, xo, N); break;
+        case 64:  hadamard_rotate_kernel<2><<<grid, ROWS_PER_CTA * 32, 0, st>>>(xi, xo, N); break;
+        case 128: hadamard_rotate_kernel<4><<<grid, ROWS_PER_CTA * 32, 0, st>>>(xi, xo, N); break;
+        case 256: hadamard_rotate_kernel<8><<<grid, ROWS_PER_CTA * 32, 0, st>>>(xi, xo, N); break;
+        default: return fail(MSAQ_ERR_UNSUPPORTED, "rotate: last dim %lld must be 32, 64, 128 or 256", (long long)D);
+    }
+    count_launch();
+    return check_launch("hadamard_rotate");
+}
+
+extern "C" int msaq_pack_weight(const void* W, int w_is_bf16, int8_t* scale_exp, uint8_t* upper, uint8_t* shared,
+                                uint8_t* upper_cm, uint8_t* shared_cm, int64_t OUT, int64_t K, int u, int gs,
+                                void* stream) {
+    Fmt f;
+    if (!make_fmt(u, gs, &f)) return fail(MSAQ_ERR_UNSUPPORTED, "unsupported format u=%d gs=%d", u, gs);
+    if (!W) return fail(MSAQ_ERR_ARG, "W is null");
+    if (OUT <= 0 || K <= 0 || K % BLOCK) return fail(MSAQ_ERR_ARG, "K must be a positive multiple of 32");
+    const int64_t nb = K / BLOCK, total = OUT * nb;
+    pack_weight_kernel<<<(unsigned)((total + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        W, w_is_bf16, scale_exp, upper, shared, upper_cm, shared_cm, OUT, nb, f);
+    count_launch();
+    return check_launch("pack_weight");
+}

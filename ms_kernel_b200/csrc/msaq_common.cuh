@@ -1,0 +1,163 @@
+// Shared device/host helpers of the MSAQ-signed decode kernels (sm_100a).
+//
+// Format constants and the block numerics follow ms_lib/pack.py:22-60 of the
+// reference; the bit layout follows ms_lib/pack.py:82-98.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/msaq_b200.h"
+
+namespace msaq {
+
+constexpr int BLOCK = 32;
+constexpr int E_MAX = 6;
+
+// Derived sizes of one (u, gs) format.
+struct Fmt {
+    int u, gs, lg_gs, wbits, UB, SB, ng;
+};
+
+inline bool make_fmt(int u, int gs, Fmt* f) {
+    if (u < 2 || u > 4) return false;
+    int lg = 0;
+    while ((1 << lg) < gs) ++lg;
+    if ((1 << lg) != gs || gs < 2 || gs > 32) return false;
+    f->u = u; f->gs = gs; f->lg_gs = lg; f->wbits = 8 - u;
+    f->UB = BLOCK * f->wbits / 8;
+    f->ng = BLOCK / gs;
+    f->SB = (f->ng * u + 7) / 8;
+    return true;
+}
+
+// ---- host-side error plumbing (defined in capi.cu) -------------------------
+int fail(int code, const char* fmt, ...);
+int check_launch(const char* what);
+void count_launch(int n = 1);
+int sm_count();               // SM count of the current device (cached per device)
+int require_sm100();          // MSAQ_OK or MSAQ_ERR_DEVICE
+
+// ---- small device helpers ---------------------------------------------------
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
+__device__ __forceinline__ float bf16_lo(uint32_t pair) { return __uint_as_float(pair << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t pair) { return __uint_as_float(pair & 0xFFFF0000u); }
+
+// 2^e as float for e in [-126, 127]; below that the subnormal / zero value.
+__device__ __forceinline__ float exp2_int(int e) {
+    return (e >= -126) ? __int_as_float((e + 127) << 23) : ldexpf(1.0f, e);
+}
+
+__device__ __forceinline__ int sext(uint32_t v, int width) {
+    return ((int)(v << (32 - width))) >> (32 - width);
+}
+
+// Code `idx` of `width` bits from a little-endian word run (run must have one
+// readable word past the last code when a code straddles a word boundary).
+__device__ __forceinline__ int code_from_words(const uint32_t* w, int idx, int width) {
+    const int bit = idx * width, wi = bit >> 5, off = bit & 31;
+    uint32_t v = w[wi] >> off;
+    if (off + width > 32) v |= w[wi + 1] << (32 - off);
+    return sext(v, width);
+}
+
+// Block exponent from the block's max-abs: clip(floor(log2(max(amax, 1e-30))) - 6, +-127).
+__device__ __forceinline__ int block_exponent(float amax) {
+    int fl;
+    if (!((double)amax >= 1e-30)) fl = -100;                      // floor(log2(1e-30)) = -100
+    else if (isinf(amax)) fl = 1000;
+    else fl = (int)((__float_as_uint(amax) >> 23) & 0xFF) - 127;  // normal numbers only reach here
+    const int e = fl - E_MAX;
+    return max(-127, min(127, e));
+}
+
+// Quantise one 32-block.  Arithmetic is float64 in the order NumPy evaluates
+// ms_lib/pack.py:47-60, so the codes equal the reference's bit for bit.
+//   up[k] : (8-u)-bit signed, sh[g] : u-bit signed, returns the exponent.
+__device__ inline int quantize_block(const float* x, const Fmt& f, int* up, int* sh) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < BLOCK; ++k) amax = fmaxf(amax, fabsf(x[k]));
+    const int e = block_exponent(amax);
+    const double fine = ldexp(1.0, e), coarse = ldexp(1.0, e + f.u);
+    const int lim = (1 << (7 - f.u)) - 1, slo = -(1 << (f.u - 1)), shi = (1 << (f.u - 1)) - 1;
+    for (int g = 0; g < f.ng; ++g) {
+        double r[8];
+        double sum = 0.0;
+        for (int t = 0; t < f.gs; ++t) {
+            const int k = g * f.gs + t;
+            const double xv = (double)x[k];
+            double q = rint(xv / coarse);
+            q = fmin(fmax(q, (double)-lim), (double)lim);
+            up[k] = (int)q;
+            const double res = xv - q * coarse;
+            if (f.gs < 8) sum += res;                      // NumPy: plain running sum below 8 terms
+            else if (t < 8) r[t] = res;                    // NumPy: 8 interleaved partial sums ...
+            else r[t & 7] += res;
+        }
+        if (f.gs >= 8) sum = ((r[0] + r[1]) + (r[2] + r[3])) + ((r[4] + r[5]) + (r[6] + r[7]));
+        double s = rint((sum / (double)f.gs) / fine);
+        s = fmin(fmax(s, (double)slo), (double)shi);
+        sh[g] = (int)s;
+    }
+    return e;
+}
+
+// Dense LSB-first packing of n codes of `width` bits into zeroed words.
+__device__ inline void pack_codes(const int* codes, int n, int width, uint32_t* words, int nwords) {
+    for (int i = 0; i < nwords; ++i) words[i] = 0u;
+    const uint32_t mask = (1u << width) - 1u;
+    for (int i = 0; i < n; ++i) {
+        const uint32_t c = (uint32_t)codes[i] & mask;
+        const int bit = i * width, wi = bit >> 5, off = bit & 31;
+        words[wi] |= c << off;
+        if (off + width > 32) words[wi + 1] |= c >> (32 - off);
+    }
+}
+
+// Quantise + pack + store one block at `slot` of token-major planes
+// (scale_exp[slot], upper[slot*UB..], shared[slot*SB..]).
+__device__ inline void store_block(const float* x, const Fmt& f, int8_t* scale_exp, uint8_t* upper,
+                                   uint8_t* shared, int64_t slot) {
+    int up[BLOCK], sh[16];
+    const int e = quantize_block(x, f, up, sh);
+    uint32_t uw[7], sw[3];
+    pack_codes(up, BLOCK, f.wbits, uw, 7);
+    pack_codes(sh, f.ng, f.u, sw, 3);
+    uint32_t* du = reinterpret_cast<uint32_t*>(upper + slot * f.UB);   // UB is a multiple of 4
+    for (int i = 0; i < f.UB / 4; ++i) du[i] = uw[i];
+    uint8_t* ds = shared + slot * f.SB;
+    for (int i = 0; i < f.SB; ++i) ds[i] = (uint8_t)(sw[i >> 2] >> ((i & 3) * 8));
+    scale_exp[slot] = (int8_t)e;
+}
+
+// In-register Walsh-Hadamard butterfly over a row of 32*EPL values held as EPL
+// consecutive elements per lane.  Stage order h = 1, 2, 4, ...: strides below
+// EPL stay inside the lane, the rest are lane exchanges.  Every stage is one
+// fp32 add or subtract per element, so the result does not depend on which
+// thread evaluates it.
+template <int EPL>
+__device__ __forceinline__ void fwht_warp(float (&v)[EPL], int lane) {
+#pragma unroll
+    for (int h = 1; h < EPL; h <<= 1) {
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            if ((i & h) == 0) {
+                const float a = v[i], b = v[i + h];
+                v[i] = a + b;
+                v[i + h] = a - b;
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], m);
+            v[i] = (lane & m) ? (other - v[i]) : (v[i] + other);
+        }
+    }
+}
+
+}  // namespace msaq

@@ -1,0 +1,317 @@
+// `ms_cuda`: the torch operator surface of the decode path.
+//
+// Importing the module registers torch.ops.msaq.* with the schemas of the
+// reference (csrc/pybind.cpp:198-286); each op checks its tensors, allocates
+// outputs and scratch through torch's caching allocator, and forwards to the C
+// ABI in include/msaq_b200.h on the current CUDA stream.  No host sync, so the
+// ops can be captured in CUDA graphs.
+#include <Python.h>
+
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include <cstdlib>
+
+#include "../../include/msaq_b200.h"
+
+namespace {
+
+using at::Tensor;
+
+void check_rc(int rc, const char* op) {
+    TORCH_CHECK(rc == MSAQ_OK, "msaq::", op, " failed (", rc, "): ", msaq_last_error());
+}
+
+void check_act(const Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16, name, " must be a CUDA bf16 tensor");
+    TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+
+void check_plane(const Tensor& t, at::ScalarType ty, const Tensor& like, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == ty, name, " has the wrong dtype or is not on CUDA");
+    TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+    TORCH_CHECK(t.device() == like.device(), name, " is on a different device than the activation");
+}
+
+void check_planes(const Tensor& s, const Tensor& u, const Tensor& h, const Tensor& like, int64_t n_blocks, int64_t UB,
+                  int64_t SB) {
+    check_plane(s, at::kChar, like, "scale_exp");
+    check_plane(u, at::kByte, like, "upper");
+    check_plane(h, at::kByte, like, "shared");
+    TORCH_CHECK(s.numel() >= n_blocks, "scale_exp holds ", s.numel(), " blocks, ", n_blocks, " needed");
+    TORCH_CHECK(u.numel() >= n_blocks * UB, "upper plane too small");
+    TORCH_CHECK(h.numel() >= n_blocks * SB, "shared plane too small");
+}
+
+void fmt_sizes(int64_t u, int64_t gs, int64_t* UB, int64_t* SB) {
+    TORCH_CHECK(u >= 2 && u <= 4, "u must be 2, 3 or 4");
+    TORCH_CHECK(gs == 2 || gs == 4 || gs == 8 || gs == 16 || gs == 32, "gs must be a power of two in [2, 32]");
+    *UB = 32 * (8 - u) / 8;
+    *SB = ((32 / gs) * u + 7) / 8;
+}
+
+void* stream_of(const Tensor& t) { return at::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
+
+Tensor workspace(const Tensor& like, size_t bytes) {
+    return at::empty({(int64_t)(bytes ? bytes : 256)}, like.options().dtype(at::kByte));
+}
+
+// ---- GEMV ---------------------------------------------------------------
+Tensor gemv_common(const Tensor& x, const Tensor& s, const Tensor& up, const Tensor& sh, int64_t M, int64_t OUT,
+                   int64_t NB, int64_t u, int64_t gs, int kind) {
+    check_act(x, "x");
+    int64_t UB, SB;
+    fmt_sizes(u, gs, &UB, &SB);
+    TORCH_CHECK(M >= 1 && OUT >= 1 && NB >= 1, "M, OUT and NB must be positive");
+    TORCH_CHECK(x.numel() == M * NB * 32, "x has ", x.numel(), " elements, expected M*K = ", M * NB * 32);
+    check_planes(s, up, sh, x, NB * OUT, UB, SB);
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor y = kind == 2 ? at::empty({M, OUT}, x.options()) : at::empty({OUT}, x.options());
+    const size_t wsb = msaq_wonly_gemv_workspace(M, OUT, NB, (int)u, (int)gs);
+    Tensor ws = workspace(x, wsb);
+    int rc;
+    if (kind == 0)
+        rc = msaq_wonly_gemv(x.data_ptr(), s.data_ptr<int8_t>(), up.data_ptr<uint8_t>(), sh.data_ptr<uint8_t>(),
+                             y.data_ptr(), nullptr, OUT, NB, (int)u, (int)gs, ws.data_ptr(), wsb, stream_of(x));
+    else if (kind == 1)
+        rc = msaq_wonly_gemv_wide(x.data_ptr(), s.data_ptr<int8_t>(), up.data_ptr<uint8_t>(), sh.data_ptr<uint8_t>(),
+                                  y.data_ptr(), nullptr, OUT, NB, (int)u, (int)gs, ws.data_ptr(), wsb, stream_of(x));
+    else
+        rc = msaq_wonly_gemv_batched(x.data_ptr(), s.data_ptr<int8_t>(), up.data_ptr<uint8_t>(),
+                                     sh.data_ptr<uint8_t>(), y.data_ptr(), nullptr, M, OUT, NB, (int)u, (int)gs,
+                                     ws.data_ptr(), wsb, stream_of(x));
+    check_rc(rc, kind == 0 ? "wonly_gemv" : kind == 1 ? "wonly_gemv_wide" : "wonly_gemv_batched");
+    return y;
+}
+
+Tensor wonly_gemv(const Tensor& x, const Tensor& s, const Tensor& up, const Tensor& sh, int64_t OUT, int64_t NB,
+                  int64_t u, int64_t gs) {
+    return gemv_common(x, s, up, sh, 1, OUT, NB, u, gs, 0);
+}
+Tensor wonly_gemv_wide(const Tensor& x, const Tensor& s, const Tensor& up, const Tensor& sh, int64_t OUT, int64_t NB,
+                       int64_t u, int64_t gs) {
+    return gemv_common(x, s, up, sh, 1, OUT, NB, u, gs, 1);
+}
+Tensor wonly_gemv_batched(const Tensor& x, const Tensor& s, const Tensor& up, const Tensor& sh, int64_t M, int64_t OUT,
+                          int64_t NB, int64_t u, int64_t gs) {
+    return gemv_common(x, s, up, sh, M, OUT, NB, u, gs, 2);
+}
+
+// ---- KV write paths -------------------------------------------------------
+void append_common(const Tensor& X, Tensor& s, Tensor& up, Tensor& sh, int64_t H, int64_t D, int64_t NB, int64_t pos,
+                   int64_t Lcap, int64_t u, int64_t gs, bool rot) {
+    check_act(X, "X");
+    int64_t UB, SB;
+    fmt_sizes(u, gs, &UB, &SB);
+    TORCH_CHECK(X.numel() == H * D, "X must hold H*D elements");
+    TORCH_CHECK(pos >= 0 && pos < Lcap, "pos ", pos, " is outside the cache capacity ", Lcap);
+    check_planes(s, up, sh, X, H * NB * Lcap, UB, SB);
+    c10::cuda::CUDAGuard guard(X.device());
+    const int rc = rot ? msaq_kv_append_rot(X.data_ptr(), s.data_ptr<int8_t>(), up.data_ptr<uint8_t>(),
+                                            sh.data_ptr<uint8_t>(), H, D, NB, pos, Lcap, (int)u, (int)gs, stream_of(X))
+                       : msaq_kv_append(X.data_ptr(), s.data_ptr<int8_t>(), up.data_ptr<uint8_t>(),
+                                        sh.data_ptr<uint8_t>(), H, D, NB, pos, Lcap, (int)u, (int)gs, stream_of(X));
+    check_rc(rc, rot ? "kv_append_rot" : "kv_append");
+}
+
+void kv_append(const Tensor& X, Tensor s, Tensor up, Tensor sh, int64_t H, int64_t D, int64_t NB, int64_t pos,
+               int64_t Lcap, int64_t u, int64_t gs) {
+    append_common(X, s, up, sh, H, D, NB, pos, Lcap, u, gs, false);
+}
+void kv_append_rot(const Tensor& X, Tensor s, Tensor up, Tensor sh, int64_t H, int64_t D, int64_t NB, int64_t pos,
+                   int64_t Lcap, int64_t u, int64_t gs) {
+    append_common(X, s, up, sh, H, D, NB, pos, Lcap, u, gs, true);
+}
+
+void kv_append_varlen(const Tensor& X, Tensor s, Tensor up, Tensor sh, const Tensor& pos, int64_t B, int64_t Hkv,
+                      int64_t D, int64_t NB, int64_t Lcap, int64_t u, int64_t gs, bool rotate) {
+    check_act(X, "X");
+    int64_t UB, SB;
+    fmt_sizes(u, gs, &UB, &SB);
+    TORCH_CHECK(X.numel() == B * Hkv * D, "X must hold B*Hkv*D elements");
+    TORCH_CHECK(pos.is_cuda() && pos.scalar_type() == at::kInt && pos.is_contiguous() && pos.numel() == B,
+                "pos must be a contiguous CUDA int32 tensor of B elements");
+    check_planes(s, up, sh, X, B * Hkv * NB * Lcap, UB, SB);
+    c10::cuda::CUDAGuard guard(X.device());
+    check_rc(msaq_kv_append_varlen(X.data_ptr(), s.data_ptr<int8_t>(), up.data_ptr<uint8_t>(), sh.data_ptr<uint8_t>(),
+                                   B, Hkv, D, NB, pos.data_ptr<int32_t>(), Lcap, (int)u, (int)gs, rotate ? 1 : 0,
+                                   stream_of(X)),
+             "kv_append_varlen");
+}
+
+std::vector<Tensor> kv_write_impl(const Tensor& X, int64_t H, int64_t L, int64_t D, int64_t NB, int64_t u, int64_t gs,
+                                  bool rot) {
+    check_act(X, "X");
+    int64_t UB, SB;
+    fmt_sizes(u, gs, &UB, &SB);
+    TORCH_CHECK(X.numel() == H * L * D, "X must hold H*L*D elements");
+    c10::cuda::CUDAGuard guard(X.device());
+    Tensor s = at::empty({H, NB, L}, X.options().dtype(at::kChar));
+    Tensor up = at::empty({H, NB, L, UB}, X.options().dtype(at::kByte));
+    Tensor sh = at::empty({H, NB, L, SB}, X.options().dtype(at::kByte));
+    check_rc(msaq_kv_write(X.data_ptr(), s.data_ptr<int8_t>(), up.data_ptr<uint8_t>(), sh.data_ptr<uint8_t>(), H, L, D,
+                           NB, 0, L, (int)u, (int)gs, rot ? 1 : 0, stream_of(X)),
+             "kv_write");
+    return {s, up, sh};
+}
+std::vector<Tensor> kv_write(const Tensor& X, int64_t H, int64_t L, int64_t D, int64_t NB, int64_t u, int64_t gs) {
+    return kv_write_impl(X, H, L, D, NB, u, gs, false);
+}
+std::vector<Tensor> kv_write_rot(const Tensor& X, int64_t H, int64_t L, int64_t D, int64_t NB, int64_t u,
+                                 int64_t gs) {
+    return kv_write_impl(X, H, L, D, NB, u, gs, true);
+}
+
+void kv_write_into(const Tensor& X, Tensor s, Tensor up, Tensor sh, int64_t H, int64_t L, int64_t D, int64_t NB,
+                   int64_t key0, int64_t Lcap, int64_t u, int64_t gs, bool rotate) {
+    check_act(X, "X");
+    int64_t UB, SB;
+    fmt_sizes(u, gs, &UB, &SB);
+    TORCH_CHECK(X.numel() == H * L * D, "X must hold H*L*D elements");
+    check_planes(s, up, sh, X, H * NB * Lcap, UB, SB);
+    c10::cuda::CUDAGuard guard(X.device());
+    check_rc(msaq_kv_write(X.data_ptr(), s.data_ptr<int8_t>(), up.data_ptr<uint8_t>(), sh.data_ptr<uint8_t>(), H, L, D,
+                           NB, key0, Lcap, (int)u, (int)gs, rotate ? 1 : 0, stream_of(X)),
+             "kv_write_into");
+}
+
+Tensor hadamard_rotate(const Tensor& x) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16, "x must be a CUDA bf16 tensor");
+    Tensor xc = x.contiguous();
+    const int64_t D = xc.size(-1);
+    c10::cuda::CUDAGuard guard(xc.device());
+    Tensor out = at::empty_like(xc);
+    check_rc(msaq_hadamard_rotate(xc.data_ptr(), out.data_ptr(), xc.numel() / D, D, stream_of(xc)), "hadamard_rotate");
+    return out;
+}
+
+std::vector<Tensor> pack_weight(const Tensor& W, int64_t u, int64_t gs) {
+    TORCH_CHECK(W.is_cuda() && W.dim() == 2 && W.is_contiguous(), "W must be a contiguous 2-D CUDA tensor");
+    TORCH_CHECK(W.scalar_type() == at::kBFloat16 || W.scalar_type() == at::kFloat, "W must be bf16 or fp32");
+    int64_t UB, SB;
+    fmt_sizes(u, gs, &UB, &SB);
+    const int64_t OUT = W.size(0), K = W.size(1);
+    TORCH_CHECK(K % 32 == 0, "K must be a multiple of 32");
+    const int64_t nb = K / 32;
+    c10::cuda::CUDAGuard guard(W.device());
+    auto b = W.options().dtype(at::kByte);
+    Tensor s = at::empty({nb, OUT}, W.options().dtype(at::kChar));
+    Tensor up = at::empty({nb, UB, OUT}, b), sh = at::empty({nb, SB, OUT}, b);
+    Tensor upc = at::empty({nb, OUT, UB}, b), shc = at::empty({nb, OUT, SB}, b);
+    check_rc(msaq_pack_weight(W.data_ptr(), W.scalar_type() == at::kBFloat16, s.data_ptr<int8_t>(),
+                              up.data_ptr<uint8_t>(), sh.data_ptr<uint8_t>(), upc.data_ptr<uint8_t>(),
+                              shc.data_ptr<uint8_t>(), OUT, K, (int)u, (int)gs, stream_of(W)),
+             "pack_weight");
+    return {s, up, sh, upc, shc};
+}
+
+// ---- decode attention -------------------------------------------------------
+int env_flag(const char* name) {
+    const char* e = std::getenv(name);
+    return (e && std::atoi(e) != 0) ? 1 : 0;
+}
+
+void reject_numeric_toggles() {
+    TORCH_CHECK(!env_flag("MS_KV_AA"), "MS_KV_AA=1 (fake-quantised attention activations) is not supported");
+}
+
+Tensor decode_common(const Tensor& q, const Tensor& ks, const Tensor& ku, const Tensor& kh, const Tensor& vs,
+                     const Tensor& vu, const Tensor& vh, const c10::optional<Tensor>& seq_lens, int64_t B, int64_t H,
+                     int64_t Hkv, int64_t Lk, int64_t D, int64_t NB, int64_t u, int64_t gs, int64_t Lcap, int qrot,
+                     bool batched) {
+    check_act(q, "q");
+    reject_numeric_toggles();
+    int64_t UB, SB;
+    fmt_sizes(u, gs, &UB, &SB);
+    if (Lcap < 0) Lcap = Lk;
+    TORCH_CHECK(B >= 1 && H >= 1 && Hkv >= 1 && Lk >= 1, "B, H, Hkv and Lk must be positive");
+    TORCH_CHECK(q.numel() == B * H * D, "q must hold B*H*D elements");
+    check_planes(ks, ku, kh, q, B * Hkv * NB * Lcap, UB, SB);
+    check_planes(vs, vu, vh, q, B * Hkv * NB * Lcap, UB, SB);
+    const int32_t* lens = nullptr;
+    if (seq_lens.has_value()) {
+        const Tensor& sl = *seq_lens;
+        TORCH_CHECK(sl.is_cuda() && sl.scalar_type() == at::kInt && sl.is_contiguous() && sl.numel() == B,
+                    "seq_lens must be a contiguous CUDA int32 tensor of B elements");
+        lens = sl.data_ptr<int32_t>();
+    }
+    c10::cuda::CUDAGuard guard(q.device());
+    Tensor out = batched ? at::empty({B, H, D}, q.options()) : at::empty({H, D}, q.options());
+    const size_t wsb = msaq_kv_decode_workspace(B, H, Hkv, Lk, D);
+    Tensor ws = workspace(q, wsb);
+    check_rc(msaq_kv_decode_attention_batched(q.data_ptr(), ks.data_ptr<int8_t>(), ku.data_ptr<uint8_t>(),
+                                              kh.data_ptr<uint8_t>(), vs.data_ptr<int8_t>(), vu.data_ptr<uint8_t>(),
+                                              vh.data_ptr<uint8_t>(), out.data_ptr(), nullptr, lens, B, H, Hkv, Lk, D,
+                                              NB, (int)u, (int)gs, Lcap, qrot, ws.data_ptr(), wsb, stream_of(q)),
+             batched ? "kv_decode_attention_batched" : "kv_decode_attention");
+    return out;
+}
+
+Tensor kv_decode_attention(const Tensor& q, const Tensor& ks, const Tensor& ku, const Tensor& kh, const Tensor& vs,
+                           const Tensor& vu, const Tensor& vh, int64_t H, int64_t Hkv, int64_t Lk, int64_t D,
+                           int64_t NB, int64_t u, int64_t gs, int64_t Lcap) {
+    // The single-sequence op never rotates the query (csrc/kv_attention.cu:2011 of the reference).
+    return decode_common(q, ks, ku, kh, vs, vu, vh, c10::nullopt, 1, H, Hkv, Lk, D, NB, u, gs, Lcap, 0, false);
+}
+
+Tensor kv_decode_attention_batched(const Tensor& q, const Tensor& ks, const Tensor& ku, const Tensor& kh,
+                                   const Tensor& vs, const Tensor& vu, const Tensor& vh, int64_t B, int64_t H,
+                                   int64_t Hkv, int64_t Lk, int64_t D, int64_t NB, int64_t u, int64_t gs,
+                                   int64_t Lcap) {
+    return decode_common(q, ks, ku, kh, vs, vu, vh, c10::nullopt, B, H, Hkv, Lk, D, NB, u, gs, Lcap,
+                         env_flag("MS_KV_QROT"), true);
+}
+
+Tensor kv_decode_attention_varlen(const Tensor& q, const Tensor& ks, const Tensor& ku, const Tensor& kh,
+                                  const Tensor& vs, const Tensor& vu, const Tensor& vh, const Tensor& seq_lens,
+                                  int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D, int64_t NB, int64_t u,
+                                  int64_t gs, int64_t Lcap, bool qrot) {
+    return decode_common(q, ks, ku, kh, vs, vu, vh, seq_lens, B, H, Hkv, Lk, D, NB, u, gs, Lcap, qrot ? 1 : 0, true);
+}
+
+int64_t launch_count() { return (int64_t)msaq_launch_count(); }
+
+}  // namespace
+
+TORCH_LIBRARY(msaq, m) {
+    // schemas of the reference, verbatim (csrc/pybind.cpp:199-206, 235-239, 266-273, 286)
+    m.def("wonly_gemv(Tensor x, Tensor scale_exp, Tensor upper, Tensor shared, "
+          "int OUT, int NB, int u, int gs) -> Tensor", &wonly_gemv);
+    m.def("wonly_gemv_wide(Tensor x, Tensor scale_exp, Tensor upper_cm, Tensor shared_cm, "
+          "int OUT, int NB, int u, int gs) -> Tensor", &wonly_gemv_wide);
+    m.def("wonly_gemv_batched(Tensor x, Tensor scale_exp, Tensor upper_cm, Tensor shared_cm, "
+          "int M, int OUT, int NB, int u, int gs) -> Tensor", &wonly_gemv_batched);
+    m.def("kv_write(Tensor X, int H, int L, int D, int NB, int u, int gs) -> Tensor[]", &kv_write);
+    m.def("kv_append(Tensor X, Tensor(a!) scale_exp, Tensor(b!) upper, Tensor(c!) shared, "
+          "int H, int D, int NB, int pos, int Lcap, int u, int gs) -> ()", &kv_append);
+    m.def("kv_append_rot(Tensor X, Tensor(a!) scale_exp, Tensor(b!) upper, Tensor(c!) shared, "
+          "int H, int D, int NB, int pos, int Lcap, int u, int gs) -> ()", &kv_append_rot);
+    m.def("kv_decode_attention(Tensor q, Tensor ks, Tensor ku, Tensor kh, "
+          "Tensor vs, Tensor vu, Tensor vh, "
+          "int H, int Hkv, int Lk, int D, int NB, int u, int gs, int Lcap=-1) -> Tensor", &kv_decode_attention);
+    m.def("kv_decode_attention_batched(Tensor q, Tensor ks, Tensor ku, Tensor kh, "
+          "Tensor vs, Tensor vu, Tensor vh, "
+          "int B, int H, int Hkv, int Lk, int D, int NB, int u, int gs, int Lcap=-1) -> Tensor",
+          &kv_decode_attention_batched);
+    m.def("hadamard_rotate(Tensor x) -> Tensor", &hadamard_rotate);
+    // additions of this library (no counterpart op in the reference)
+    m.def("kv_write_rot(Tensor X, int H, int L, int D, int NB, int u, int gs) -> Tensor[]", &kv_write_rot);
+    m.def("kv_write_into(Tensor X, Tensor(a!) scale_exp, Tensor(b!) upper, Tensor(c!) shared, "
+          "int H, int L, int D, int NB, int key0, int Lcap, int u, int gs, bool rotate) -> ()", &kv_write_into);
+    m.def("kv_append_varlen(Tensor X, Tensor(a!) scale_exp, Tensor(b!) upper, Tensor(c!) shared, Tensor pos, "
+          "int B, int Hkv, int D, int NB, int Lcap, int u, int gs, bool rotate) -> ()", &kv_append_varlen);
+    m.def("kv_decode_attention_varlen(Tensor q, Tensor ks, Tensor ku, Tensor kh, "
+          "Tensor vs, Tensor vu, Tensor vh, Tensor seq_lens, "
+          "int B, int H, int Hkv, int Lk, int D, int NB, int u, int gs, int Lcap, bool qrot) -> Tensor",
+          &kv_decode_attention_varlen);
+    m.def("pack_weight(Tensor W, int u, int gs) -> Tensor[]", &pack_weight);
+    m.def("launch_count() -> int", &launch_count);
+}
+
+// An importable, otherwise empty Python module: `import ms_cuda` loads this
+// shared object, which runs the registration above.
+static struct PyModuleDef ms_cuda_module = {PyModuleDef_HEAD_INIT, "ms_cuda",
+                                            "Registers torch.ops.msaq.* (B200 decode path).", -1, nullptr};
+PyMODINIT_FUNC PyInit_ms_cuda(void) { return PyModule_Create(&ms_cuda_module); }

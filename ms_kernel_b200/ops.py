@@ -1,0 +1,162 @@
+"""Python API of the decode path; same names and argument meaning as the
+reference's `ms_lib/ops.py` (wonly_gemv :67-82, kv_decode_attention :134-143,
+available :33-35), plus device-resident holders for callers that do not want a
+host-to-device copy of the planes on every call.
+
+Pack dicts are the ones `ms_lib.pack.pack_weight` / `pack_kv` produce (or the
+device packers in `ms_kernel_b200.pack`): NumPy arrays or torch tensors under
+the keys scale_exp / upper / shared / upper_cm / shared_cm plus the meta ints.
+"""
+
+import os
+import sys
+
+_IMPORT_ERROR = None
+try:
+    import torch
+    from . import ms_cuda as _ms_cuda          # side effect: registers torch.ops.msaq.*
+    sys.modules.setdefault("ms_cuda", _ms_cuda)  # so `import ms_cuda` finds this build
+    _OPS = torch.ops.msaq
+    _AVAILABLE = True
+except Exception as e:                          # torch missing or extension not built
+    _IMPORT_ERROR = e
+    _AVAILABLE = False
+    _OPS = None
+
+
+def available() -> bool:
+    """True iff the compiled `ms_cuda` module imported and registered the ops."""
+    return _AVAILABLE
+
+
+def _require():
+    if not _AVAILABLE:
+        raise RuntimeError(
+            "ms_cuda backend not available (%s: %s). Build it with "
+            "`python -m ms_kernel_b200.build`; there is no fallback path."
+            % (type(_IMPORT_ERROR).__name__, _IMPORT_ERROR))
+
+
+def _dev(t, device):
+    """NumPy array or tensor -> tensor on `device` (no copy if already there)."""
+    if isinstance(t, torch.Tensor):
+        return t.to(device)
+    return torch.from_numpy(t).to(device)
+
+
+# --------------------------------------------------------------------------
+# reference-compatible wrappers (planes travel host -> device on every call)
+# --------------------------------------------------------------------------
+def wonly_gemv(p, x_bf16):
+    """W-only decode GEMV.  p from pack_weight; x_bf16 [K] -> y [OUT] bf16."""
+    _require()
+    dev = x_bf16.device
+    s = _dev(p["scale_exp"], dev)
+    if "upper_cm" in p:
+        return _OPS.wonly_gemv_wide(x_bf16, s, _dev(p["upper_cm"], dev), _dev(p["shared_cm"], dev),
+                                    int(p["OUT"]), int(p["nb"]), int(p["u"]), int(p["gs"]))
+    return _OPS.wonly_gemv(x_bf16, s, _dev(p["upper"], dev), _dev(p["shared"], dev),
+                           int(p["OUT"]), int(p["nb"]), int(p["u"]), int(p["gs"]))
+
+
+def wonly_gemv_batched(p, X_bf16):
+    """Small-batch decode GEMV.  X_bf16 [M,K] -> Y [M,OUT] bf16."""
+    _require()
+    dev = X_bf16.device
+    return _OPS.wonly_gemv_batched(X_bf16, _dev(p["scale_exp"], dev), _dev(p["upper_cm"], dev),
+                                   _dev(p["shared_cm"], dev), int(X_bf16.shape[0]),
+                                   int(p["OUT"]), int(p["nb"]), int(p["u"]), int(p["gs"]))
+
+
+def kv_decode_attention(q_bf16, pK, pV):
+    """Fused-dequant flash-decode attention.  q_bf16 [H,D]; pK, pV from pack_kv -> [H,D] bf16."""
+    _require()
+    dev = q_bf16.device
+    ks, ku, kh = (_dev(pK[k], dev) for k in ("scale_exp", "upper", "shared"))
+    vs, vu, vh = (_dev(pV[k], dev) for k in ("scale_exp", "upper", "shared"))
+    return _OPS.kv_decode_attention(q_bf16, ks, ku, kh, vs, vu, vh,
+                                    int(q_bf16.shape[0]), int(pK["H"]), int(pK["L"]), int(pK["D"]),
+                                    int(pK["nb"]), int(pK["u"]), int(pK["gs"]))
+
+
+# --------------------------------------------------------------------------
+# device-resident holders
+# --------------------------------------------------------------------------
+class PackedLinear:
+    """A packed weight kept on the device; `fwd` picks the op by batch size
+    (the dispatch of the reference harness, tests/harness_batchsweep.py:77-111,
+    without its dequant+cuBLAS branch)."""
+
+    def __init__(self, p, device):
+        _require()
+        self.OUT, self.nb, self.u, self.gs = int(p["OUT"]), int(p["nb"]), int(p["u"]), int(p["gs"])
+        self.K = self.nb * 32
+        self.scale_exp = _dev(p["scale_exp"], device).contiguous()
+        self.upper_cm = _dev(p["upper_cm"], device).contiguous()
+        self.shared_cm = _dev(p["shared_cm"], device).contiguous()
+
+    def nbytes(self):
+        return self.scale_exp.numel() + self.upper_cm.numel() + self.shared_cm.numel()
+
+    def fwd(self, x):
+        """x [K] or [M,K] bf16 -> [OUT] or [M,OUT] bf16."""
+        if x.dim() == 1:
+            return _OPS.wonly_gemv_wide(x, self.scale_exp, self.upper_cm, self.shared_cm,
+                                        self.OUT, self.nb, self.u, self.gs)
+        return _OPS.wonly_gemv_batched(x, self.scale_exp, self.upper_cm, self.shared_cm,
+                                       int(x.shape[0]), self.OUT, self.nb, self.u, self.gs)
+
+
+class KVCache:
+    """Packed K and V caches [B,Hkv,nb,Lcap,*] with append and attend.
+
+    Mirrors the KVCache of the reference harness (tests/harness_batchsweep.py:
+    139-199): keys are Hadamard-rotated on append when `rotate` is set and the
+    query is then rotated inside the attention kernel.
+    """
+
+    def __init__(self, B, Hkv, D, Lcap, u, gs, device, rotate=True):
+        _require()
+        self.B, self.Hkv, self.D, self.Lcap, self.u, self.gs = B, Hkv, D, Lcap, u, gs
+        self.nb = D // 32
+        self.UB = 32 * (8 - u) // 8
+        self.SB = ((32 // gs) * u + 7) // 8
+        self.rotate = bool(rotate)
+
+        def planes():
+            return (torch.zeros((B, Hkv, self.nb, Lcap), dtype=torch.int8, device=device),
+                    torch.zeros((B, Hkv, self.nb, Lcap, self.UB), dtype=torch.uint8, device=device),
+                    torch.zeros((B, Hkv, self.nb, Lcap, self.SB), dtype=torch.uint8, device=device))
+
+        self.k, self.v = planes(), planes()
+
+    def nbytes_per_key(self):
+        return 2 * self.Hkv * self.nb * (self.UB + self.SB + 1)
+
+    def fill(self, K, V, key0=0):
+        """Prefill: K, V [B,Hkv,L,D] bf16 written to slots [key0, key0+L)."""
+        B, Hkv, L, D = K.shape
+        for X, pl, rot in ((K, self.k, self.rotate), (V, self.v, False)):
+            _OPS.kv_write_into(X.contiguous(), pl[0], pl[1], pl[2], B * Hkv, L, D, self.nb, key0,
+                               self.Lcap, self.u, self.gs, rot)
+
+    def append(self, k_new, v_new, pos):
+        """k_new, v_new [B,Hkv,D] bf16; pos an int (all sequences) or int32 tensor [B]."""
+        H = self.B * self.Hkv
+        if isinstance(pos, int):
+            kop = _OPS.kv_append_rot if self.rotate else _OPS.kv_append
+            kop(k_new.reshape(H, self.D), *self.k, H, self.D, self.nb, pos, self.Lcap, self.u, self.gs)
+            _OPS.kv_append(v_new.reshape(H, self.D), *self.v, H, self.D, self.nb, pos, self.Lcap, self.u, self.gs)
+        else:
+            _OPS.kv_append_varlen(k_new.reshape(H, self.D), *self.k, pos, self.B, self.Hkv, self.D, self.nb,
+                                  self.Lcap, self.u, self.gs, self.rotate)
+            _OPS.kv_append_varlen(v_new.reshape(H, self.D), *self.v, pos, self.B, self.Hkv, self.D, self.nb,
+                                  self.Lcap, self.u, self.gs, False)
+
+    def attend(self, q, Lk, seq_lens=None):
+        """q [B,Hq,D] bf16 -> [B,Hq,D] bf16 over the first Lk keys (seq_lens[b] if given)."""
+        Hq = int(q.shape[1])
+        if seq_lens is None:
+            seq_lens = torch.full((self.B,), Lk, dtype=torch.int32, device=q.device)
+        return _OPS.kv_decode_attention_varlen(q, *self.k, *self.v, seq_lens, self.B, Hq, self.Hkv, Lk, self.D,
+                                               self.nb, self.u, self.gs, self.Lcap, self.rotate)

@@ -1,0 +1,143 @@
+"""Generate tests/golden/msaq_golden.npz from the reference project's own NumPy code.
+
+Run once, in a container that has the reference checkout:
+
+    python tests/golden/make_golden.py /path/to/reference
+
+It imports the reference's `ms_lib.pack` / `ms_lib.reference` (NumPy only) and
+records their outputs on small seeded inputs.  The fixtures pin the CPU oracle
+under oracle/; nothing at test time needs the reference checkout.
+
+What is recorded
+  dec_*   decompose(): exponent / upper / shared codes for hand-made edge blocks
+          and random blocks, for u in {2,3,4} x gs in {2,4,8,16,32}
+  w_*     pack_weight(): every plane, dequant_weight(), wonly_matmul()
+  kv_*    pack_kv(): planes; kv_attention() causal prefill and single query
+  rot_*   the fp32 butterfly rotation written out as plain loops (the formula of
+          the reference's append/rotate kernels), reference pack_kv() of those
+          values, and the reference's host formulation bf16(K) @ H/sqrt(n)
+"""
+
+import math
+import os
+import sys
+
+import numpy as np
+
+
+def bf16_round(a):
+    a = np.ascontiguousarray(a, np.float32)
+    b = a.view(np.uint32).astype(np.uint64)
+    r = ((b + 0x7FFF + ((b >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+    return r.view(np.float32).reshape(a.shape)
+
+
+def butterfly_rows(x):
+    """Row-wise fp32 butterfly: stages h=1,2,..; lo' = lo + hi, hi' = lo - hi; then * f32(1/sqrt n)."""
+    x = np.array(x, np.float32)
+    rows, n = x.shape
+    out = np.empty_like(x)
+    inv = np.float32(1.0 / math.sqrt(n))
+    for r in range(rows):
+        v = [np.float32(t) for t in x[r]]
+        h = 1
+        while h < n:
+            nv = list(v)
+            for e in range(n):
+                p = e ^ h
+                nv[e] = np.float32(v[p] - v[e]) if (e & h) else np.float32(v[e] + v[p])
+            v = nv
+            h <<= 1
+        out[r] = np.array(v, np.float32) * inv
+    return out
+
+
+def edge_blocks(rng):
+    b = []
+    b.append(np.zeros(32))                                   # all-zero block
+    b.append(np.full(32, 1.0))                               # exact power of two
+    b.append(np.full(32, -1.0))
+    x = np.zeros(32); x[5] = 3e-38; b.append(x)              # below the max-abs floor
+    x = np.zeros(32); x[0] = 2.0 ** 100; b.append(x)         # huge
+    x = np.zeros(32); x[31] = 2.0 ** -100; b.append(x)       # tiny
+    b.append(np.linspace(-1, 1, 32))                         # many rounding ties
+    b.append(np.arange(32) * 0.5)                            # half-integers (ties to even)
+    b.append(np.where(np.arange(32) % 2, 127.0, -127.0))     # saturating both signs
+    b.append(np.where(np.arange(32) % 2, 127.5, -128.0))
+    x = rng.standard_normal(32); x[3] *= 20; b.append(x)     # one outlier
+    b.append(np.full(32, 1.9999999))                         # just below a power of two
+    b.append(np.full(32, 2.0 ** -126))                       # smallest normal f32
+    return np.array(b, np.float64).astype(np.float32)
+
+
+def main():
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    sys.path.insert(0, ref_root)
+    from ms_lib import pack as rp
+    from ms_lib import reference as rr
+
+    rng = np.random.default_rng(20251125)
+    out = {}
+
+    blocks = np.concatenate([
+        edge_blocks(rng),
+        bf16_round((rng.standard_normal((48, 32)) * rng.uniform(0.01, 30, (48, 1))).astype(np.float32)),
+        (rng.standard_normal((32, 32)) * rng.uniform(0.01, 30, (32, 1))).astype(np.float32),
+    ])
+    out["dec_blocks"] = blocks
+    for u in (2, 3, 4):
+        for gs in (2, 4, 8, 16, 32):
+            s, qu, rs = rp.decompose(blocks, u, gs)
+            out[f"dec_exp_u{u}_gs{gs}"] = np.rint(np.log2(s.reshape(-1))).astype(np.int16)
+            out[f"dec_up_u{u}_gs{gs}"] = qu.astype(np.int8)
+            out[f"dec_sh_u{u}_gs{gs}"] = rs.astype(np.int8)
+
+    OUT, K, M = 48, 96, 3
+    W = bf16_round((rng.standard_normal((OUT, K)) * rng.uniform(0.005, 0.08, (OUT, 1))).astype(np.float32))
+    X = bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    out["w_W"], out["w_X"] = W, X
+    for u in (2, 3, 4):
+        for gs in (2, 4, 8):
+            p = rp.pack_weight(W, u, gs)
+            tag = f"u{u}_gs{gs}"
+            for k in ("scale_exp", "upper", "shared", "upper_cm", "shared_cm"):
+                out[f"w_{k}_{tag}"] = p[k]
+            out[f"w_deq_{tag}"] = rp.dequant_weight(p)
+            out[f"w_y_{tag}"] = rr.wonly_matmul(p, X)
+
+    H, L, D = 2, 20, 64
+    Kt = bf16_round((rng.standard_normal((H, L, D)) * 0.5).astype(np.float32))
+    Vt = bf16_round((rng.standard_normal((H, L, D)) * 0.5).astype(np.float32))
+    Qp = bf16_round((rng.standard_normal((H, L, D)) * 0.5).astype(np.float32))
+    out["kv_K"], out["kv_V"], out["kv_Q"] = Kt, Vt, Qp
+    for u in (2, 3, 4):
+        for gs in (2, 4, 8):
+            pK, pV = rp.pack_kv(Kt, u, gs), rp.pack_kv(Vt, u, gs)
+            tag = f"u{u}_gs{gs}"
+            for k in ("scale_exp", "upper", "shared"):
+                out[f"kv_K{k}_{tag}"] = pK[k]
+                out[f"kv_V{k}_{tag}"] = pV[k]
+            out[f"kv_prefill_{tag}"] = rr.kv_attention(Qp, pK, pV, causal=True)
+            out[f"kv_decode_{tag}"] = rr.kv_attention(Qp[:, -1:, :], pK, pV, causal=True)[:, 0]
+
+    Hr, Lr, Dr = 2, 6, 128
+    Kr = bf16_round(rng.standard_normal((Hr, Lr, Dr)).astype(np.float32))
+    Kr[:, :, [3, 40, 77, 120]] *= 20                      # persistent outlier channels
+    Kr = bf16_round(Kr)
+    rot = butterfly_rows(Kr.reshape(-1, Dr)).reshape(Hr, Lr, Dr)
+    out["rot_K"], out["rot_f32"] = Kr, rot
+    from scipy.linalg import hadamard
+    Hn = hadamard(Dr).astype(np.float32) / np.sqrt(np.float32(Dr))
+    out["rot_host"] = (Kr.reshape(-1, Dr) @ Hn).reshape(Hr, Lr, Dr)
+    for u, gs in ((4, 2), (3, 8), (2, 4)):
+        p = rp.pack_kv(rot, u, gs)
+        for k in ("scale_exp", "upper", "shared"):
+            out[f"rot_{k}_u{u}_gs{gs}"] = p[k]
+
+    dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "msaq_golden.npz")
+    np.savez_compressed(dst, **out)
+    print("wrote", dst, os.path.getsize(dst), "bytes,", len(out), "arrays")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,101 @@
+"""GPU parity: weight-only GEMV entry points against the float64 oracle."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import F32_REL_FRO_TOL, MAX_ABS_REL_TOL, REL_FRO_TOL
+from oracle import msaq_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(rng, OUT, K, u, gs, M=1, wscale=(0.005, 0.08)):
+    W = orc.to_bf16((rng.standard_normal((OUT, K)) * rng.uniform(*wscale, (OUT, 1))).astype(np.float32))
+    X = orc.to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    return W, X, orc.pack_weight(W, u, gs)
+
+
+def _check(got, gotf, ref):
+    import cabi
+    cabi.check_output(got, gotf, ref, MAX_ABS_REL_TOL, REL_FRO_TOL, F32_REL_FRO_TOL)
+
+
+@pytest.mark.parametrize("OUT,K", [(128, 256), (200, 96), (1, 32), (4096, 4096 // 8)])
+def test_gemv_wide_and_rowmajor(rng, cfg, OUT, K):
+    import cabi
+    u, gs = cfg
+    W, X, p = _case(rng, OUT, K, u, gs)
+    pd = cabi.planes_to_dev(p)
+    ref = orc.wonly_matmul(p, X)[0]
+    x = cabi.bf16_dev(X[0])
+    for kind in ("wide", "rowmajor"):
+        got, gotf = cabi.gemv(kind, x, pd)
+        _check(got, gotf, ref)
+
+
+@pytest.mark.parametrize("gs", (16, 32))
+@pytest.mark.parametrize("u", (2, 3, 4))
+def test_gemv_large_groups(rng, u, gs):
+    import cabi
+    W, X, p = _case(rng, 256, 512, u, gs)
+    got, gotf = cabi.gemv("wide", cabi.bf16_dev(X[0]), cabi.planes_to_dev(p))
+    _check(got, gotf, orc.wonly_matmul(p, X)[0])
+
+
+@pytest.mark.parametrize("M", (1, 2, 3, 4, 7, 8, 16, 33, 64))
+def test_gemv_batched(rng, cfg, M):
+    import cabi
+    u, gs = cfg
+    W, X, p = _case(rng, 384, 512, u, gs, M=M)
+    got, gotf = cabi.gemv("batched", cabi.bf16_dev(X), cabi.planes_to_dev(p), M=M)
+    _check(got, gotf, orc.wonly_matmul(p, X))
+
+
+@pytest.mark.parametrize("u", (2, 3, 4))
+def test_gemv_llama_shape_vs_oracle(rng, u):
+    """One full Llama-3.1-8B projection (O: 4096x4096) at gs=2, packed on the device."""
+    import cabi
+    OUT, K, gs = 4096, 4096, 2
+    g = torch.Generator(device="cuda").manual_seed(3)
+    W = (torch.randn((OUT, K), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    x = torch.randn((K,), generator=g, device="cuda").to(torch.bfloat16)
+    pd = cabi.pack_weight(W, u, gs)
+    got, gotf = cabi.gemv("wide", x, pd)
+    Wq = orc.quantize_dequantize(W.float().cpu().numpy().reshape(-1, 32), u, gs).reshape(OUT, K)
+    ref = Wq @ x.float().cpu().numpy().astype(np.float64)
+    _check(got, gotf, ref)
+
+
+def test_gemv_linearity_full_size(rng):
+    """Size-independent property at the largest configured shape (28672x4096):
+    y(a+b) == y(a) + y(b) in the fp32 output, to fp32 rounding."""
+    import cabi
+    OUT, K, u, gs = 28672, 4096, 4, 2
+    g = torch.Generator(device="cuda").manual_seed(4)
+    W = (torch.randn((OUT, K), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    pd = cabi.pack_weight(W, u, gs)
+    a = torch.zeros(K, device="cuda"); b = torch.zeros(K, device="cuda")
+    a[::2] = torch.randn(K // 2, generator=g, device="cuda")
+    b[1::2] = torch.randn(K // 2, generator=g, device="cuda")
+    a, b = a.to(torch.bfloat16), b.to(torch.bfloat16)
+    ab = (a.float() + b.float()).to(torch.bfloat16)        # disjoint supports: the sum is exact in bf16
+    _, ya = cabi.gemv("wide", a, pd)
+    _, yb = cabi.gemv("wide", b, pd)
+    _, yab = cabi.gemv("wide", ab, pd)
+    assert orc.rel_fro(ya + yb, yab) < 1e-5
+
+
+def test_gemv_rejects_bad_arguments():
+    import cabi
+    from ms_kernel_b200 import _lib
+    L = _lib.lib()
+    x = torch.zeros(64, dtype=torch.bfloat16, device="cuda")
+    rc = L.msaq_wonly_gemv_wide(x.data_ptr(), None, None, None, None, None, 8, 2, 4, 2, None, 0, None)
+    assert rc == -1 and b"null" in L.msaq_last_error()
+    rc = L.msaq_wonly_gemv_wide(x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), None,
+                                8, 2, 5, 2, None, 0, None)
+    assert rc == -2
+    rc = L.msaq_wonly_gemv_wide(x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), None,
+                                8, 2, 4, 2, None, 0, None)
+    assert rc == -3

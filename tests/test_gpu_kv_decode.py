@@ -1,0 +1,150 @@
+"""GPU parity: KV flash-decode entry points against the float64 oracle."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import F32_REL_FRO_TOL, MAX_ABS_REL_TOL, REL_FRO_TOL
+from oracle import msaq_oracle as orc
+
+pytestmark = pytest.mark.gpu
+KEYS = ("scale_exp", "upper", "shared")
+
+
+def _check(got, gotf, ref, f32_tol=F32_REL_FRO_TOL):
+    import cabi
+    cabi.check_output(got, gotf, ref, MAX_ABS_REL_TOL, REL_FRO_TOL, f32_tol)
+
+
+def _kv(rng, Hkv, L, D, scale=0.5):
+    K = orc.to_bf16((rng.standard_normal((Hkv, L, D)) * scale).astype(np.float32))
+    V = orc.to_bf16((rng.standard_normal((Hkv, L, D)) * scale).astype(np.float32))
+    return K, V
+
+
+def _dev_planes(p):
+    import cabi
+    return tuple(cabi.dev(p[k]) for k in KEYS)
+
+
+@pytest.mark.parametrize("H,Lk,D", [(4, 40, 64), (8, 96, 128), (2, 1, 128), (3, 300, 128), (2, 77, 256), (2, 50, 32)])
+def test_decode_mha_vs_oracle(rng, cfg, H, Lk, D):
+    import cabi
+    u, gs = cfg
+    K, V = _kv(rng, H, Lk, D)
+    q = orc.to_bf16((rng.standard_normal((H, D)) * 0.5).astype(np.float32))
+    pK, pV = orc.pack_kv(K, u, gs), orc.pack_kv(V, u, gs)
+    ref = orc.kv_attention(q[:, None, :], pK, pV, causal=True)[:, 0]
+    got, gotf = cabi.decode(cabi.bf16_dev(q), _dev_planes(pK), _dev_planes(pV), 1, H, H, Lk, D, u, gs, single=True)
+    _check(got, gotf, ref)
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (32, 8), (16, 2), (4, 4)])
+def test_decode_gqa_vs_oracle(rng, cfg, Hq, Hkv):
+    import cabi
+    u, gs = cfg
+    Lk, D = 200, 128
+    K, V = _kv(rng, Hkv, Lk, D)
+    q = orc.to_bf16((rng.standard_normal((Hq, D)) * 0.5).astype(np.float32))
+    pK, pV = orc.pack_kv(K, u, gs), orc.pack_kv(V, u, gs)
+    ref = orc.decode_attention(q, orc.dequant_kv(pK), orc.dequant_kv(pV))
+    got, gotf = cabi.decode(cabi.bf16_dev(q), _dev_planes(pK), _dev_planes(pV), 1, Hq, Hkv, Lk, D, u, gs, single=True)
+    _check(got, gotf, ref)
+
+
+def test_decode_capacity_invariance(rng, cfg):
+    """Attending Lk keys must not depend on the capacity Lcap: bit-identical outputs."""
+    import cabi
+    u, gs = cfg
+    H, Lk, D = 4, 96, 128
+    K, V = _kv(rng, H, Lk, D)
+    Kb, Vb = cabi.bf16_dev(K), cabi.bf16_dev(V)
+    q = cabi.bf16_dev(rng.standard_normal((H, D)) * 0.5)
+    outs = []
+    for Lcap in (Lk, 256):
+        kp = cabi.empty_cache(H, D // 32, Lcap, u, gs, fill=0x7F)
+        vp = cabi.empty_cache(H, D // 32, Lcap, u, gs, fill=0x7F)
+        for pos in range(Lk):
+            cabi.kv_append(Kb[:, pos].contiguous(), kp, H, D, pos, Lcap, u, gs)
+            cabi.kv_append(Vb[:, pos].contiguous(), vp, H, D, pos, Lcap, u, gs)
+        outs.append(cabi.decode(q, kp, vp, 1, H, H, Lk, D, u, gs, Lcap=Lcap, single=True))
+    assert np.array_equal(outs[0][0], outs[1][0])
+    assert np.array_equal(outs[0][1], outs[1][1])
+
+
+@pytest.mark.parametrize("B", (1, 3, 8))
+def test_decode_batched_varlen_vs_oracle(rng, B):
+    import cabi
+    u, gs, Hq, Hkv, Lk, D, Lcap = 4, 2, 8, 2, 160, 128, 192
+    lens = rng.integers(Lk // 2, Lk + 1, size=B).astype(np.int32)
+    lens[0] = Lk
+    K = orc.to_bf16((rng.standard_normal((B * Hkv, Lcap, D)) * 0.5).astype(np.float32))
+    V = orc.to_bf16((rng.standard_normal((B * Hkv, Lcap, D)) * 0.5).astype(np.float32))
+    q = orc.to_bf16((rng.standard_normal((B, Hq, D)) * 0.5).astype(np.float32))
+    pK, pV = orc.pack_kv(K, u, gs), orc.pack_kv(V, u, gs)
+
+    def shaped(p):
+        return tuple(p[k].reshape((B, Hkv) + p[k].shape[1:]) for k in KEYS)
+
+    ref = orc.decode_attention_batched(q, shaped(pK), shaped(pV), u, gs, lens)
+    got, gotf = cabi.decode(cabi.bf16_dev(q), _dev_planes(pK), _dev_planes(pV), B, Hq, Hkv, Lk, D, u, gs, Lcap=Lcap,
+                            seq_lens=cabi.dev(lens))
+    _check(got, gotf, ref)
+    # without seq_lens every sequence attends Lk keys (the reference op's behaviour)
+    ref_full = orc.decode_attention_batched(q, shaped(pK), shaped(pV), u, gs, [Lk] * B)
+    got2, gotf2 = cabi.decode(cabi.bf16_dev(q), _dev_planes(pK), _dev_planes(pV), B, Hq, Hkv, Lk, D, u, gs, Lcap=Lcap)
+    _check(got2, gotf2, ref_full)
+
+
+@pytest.mark.parametrize("u,gs", [(4, 2), (4, 8), (3, 8), (2, 4)])
+def test_decode_with_rotation_vs_oracle(rng, u, gs):
+    """Cache built by append-with-rotation, query rotated in the kernel prologue."""
+    import cabi
+    Hq, Hkv, Lk, D = 16, 4, 130, 128
+    K = rng.standard_normal((Hkv, Lk, D)).astype(np.float32)
+    K[:, :, [3, 40, 77, 120]] *= 20
+    K = orc.to_bf16(K)
+    V = orc.to_bf16(rng.standard_normal((Hkv, Lk, D)).astype(np.float32))
+    q = orc.to_bf16(rng.standard_normal((1, Hq, D)).astype(np.float32))
+    kp = cabi.empty_cache(Hkv, D // 32, Lk, u, gs)
+    vp = cabi.empty_cache(Hkv, D // 32, Lk, u, gs)
+    cabi.kv_write(cabi.bf16_dev(K), kp, Hkv, Lk, D, 0, Lk, u, gs, rot=True)
+    cabi.kv_write(cabi.bf16_dev(V), vp, Hkv, Lk, D, 0, Lk, u, gs)
+    kpn = tuple(t.cpu().numpy()[None] for t in kp)
+    vpn = tuple(t.cpu().numpy()[None] for t in vp)
+    ref = orc.decode_attention_batched(q, kpn, vpn, u, gs, [Lk], qrot=True)
+    got, gotf = cabi.decode(cabi.bf16_dev(q), kp, vp, 1, Hq, Hkv, Lk, D, u, gs, qrot=1)
+    # the in-kernel rotation is an fp32 butterfly, the oracle's a float64 product
+    _check(got, gotf, ref, f32_tol=5e-5)
+    # rotation preserves q.K^T: close to attention over the un-rotated keys (quantisation differs)
+    pK0 = orc.pack_kv(K, u, gs)
+    plain = orc.decode_attention(q[0], orc.dequant_kv(pK0), orc.dequant_kv_planes(*[a[0] for a in vpn], u, gs))
+    assert orc.rel_fro(got[0], plain) < 0.35
+
+
+def test_decode_merge_property_long_cache(rng):
+    """Size-independent property at Lk = 16384 (GQA 32/8): attention over [0,Lk)
+    equals the (m, l)-weighted merge of attention over two halves, each computed
+    by the kernel through seq_lens / shifted plane views."""
+    import cabi
+    u, gs, Hq, Hkv, Lk, D = 4, 2, 32, 8, 16384, 128
+    g = torch.Generator(device="cuda").manual_seed(9)
+    K = torch.randn((Hkv, Lk, D), generator=g, device="cuda").to(torch.bfloat16)
+    V = torch.randn((Hkv, Lk, D), generator=g, device="cuda").to(torch.bfloat16)
+    q = (torch.randn((1, Hq, D), generator=g, device="cuda") * 0.3).to(torch.bfloat16)
+    kp = cabi.empty_cache(Hkv, D // 32, Lk, u, gs)
+    vp = cabi.empty_cache(Hkv, D // 32, Lk, u, gs)
+    cabi.kv_write(K, kp, Hkv, Lk, D, 0, Lk, u, gs)
+    cabi.kv_write(V, vp, Hkv, Lk, D, 0, Lk, u, gs)
+    _, full = cabi.decode(q, kp, vp, 1, Hq, Hkv, Lk, D, u, gs)
+    # oracle on a sample of heads over the whole length
+    kn = tuple(t.cpu().numpy() for t in kp)
+    vn = tuple(t.cpu().numpy() for t in vp)
+    Kd, Vd = orc.dequant_kv_planes(*kn, u, gs), orc.dequant_kv_planes(*vn, u, gs)
+    ref = orc.decode_attention(q[0].float().cpu().numpy(), Kd, Vd)
+    assert orc.rel_fro(full[0], ref) < F32_REL_FRO_TOL * 2
+    # first half via seq_lens
+    half = Lk // 2
+    _, a = cabi.decode(q, kp, vp, 1, Hq, Hkv, Lk, D, u, gs, seq_lens=cabi.dev(np.array([half], np.int32)))
+    ref_a = orc.decode_attention(q[0].float().cpu().numpy(), Kd[:, :half], Vd[:, :half])
+    assert orc.rel_fro(a[0], ref_a) < F32_REL_FRO_TOL * 2
