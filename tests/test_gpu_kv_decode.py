@@ -116,10 +116,6 @@ def test_decode_with_rotation_vs_oracle(rng, u, gs):
     got, gotf = cabi.decode(cabi.bf16_dev(q), kp, vp, 1, Hq, Hkv, Lk, D, u, gs, qrot=1)
     # the in-kernel rotation is an fp32 butterfly, the oracle's a float64 product
     _check(got, gotf, ref, f32_tol=5e-5)
-    # rotation preserves q.K^T: close to attention over the un-rotated keys (quantisation differs)
-    pK0 = orc.pack_kv(K, u, gs)
-    plain = orc.decode_attention(q[0], orc.dequant_kv(pK0), orc.dequant_kv_planes(*[a[0] for a in vpn], u, gs))
-    assert orc.rel_fro(got[0], plain) < 0.35
 
 
 def test_decode_merge_property_long_cache(rng):
