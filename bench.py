@@ -1,0 +1,514 @@
+"""Benchmark of the MSAQ-signed decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch B]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \\
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+One step = one decode step of a Llama-3.1-70B-shaped decoder layer on packed
+u4/gs2 weights, tensor-parallel over N GPUs: QKV GEMV -> K/V append (keys
+Hadamard-rotated) -> GQA flash-decode over Lk cached keys -> O GEMV -> all-reduce
+-> gate/up GEMV -> SiLU*mul -> down GEMV -> all-reduce.  Total work is fixed as N
+grows (strong scaling).  The metric is achieved HBM bandwidth on ALGORITHMIC
+bytes (packed codes + scales + activations of every op of the step, summed over
+ranks) divided by the device-timed step, max over ranks.
+
+Rank 0 prints ONE JSON line.  At N=1 the line also carries `detail`: per-op
+microseconds and GB/s for the single-GPU configurations (Llama-3.1-8B GEMV
+shapes at u in {2,3,4}, M in {1,4,16,64}; MHA and GQA flash-decode), a
+`roofline` object for the dominant kernel and the CPU oracle timed beside it.
+"""
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+NOMINAL_PEAK_GBS = 8000.0
+FALLBACK_PEAK_GBS = 6650.0
+U, GS = 4, 2
+LK = 8192                     # cached keys per sequence of the layer step
+L2_BYTES = 126 << 20
+
+# DRAM bytes (read + write) per launch of the dominant kernel from one ncu capture of
+# `gemv_u4gs2_mma_kernel` on the 28672 x 4096 u4/gs2 M=1 GEMV (summary under profiles/).
+NCU_TRAFFIC = {"kernel": "gemv_u4gs2_mma_kernel", "shape": [28672, 4096], "bytes_per_launch": 91.8e6 + 5.3e6}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--no-detail", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_PEAK_GBS, "fallback"
+
+
+# --------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
+
+    BITS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    def _once(self):
+        nv = self._nv
+        self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+        try:
+            r = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+        except Exception:
+            r = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+        for bit, name in self.BITS.items():
+            if r & bit:
+                self.reasons.add(name)
+
+    def __enter__(self):
+        if self._nv is not None:
+            def loop():
+                while not self._stop.is_set():
+                    try:
+                        self._once()
+                    except Exception:
+                        pass
+                    self._stop.wait(0.002)
+            self._thread = threading.Thread(target=loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# --------------------------------------------------------------------------
+# building blocks
+# --------------------------------------------------------------------------
+def plane_bytes(u, gs):
+    return 32 * (8 - u) // 8 + ((32 // gs) * u + 7) // 8 + 1
+
+
+def gemv_bytes(OUT, K, M, u, gs):
+    return OUT * (K // 32) * plane_bytes(u, gs) + 2 * K * M + 2 * OUT * M
+
+
+def make_linear(OUT, K, u, gs, seed, dev):
+    """Random bf16 ~N(0, 0.02) weight packed on the device -> resident PackedLinear."""
+    import torch
+    from ms_kernel_b200 import ops, pack
+    g = torch.Generator(device=dev).manual_seed(seed)
+    lin = None
+    # pack in row chunks so that the bf16 source never needs more than ~1 GB
+    rows = max(1, min(OUT, (512 << 20) // (2 * K)))
+    parts = []
+    for r0 in range(0, OUT, rows):
+        W = (torch.randn((min(rows, OUT - r0), K), generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        parts.append(pack.pack_weight(W, u, gs, device=dev))
+        del W
+    if len(parts) == 1:
+        p = parts[0]
+    else:
+        from ms_kernel_b200 import tp
+        p = tp.concat_rows(parts)
+    lin = ops.PackedLinear(p, dev)
+    return lin
+
+
+def graph_time(fns, iters, dev):
+    """Capture `fns` (called in order) in one CUDA graph, replay `iters` times, return us per call of fns."""
+    import torch
+    s = torch.cuda.Stream(device=dev)
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for f in fns:
+            f()
+    torch.cuda.current_stream().wait_stream(s)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in fns:
+            f()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(True), torch.cuda.Event(True)
+    best = float("inf")
+    for _ in range(3):
+        a.record()
+        for _ in range(iters):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        best = min(best, a.elapsed_time(b) * 1e3 / iters / len(fns))
+    return best
+
+
+# --------------------------------------------------------------------------
+# the layer step
+# --------------------------------------------------------------------------
+class LayerSet:
+    """One rank's share of one decoder layer (weights + KV cache) and its graph."""
+
+    def __init__(self, shape, world, rank, B, dev, seed, all_reduce):
+        import torch
+        from ms_kernel_b200 import ops, tp
+        self.B = B
+        lin = {}
+        for i, (name, (OUT, K)) in enumerate(shape.weight_shapes_local(world).items()):
+            lin[name] = make_linear(OUT, K, U, GS, seed * 16 + i + 1000 * rank, dev)
+        q, kv, f = shape.local(world)
+        self.Lcap = LK + 8
+        self.cache = ops.KVCache(B, kv, shape.head_dim, self.Lcap, U, GS, dev, rotate=True)
+        g = torch.Generator(device=dev).manual_seed(seed + 77)
+        chunk = 2048
+        for k0 in range(0, LK, chunk):
+            Kt = torch.randn((B, kv, chunk, shape.head_dim), generator=g, device=dev).to(torch.bfloat16)
+            Vt = torch.randn((B, kv, chunk, shape.head_dim), generator=g, device=dev).to(torch.bfloat16)
+            self.cache.fill(Kt, Vt, key0=k0)
+        self.layer = tp.DecoderLayerTP(shape, world, lin, self.cache, all_reduce)
+        self.h_in = torch.zeros((B, shape.hidden), dtype=torch.bfloat16, device=dev)
+        self.h_out = None
+        self.graph = None
+        self.weight_bytes = sum(l.nbytes() for l in lin.values())
+
+    def eager(self):
+        return self.layer.step(self.h_in, LK - 1, LK)
+
+    def capture(self):
+        import torch
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self.eager()
+        torch.cuda.current_stream().wait_stream(s)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.h_out = self.eager()
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from ms_kernel_b200 import ops, tp
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE=%d: launch with torch.distributed.run" % (args.gpus, world))
+    ops._require()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def all_reduce(t):
+        dist.all_reduce(t)
+        return t
+
+    shape = tp.LayerShape.llama31_70b()
+    B = args.batch
+    probe = LayerSet(shape, world, rank, B, dev, 1, all_reduce)
+    per_rank_bytes = probe.layer.algorithmic_bytes(B, B * LK, U, GS)
+    # rotate over enough distinct weight + cache sets that a step never finds its bytes in L2
+    n_sets = max(1, -(-3 * L2_BYTES // max(1, per_rank_bytes)))
+    n_sets = min(n_sets, 8)
+    sets = [probe] + [LayerSet(shape, world, rank, B, dev, 2 + i, all_reduce) for i in range(n_sets - 1)]
+
+    launches0 = torch.ops.msaq.launch_count()
+    sets[0].eager()
+    launches_per_step = int(torch.ops.msaq.launch_count() - launches0)
+    for s in sets:
+        s.capture()
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(3, args.warmup)):
+        sets[i % n_sets].graph.replay()
+    barrier()
+    e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+    with ClockSampler(local) as clocks:
+        e0.record()
+        for i in range(args.steps):
+            sets[i % n_sets].graph.replay()
+        e1.record()
+        barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(ms.item()) / args.steps
+    total_bytes = per_rank_bytes * world
+    value = total_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end: eager public API, host buffers in and out every step -------------------
+    h_host = torch.randn((B, shape.hidden)).to(torch.bfloat16).pin_memory()
+    out_host = torch.empty((B, shape.hidden), dtype=torch.bfloat16).pin_memory()
+    e2e_steps = min(args.steps, 50)
+
+    def e2e_step(i):
+        s = sets[i % n_sets]
+        s.h_in.copy_(h_host, non_blocking=True)
+        out = s.eager()
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    barrier()
+    e2e_ms = torch.tensor([(time.perf_counter() - t0) * 1e3 / e2e_steps], device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_value = total_bytes / (float(e2e_ms.item()) * 1e-3) / 1e9
+
+    peak, peak_kind = measured_peak()
+    line = {
+        "metric": "achieved_hbm_bandwidth_on_algorithmic_bytes", "value": round(value, 1), "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": round(ms_per_step, 5), "us_per_step": round(ms_per_step * 1e3, 2),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "u4 codes + int8 MMA, fp32 accumulate, bf16 in/out", "data": "synthetic",
+        "config": {
+            "workload": "llama-3.1-70b-shaped decoder layer, one decode step, u4/gs2 packed weights and KV cache, "
+                        "hidden 8192, Hq 64, Hkv 8, D 128, FFN 28672, Lk %d, B %d" % (LK, B),
+            "parallelism": "tp%d (rows of QKV/gate/up, K blocks of O/down, kv heads; 2 all-reduces per layer)" % world,
+            "l2": "rotating over %d distinct weight+cache sets (%.0f MB per GPU per set)" % (n_sets, per_rank_bytes / 1e6),
+            "timing": "CUDA-graph replay per step, CUDA events on the launching stream, max over ranks",
+            "algorithmic_bytes_per_step": int(total_bytes),
+        },
+        "frac_of_nominal_8TBs_per_gpu": round(value / world / NOMINAL_PEAK_GBS, 4),
+        "frac_of_%s_peak_per_gpu" % peak_kind: round(value / world / peak, 4),
+        "clocks": clocks.summary(),
+        "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "us_per_step": round(float(e2e_ms.item()) * 1e3, 1),
+                "h2d_bytes_per_step": int(h_host.numel() * 2), "d2h_bytes_per_step": int(out_host.numel() * 2),
+                "api": "ms_kernel_b200.tp.DecoderLayerTP.step over ops.PackedLinear / ops.KVCache, eager, pinned host buffers"},
+        "gpu_launches": launches_per_step * args.steps,
+        "gpu_launches_per_step": launches_per_step,
+    }
+    if world == 1 and rank == 0 and not args.no_detail:
+        del sets, probe
+        torch.cuda.empty_cache()
+        line.update(single_gpu_detail(dev, peak, peak_kind))
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------
+# single-GPU detail: per-op numbers, roofline of the dominant kernel, CPU oracle
+# --------------------------------------------------------------------------
+def single_gpu_detail(dev, peak, peak_kind):
+    import numpy as np
+    import torch
+    from ms_kernel_b200 import ops
+
+    out = {"detail": {"gemv": [], "kv_decode": []}}
+    shapes = [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)]
+    roof = None
+    for u in (4, 3, 2):
+        for name, OUT, K in shapes:
+            nbytes = OUT * (K // 32) * plane_bytes(u, GS)
+            copies = max(2, -(-3 * L2_BYTES // nbytes))
+            lins = [make_linear(OUT, K, u, GS, 31 * c + u, dev) for c in range(copies)]
+            for M in (1, 4, 16, 64):
+                x = torch.randn((M, K) if M > 1 else (K,), device=dev).to(torch.bfloat16)
+                usec = graph_time([(lambda l=l: l.fwd(x)) for l in lins], 10, dev)
+                b = gemv_bytes(OUT, K, M, u, GS)
+                gbs = b / usec / 1e3
+                out["detail"]["gemv"].append({"u": u, "gs": GS, "shape": name, "OUT": OUT, "K": K, "M": M,
+                                              "us": round(usec, 2), "GBps": round(gbs, 1),
+                                              "frac_8TBs": round(gbs / NOMINAL_PEAK_GBS, 3)})
+                if u == 4 and name == "gate_up" and M == 1:
+                    roof = {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
+                            "frac": round(gbs / peak, 4), "peak_source": peak_kind + " copy bandwidth (burst)",
+                            "traffic": NCU_TRAFFIC["bytes_per_launch"], "algorithmic_bytes": b,
+                            "kernel": "gemv_xprep_kernel + gemv_u4gs2_mma_kernel (one op, 28672x4096 u4/gs2 M=1)",
+                            "us_per_launch": round(usec, 2)}
+            del lins
+            torch.cuda.empty_cache()
+    out["roofline"] = roof
+
+    def kv_case(tag, B, Hq, Hkv, Lk, varlen):
+        D = 128
+        rng = np.random.default_rng(5)
+        lens = rng.integers(Lk // 2, Lk + 1, size=B).astype(np.int32) if varlen else np.full(B, Lk, np.int32)
+        per_key = 2 * Hkv * (D // 32) * plane_bytes(U, GS)
+        nbytes = int(lens.sum()) * per_key
+        copies = int(max(1, min(6, -(-3 * L2_BYTES // max(nbytes, 1)))))
+        caches = []
+        g = torch.Generator(device=dev).manual_seed(9)
+        for _ in range(copies):
+            c = ops.KVCache(B, Hkv, D, Lk + 8, U, GS, dev, rotate=True)
+            for k0 in range(0, Lk, 4096):
+                n = min(4096, Lk - k0)
+                Kt = torch.randn((B, Hkv, n, D), generator=g, device=dev).to(torch.bfloat16)
+                Kt[..., [3, 40, 77, 120]] *= 20
+                c.fill(Kt, torch.randn((B, Hkv, n, D), generator=g, device=dev).to(torch.bfloat16), key0=k0)
+            caches.append(c)
+        q = torch.randn((B, Hq, D), generator=g, device=dev).to(torch.bfloat16)
+        kn = torch.randn((B, Hkv, D), generator=g, device=dev).to(torch.bfloat16)
+        sl = torch.from_numpy(lens).to(dev)
+        pos = (sl - 1).to(torch.int32)
+
+        def step(c):
+            c.append(kn, kn, pos)          # one new token per sequence, then attend
+            return c.attend(q, Lk, sl)
+
+        usec = graph_time([(lambda c=c: step(c)) for c in caches], 10, dev)
+        b = nbytes + 4 * B * Hq * D
+        out["detail"]["kv_decode"].append({"case": tag, "B": B, "Hq": Hq, "Hkv": Hkv, "Lk": Lk, "varlen": varlen,
+                                           "us": round(usec, 2), "GBps": round(b / usec / 1e3, 1),
+                                           "frac_8TBs": round(b / usec / 1e3 / NOMINAL_PEAK_GBS, 3),
+                                           "includes": "K/V append of one token + flash-decode"})
+        del caches
+        torch.cuda.empty_cache()
+
+    for Hq, Lk in ((8, 4096), (8, 16384), (16, 16384)):
+        kv_case("mha", 1, Hq, Hq, Lk, False)
+    for Lk, B in ((4096, 1), (16384, 1), (16384, 8), (32768, 16)):
+        kv_case("gqa32/8", B, 32, 8, Lk, True)
+    out["cpu_baseline"] = cpu_oracle_sample()
+    return out
+
+
+def cpu_oracle_sample():
+    """The NumPy oracle on this box's host cores: W-only GEMV 4096x4096 u4/gs2 M=1 (BASELINE config 0)."""
+    import numpy as np
+    import torch
+    from ms_kernel_b200 import pack
+    from oracle import msaq_oracle as orc
+
+    OUT = K = 4096
+    rng = np.random.default_rng(0)
+    W = torch.from_numpy((rng.standard_normal((OUT, K)) * 0.02).astype(np.float32)).to(torch.bfloat16)
+    p = pack.to_numpy(pack.pack_weight(W.cuda(), U, GS)) if torch.cuda.is_available() else orc.pack_weight(
+        W.float().numpy(), U, GS)
+    x = orc.to_bf16(rng.standard_normal((1, K)).astype(np.float32))
+    orc.wonly_matmul(p, x)
+    times = []
+    t_end = time.perf_counter() + 15.0
+    while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 8):
+        t0 = time.perf_counter()
+        orc.wonly_matmul(p, x)
+        times.append(time.perf_counter() - t0)
+    best = min(times)
+    Wdq = orc.dequant_weight(p)
+    t0 = time.perf_counter()
+    for _ in range(5):
+        orc.wonly_matmul_predequant(Wdq, x)
+    hoisted = (time.perf_counter() - t0) / 5
+    b = gemv_bytes(OUT, K, 1, U, GS)
+    return {"value": round(b / best / 1e9, 5), "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": "oracle.wonly_matmul (dequantises the packed weight on every call, as the reference's NumPy "
+                      "oracle does) on W-only GEMV 4096x4096 u4/gs2 M=1, best of %d calls" % len(times),
+            "seconds_per_op": round(best, 4), "seconds_per_op_dequant_hoisted": round(hoisted, 5),
+            "numpy": np.__version__}
+
+
+# --------------------------------------------------------------------------
+# reference arm: the CPU oracle on the host cores, same metric and config
+# --------------------------------------------------------------------------
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    from ms_kernel_b200 import tp
+    from oracle import msaq_oracle as orc
+
+    shape = tp.LayerShape.llama31_70b()
+    B = args.batch
+    # bounded sample of the step: a 1/32 slice of every GEMV's output rows and one kv head's decode over Lk/8 keys
+    rng = np.random.default_rng(0)
+    frac_rows, frac_keys = 32, 8
+    mats = {name: (max(32, OUT // frac_rows), K) for name, (OUT, K) in shape.weight_shapes_local(1).items()}
+    packs = {n: orc.pack_weight(orc.to_bf16((rng.standard_normal(s) * 0.02).astype(np.float32)), U, GS)
+             for n, s in mats.items()}
+    xs = {n: orc.to_bf16(rng.standard_normal((B, s[1])).astype(np.float32)) for n, s in mats.items()}
+    Lk = LK // frac_keys
+    Kc = orc.pack_kv(orc.to_bf16(rng.standard_normal((1, Lk, shape.head_dim)).astype(np.float32)), U, GS)
+    Vc = orc.pack_kv(orc.to_bf16(rng.standard_normal((1, Lk, shape.head_dim)).astype(np.float32)), U, GS)
+    qh = orc.to_bf16(rng.standard_normal((shape.n_q // shape.n_kv, shape.head_dim)).astype(np.float32))
+    sample_bytes = sum(gemv_bytes(s[0], s[1], B, U, GS) for s in mats.values()) \
+        + B * (Lk * 2 * 4 * plane_bytes(U, GS) + 4 * qh.size)
+
+    def step():
+        for n in mats:
+            orc.wonly_matmul(packs[n], xs[n])
+        kp = (Kc["scale_exp"], Kc["upper"], Kc["shared"])
+        vp = (Vc["scale_exp"], Vc["upper"], Vc["shared"])
+        for _ in range(B):
+            orc.decode_attention_planes(qh, kp, vp, U, GS, Lk)
+
+    for _ in range(max(1, min(args.warmup, 2))):
+        step()
+    steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    sec = (time.perf_counter() - t0) / steps
+    value = sample_bytes / sec / 1e9
+    sample = ("NumPy oracle port on the host cores: 1/%d of the output rows of each of the four layer GEMVs and one "
+              "kv head's decode over Lk/%d keys per sequence; %d timed passes" % (frac_rows, frac_keys, steps))
+    line = {
+        "impl": "reference", "metric": "achieved_hbm_bandwidth_on_algorithmic_bytes", "value": round(value, 5),
+        "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": max(1, min(args.warmup, 2)),
+        "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "float64 (NumPy)", "data": "synthetic",
+        "config": {"workload": "llama-3.1-70b-shaped decoder layer, one decode step, u4/gs2, Lk %d, B %d "
+                               "(bounded sample, see cpu_baseline.sample)" % (LK, B)},
+        "cpu_baseline": {"value": round(value, 5), "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(value, 5), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

@@ -1,47 +1,114 @@
 // Host side of the weight-only GEMV entry points: argument checks, the split-K
 // plan, kernel selection.  Replaces the launchers at csrc/w_gemv.cu:1410-1570
 // of the reference.
-#include "gemv_generic.cuh"
+#include "gemv_mma.cuh"
 
 namespace msaq {
 namespace {
 
-struct GemvPlan {
-    int mr;          // activation rows per CTA pass
-    int mtiles;      // ceil(M / mr)
-    int colblocks;   // ceil(OUT / GEMV_COLS)
-    int splits;      // K ranges
-    int blocks_per_split;
+// generic path, defined in gemv_generic.cu
+}  // namespace
+size_t gemv_generic_workspace(int64_t M, int64_t OUT, int64_t NB);
+int gemv_run_generic(const __nv_bfloat16* X, const int8_t* se, const uint8_t* up, const uint8_t* sh, void* Y,
+                     float* Yf, int64_t M, int64_t OUT, int64_t NB, const Fmt& f, bool cm, void* ws,
+                     cudaStream_t st);
+namespace {
+
+// ---- tuned path (u4/gs2, column-major planes, OUT % 16 == 0) --------------------
+struct MmaPlan {
+    GemvSchedule sch;
+    size_t xprep_bytes, ctl_off, partial_off, total;
 };
 
-GemvPlan plan_generic(int64_t M, int64_t OUT, int64_t NB) {
-    GemvPlan p;
-    p.mr = M >= 8 ? 8 : (M >= 4 ? 4 : (M >= 2 ? 2 : 1));
-    p.mtiles = (int)((M + p.mr - 1) / p.mr);
-    p.colblocks = (int)((OUT + GEMV_COLS - 1) / GEMV_COLS);
-    const int64_t ctas = (int64_t)p.colblocks * p.mtiles;
-    int64_t want = (4LL * sm_count() + ctas - 1) / ctas;          // ~4 CTAs per SM in flight
-    if (want > NB) want = NB;
-    if (want > 32) want = 32;
-    if (want < 1) want = 1;
-    p.blocks_per_split = (int)((NB + want - 1) / want);
-    p.splits = (int)((NB + p.blocks_per_split - 1) / p.blocks_per_split);
+bool mma_eligible(int64_t OUT, int u, int gs, bool cm) { return cm && u == 4 && gs == 2 && OUT % 16 == 0; }
+
+MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB) {
+    MmaPlan p;
+    GemvSchedule& s = p.sch;
+    const int64_t rows = M < GM_MP * GM_MAX_PASSES ? M : GM_MP * GM_MAX_PASSES;
+    const int passes = (int)((rows + GM_MP - 1) / GM_MP);
+    s.nb = (int)NB;
+    const long long slots = (long long)GM_CTAS_PER_SM * sm_count();
+    // Widest tile (fewest, largest TMA copies) that keeps the number of CTAs sharing one tile --
+    // and with it the partial sums the finishing warp has to add up -- at or below 32.
+    for (int tc = GM_MAX_TC; tc >= GM_GROUP; tc >>= 1) {
+        s.tc = tc;
+        s.col_tiles = (int)((OUT + tc - 1) / tc);
+        const long long units = s.units();
+        s.grid = (int)(units < slots ? units : slots);
+        if (tc == GM_GROUP || (s.grid + s.col_tiles - 1) / s.col_tiles <= 32) break;
+    }
+    const long long units = s.units();
+    s.max_slots = (int)(((long long)s.nb * s.grid + units - 1) / units) + 1;
+    const int per_sm = (s.grid + sm_count() - 1) / sm_count();
+    const int stage = gm_stage_bytes(s.tc, passes);
+    int stages = (200 * 1024 / per_sm) / stage;
+    if (stages > GM_MAX_STAGES) stages = GM_MAX_STAGES;
+    if (stages < 2) stages = 2;
+    s.stages = stages;
+    p.xprep_bytes = ((size_t)NB * passes * GM_XREC + 255) & ~(size_t)255;
+    p.ctl_off = p.xprep_bytes;                                        // status word, then the tile counters
+    p.partial_off = p.ctl_off + ((256 + (size_t)s.col_tiles * GM_WARPS * sizeof(int) + 255) & ~(size_t)255);
+    p.total = p.partial_off + (((size_t)s.max_slots * rows * OUT * sizeof(float) + 255) & ~(size_t)255);
     return p;
 }
 
-template <int U, bool CM>
-void launch_generic(const GemvPlan& p, const __nv_bfloat16* X, const int8_t* se, const uint8_t* up,
-                    const uint8_t* sh, float* partial, int M, int OUT, int NB, const Fmt& f, cudaStream_t st) {
-    dim3 grid(p.colblocks, p.splits, p.mtiles);
-#define MSAQ_GO(MR) gemv_generic_kernel<U, CM, MR><<<grid, GEMV_COLS, 0, st>>>( \
-        X, se, up, sh, partial, M, OUT, NB, f.lg_gs, f.UB, f.SB, p.blocks_per_split)
-    switch (p.mr) {
-        case 1: MSAQ_GO(1); break;
-        case 2: MSAQ_GO(2); break;
-        case 4: MSAQ_GO(4); break;
-        default: MSAQ_GO(8); break;
+template <int PASSES, int TC>
+int launch_mma(const GemvMmaArgs& a, cudaStream_t st) {
+    static int configured[64] = {};                      // largest dynamic smem size set per device
+    const int smem = a.sch.stages * gm_stage_bytes(TC, PASSES);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && configured[dev] < smem) {
+        if (cudaFuncSetAttribute(gemv_u4gs2_mma_kernel<PASSES, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 smem) != cudaSuccess)
+            return fail(MSAQ_ERR_CUDA, "cannot reserve %d bytes of shared memory", smem);
+        configured[dev] = smem;
     }
-#undef MSAQ_GO
+    gemv_u4gs2_mma_kernel<PASSES, TC><<<a.sch.grid, GM_THREADS, smem, st>>>(a);
+    count_launch();
+    return check_launch("gemv_u4gs2_mma");
+}
+
+template <int PASSES>
+int launch_mma_tc(const GemvMmaArgs& a, cudaStream_t st) {
+    switch (a.sch.tc) {
+        case 128: return launch_mma<PASSES, 128>(a, st);
+        case 256: return launch_mma<PASSES, 256>(a, st);
+        default: return launch_mma<PASSES, 512>(a, st);
+    }
+}
+
+int run_mma(const __nv_bfloat16* X, const int8_t* se, const uint8_t* up, const uint8_t* sh, void* Y, float* Yf,
+            int64_t M, int64_t OUT, int64_t NB, void* ws, cudaStream_t st) {
+    const MmaPlan p = plan_mma(M, OUT, NB);
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    int* status = reinterpret_cast<int*>(base + p.ctl_off);
+    int* counters = status + 64;
+    float* partial = reinterpret_cast<float*>(base + p.partial_off);
+    const int64_t tile_rows = GM_MP * GM_MAX_PASSES;
+    for (int64_t m0 = 0; m0 < M; m0 += tile_rows) {        // more than 16 rows: one launch per 16-row tile
+        const int rows = (int)(M - m0 < tile_rows ? M - m0 : tile_rows);
+        const int passes = (rows + GM_MP - 1) / GM_MP;
+        const int warps = (int)NB * passes * GM_MP;
+        gemv_xprep_kernel<<<(warps * 32 + 127) / 128, 128, 0, st>>>(X + m0 * NB * BLOCK, base, status, counters,
+                                                                     p.sch.col_tiles * GM_WARPS, m0 == 0 ? 1 : 0, rows, (int)NB,
+                                                                     passes);
+        count_launch();
+        if (int rc = check_launch("gemv_xprep")) return rc;
+        GemvMmaArgs a{se, up, sh, base, partial, counters, status, static_cast<__nv_bfloat16*>(Y), Yf,
+                      (int)m0, rows, (int)OUT, p.sch};
+        // the ring depth was planned for the first tile's pass count; a last, smaller tile may go deeper but need not
+        int rc;
+        switch (passes) {
+            case 1: rc = launch_mma_tc<1>(a, st); break;
+            case 2: rc = launch_mma_tc<2>(a, st); break;
+            case 3: rc = launch_mma_tc<3>(a, st); break;
+            default: rc = launch_mma_tc<4>(a, st); break;
+        }
+        if (rc) return rc;
+    }
+    return MSAQ_OK;
 }
 
 int gemv_dispatch(const void* X, const int8_t* se, const uint8_t* up, const uint8_t* sh, void* Y, float* Yf,
@@ -59,25 +126,13 @@ int gemv_dispatch(const void* X, const int8_t* se, const uint8_t* up, const uint
         return fail(MSAQ_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", need, ws ? ws_bytes : (size_t)0);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
-    float* partial = static_cast<float*>(ws);
 
-    const GemvPlan p = plan_generic(M, OUT, NB);
-    if (cm) {
-        if (u == 4) launch_generic<4, true>(p, x, se, up, sh, partial, (int)M, (int)OUT, (int)NB, f, st);
-        else if (u == 3) launch_generic<3, true>(p, x, se, up, sh, partial, (int)M, (int)OUT, (int)NB, f, st);
-        else launch_generic<2, true>(p, x, se, up, sh, partial, (int)M, (int)OUT, (int)NB, f, st);
-    } else {
-        if (u == 4) launch_generic<4, false>(p, x, se, up, sh, partial, (int)M, (int)OUT, (int)NB, f, st);
-        else if (u == 3) launch_generic<3, false>(p, x, se, up, sh, partial, (int)M, (int)OUT, (int)NB, f, st);
-        else launch_generic<2, false>(p, x, se, up, sh, partial, (int)M, (int)OUT, (int)NB, f, st);
-    }
-    count_launch();
-    if (int rc = check_launch("gemv_generic")) return rc;
-    const int64_t n = M * OUT;
-    splitk_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(partial, static_cast<__nv_bfloat16*>(Y), Yf, n,
-                                                                       p.splits);
-    count_launch();
-    return check_launch("splitk_combine");
+    if (mma_eligible(OUT, u, gs, cm) &&
+        !((reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(sh) | reinterpret_cast<uintptr_t>(se) |
+           reinterpret_cast<uintptr_t>(ws)) & 15))
+        return run_mma(x, se, up, sh, Y, Yf, M, OUT, NB, ws, st);
+
+    return gemv_run_generic(x, se, up, sh, Y, Yf, M, OUT, NB, f, cm, ws, st);
 }
 
 }  // namespace
@@ -86,11 +141,13 @@ int gemv_dispatch(const void* X, const int8_t* se, const uint8_t* up, const uint
 using namespace msaq;
 
 extern "C" size_t msaq_wonly_gemv_workspace(int64_t M, int64_t OUT, int64_t NB, int u, int gs) {
-    (void)u; (void)gs;
     if (M <= 0 || OUT <= 0 || NB <= 0) return 0;
-    const GemvPlan p = plan_generic(M, OUT, NB);
-    size_t bytes = (size_t)p.splits * (size_t)M * (size_t)OUT * sizeof(float);
-    return (bytes + 255) & ~(size_t)255;
+    size_t bytes = gemv_generic_workspace(M, OUT, NB);
+    if (mma_eligible(OUT, u, gs, true)) {
+        const size_t tuned = plan_mma(M, OUT, NB).total;
+        if (tuned > bytes) bytes = tuned;
+    }
+    return bytes;
 }
 
 extern "C" int msaq_wonly_gemv(const void* x, const int8_t* scale_exp, const uint8_t* upper, const uint8_t* shared,

@@ -1,0 +1,392 @@
+// Tuned weight-only GEMV for u = 4, gs = 2 on column-major planes.
+//
+// Data flow per CTA (a tile of 128 output columns x a range of K blocks):
+//   * one producer thread streams the packed bytes of its tile (upper codes,
+//     shared codes, scale bytes) and the pre-split activations into a ring of
+//     shared-memory stages with TMA bulk copies (cp.async.bulk + mbarrier);
+//   * eight consumer warps each own 16 columns.  A thread turns the nibbles of
+//     a 32-bit word into int8 tensor-core operands with three logic ops -- a
+//     two's-complement nibble in the high half of a byte IS the int8 value
+//     16*up, and the offset-binary shared nibble ORs into the low half -- so
+//     one m16n8k32 integer MMA yields the exact integer dot of a 32-block
+//     against up to four activation rows;
+//   * the integer dot is scaled by 2^(weight exponent) * 2^(activation block
+//     exponent) and accumulated in fp32; split-K partials go to the workspace.
+//
+// Activations are staged once per call by gemv_xprep_kernel as 16-bit block
+// fixed point (two int8 planes per row): x = xi * 2^(E-14) with E the exponent
+// of the block's max-abs, |xi| <= 32640.  Every bf16 element within a factor
+// 2^7 of its block maximum is represented exactly; smaller ones are rounded
+// with absolute error <= 2^(E-15).  The one unrepresentable code (+32640) is
+// stored as 32639.
+//
+// Algorithm replaced: csrc/w_gemv.cu:173-284 (wide u4 kernel) and :417-487
+// (batched kernel) of the reference.
+#pragma once
+
+#include "msaq_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace msaq {
+
+constexpr int GM_WARPS = 8;          // consumer warps; each owns 16 columns of every 128-column group
+constexpr int GM_THREADS = (GM_WARPS + 1) * 32;
+constexpr int GM_GROUP = 128;        // columns per group (8 warps x 16)
+constexpr int GM_MAX_TC = 512;       // columns per tile (1, 2 or 4 groups)
+constexpr int GM_MAX_STAGES = 12;
+constexpr int GM_MP = 4;             // activation rows per MMA pass
+constexpr int GM_MAX_PASSES = 4;     // -> at most 16 rows per launch
+constexpr int GM_XREC = 320;         // bytes of staged activations per (block, pass)
+constexpr int GM_CTAS_PER_SM = 3;
+
+// Stage layout for a tile of TC columns x one K block:
+//   upper [TC][16] | shared [TC][8] | scale [TC] | activations [passes][GM_XREC]
+__host__ __device__ inline int gm_stage_bytes(int tc, int passes) { return tc * 25 + passes * GM_XREC; }
+
+// Work decomposition shared by host and device.  A unit is (column tile c,
+// K block b); unit index n = c * NB + b.  CTA i of `grid` owns the units
+// [i*U/grid, (i+1)*U/grid): contiguous, equal to within one unit, so a grid of
+// (SMs x resident CTAs) finishes in one balanced wave.  A tile is covered by
+// consecutive CTAs; each leaves one partial sum in slot (cta - first cta of the
+// tile), and the CTA that completes a tile adds the slots up in slot order.
+struct GemvSchedule {
+    int tc;            // columns per tile: 128, 256 or 512
+    int col_tiles, nb, grid, max_slots;
+    int stages;        // depth of the shared-memory ring (<= GM_MAX_STAGES)
+    __host__ __device__ long long units() const { return (long long)col_tiles * nb; }
+    __host__ __device__ long long lo(int cta) const { return units() * cta / grid; }
+    __host__ __device__ int first_cta(int c) const { return (int)((((long long)c * nb + 1) * grid - 1) / units()); }
+    __host__ __device__ int last_cta(int c) const { return (int)((((long long)(c + 1) * nb) * grid - 1) / units()); }
+};
+
+// ---- activation staging -------------------------------------------------------
+// Record of one (block, pass): xq[8 cols][4 t][8 bytes] | tc[4 t]{corr, cx, 0, 0}.
+// Column 2*mm is the high byte plane of row 4*pass+mm, column 2*mm+1 the low one.
+// Thread-slot t = 2h + odd of a column holds, for i = 0..3, the elements
+// 16h + 4i + 2*odd (bytes 0..3) and 16h + 4i + 2*odd + 1 (bytes 4..7): the
+// elements whose shared codes are the even (odd = 0) or odd nibbles of shared
+// word h, in the byte order the consumer builds its MMA operand in.
+__global__ void __launch_bounds__(128)
+gemv_xprep_kernel(const __nv_bfloat16* __restrict__ X, uint8_t* __restrict__ xprep, int* __restrict__ status,
+                  int* __restrict__ tile_counters, int n_counters, int reset_status, int M, int NB, int passes) {
+    const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
+    const int warp = gtid >> 5, lane = threadIdx.x & 31;
+    if (reset_status && gtid == 0) *status = 0;
+    for (int i = gtid; i < n_counters; i += gridDim.x * blockDim.x) tile_counters[i] = 0;
+    if (warp >= NB * passes * GM_MP) return;
+    const int mm = warp % GM_MP, pass = (warp / GM_MP) % passes, blk = warp / (GM_MP * passes);
+    const int m = pass * GM_MP + mm;
+    const float x = (m < M) ? __bfloat162float(X[(int64_t)m * NB * BLOCK + blk * BLOCK + lane]) : 0.0f;
+    uint32_t ax = __float_as_uint(x) & 0x7FFFFFFFu;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) ax = max(ax, __shfl_xor_sync(0xffffffffu, ax, o));
+    int E = (int)(ax >> 23) - 127;
+    E = ax == 0u ? 0 : max(-100, min(127, E));
+    int xi = __float2int_rn(x * __int_as_float((14 - E + 127) << 23));
+    xi = min(xi, 32639);
+    const int lo = (int)(int8_t)(xi & 0xFF), hi = (xi - lo) >> 8;
+    uint8_t* rec = xprep + ((int64_t)blk * passes + pass) * GM_XREC;
+    const int e = lane, t = 2 * (e >> 4) + ((e >> 1) & 1), j = (e & 1) * 4 + ((e & 15) >> 2);
+    rec[(2 * mm) * 32 + t * 8 + j] = (uint8_t)hi;
+    rec[(2 * mm + 1) * 32 + t * 8 + j] = (uint8_t)lo;
+    int sh = hi, sl = lo;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        sh += __shfl_xor_sync(0xffffffffu, sh, o);
+        sl += __shfl_xor_sync(0xffffffffu, sl, o);
+    }
+    if (lane == 0) {
+        int* tc = reinterpret_cast<int*>(rec + 256 + mm * 16);
+        tc[0] = -8 * (sh * 256 + sl);                         // correction for the offset-binary shared codes
+        tc[1] = (int)((uint32_t)(E - 14 + 127) << 23);        // 2^(E-14) as float bits
+        tc[2] = 0;
+        tc[3] = 0;
+    }
+}
+
+// ---- main kernel ------------------------------------------------------------------
+struct GemvMmaArgs {
+    const int8_t* scale_exp;
+    const uint8_t* upper_cm;
+    const uint8_t* shared_cm;
+    const uint8_t* xprep;
+    float* partial;          // [max_slots][rows][OUT]
+    int* tile_counters;      // [col_tiles], zeroed by the staging kernel
+    int* status;             // set to 1 when a bounded wait gave up
+    __nv_bfloat16* y;        // [M][OUT]
+    float* y_f32;            // optional
+    int m0, rows;            // this launch covers rows [m0, m0 + rows), rows <= 16
+    int OUT;
+    GemvSchedule sch;
+};
+
+// Shared-memory loads with a register base and a compile-time byte offset, so
+// that one address register per plane serves a whole stage.
+template <int OFF>
+__device__ __forceinline__ uint2 lds64(uint32_t base) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(base), "n"(OFF));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32(uint32_t base) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(base), "n"(OFF));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ int lds_s8(uint32_t base) {
+    int v;
+    asm volatile("ld.shared.s8 %0, [%1+%2];" : "=r"(v) : "r"(base), "n"(OFF));
+    return v;
+}
+
+// Explicit single-instruction logic ops: the compiler otherwise splits these
+// three-input expressions.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t c) {      // (a & mask) | c
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(c));
+    return r;
+}
+__device__ __forceinline__ uint32_t and_xor(uint32_t a, uint32_t mask, uint32_t c) {     // (a & mask) ^ c
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(a), "r"(mask), "r"(c));
+    return r;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+
+// One 16-column x 32-element step of a warp: decode both columns' codes into the
+// int8 operand, one integer MMA per activation pass, scale and accumulate.
+template <int PASSES, int Q>
+__device__ __forceinline__ void gemv_group_step(uint32_t wbase, uint32_t sbase, uint32_t ebase, uint32_t sel,
+                                                uint32_t nshift, const uint2 (&bq)[PASSES], const int (&corr)[PASSES],
+                                                const float (&cx)[PASSES], float (&acc)[PASSES][2]) {
+    const uint2 w0 = lds64<Q * 2048>(wbase);
+    const uint2 w1 = lds64<Q * 2048 + 128>(wbase);
+    const uint32_t s0 = lds32<Q * 1024>(sbase);
+    const uint32_t s1 = lds32<Q * 1024 + 64>(sbase);
+    const int e0 = lds_s8<Q * 128>(ebase);
+    const int e1 = lds_s8<Q * 128 + 8>(ebase);
+    // shared codes (even or odd nibbles of word h) as offset-binary low nibbles
+    const uint32_t m0 = and_xor(s0 >> nshift, 0x0F0F0F0Fu, 0x08080808u);
+    const uint32_t m1 = and_xor(s1 >> nshift, 0x0F0F0F0Fu, 0x08080808u);
+    // bytes of the upper words that hold the two elements of each of those groups
+    const uint32_t x0 = prmt(w0.x, w0.y, sel), x1 = prmt(w1.x, w1.y, sel);
+    uint32_t A[4];
+    A[0] = and_or(x0 << 4, 0xF0F0F0F0u, m0);     // column r0, first element of each group
+    A[1] = and_or(x1 << 4, 0xF0F0F0F0u, m1);     // column r0 + 8
+    A[2] = and_or(x0, 0xF0F0F0F0u, m0);          // column r0, second element of each group
+    A[3] = and_or(x1, 0xF0F0F0F0u, m1);
+    const float sw0 = __int_as_float(e0 * (1 << 23) + (127 << 23));
+    const float sw1 = __int_as_float(e1 * (1 << 23) + (127 << 23));
+#pragma unroll
+    for (int p = 0; p < PASSES; ++p) {
+        const uint32_t B[2] = {bq[p].x, bq[p].y};
+        int Dm[4];
+        mma_s8_16832_z(Dm, A, B);
+        // (hi plane) * 256 + (lo plane) - 8 * sum(x): the offset-binary shared codes add 8 per element
+        const float f0 = (float)(Dm[0] * 256 + Dm[1] + corr[p]) * cx[p];
+        const float f1 = (float)(Dm[2] * 256 + Dm[3] + corr[p]) * cx[p];
+        acc[p][0] = fmaf(f0, sw0, acc[p][0]);
+        acc[p][1] = fmaf(f1, sw1, acc[p][1]);
+    }
+}
+
+template <int PASSES, int TC>
+__global__ void __launch_bounds__(GM_THREADS, GM_CTAS_PER_SM)
+gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) uint64_t bar_full[GM_MAX_STAGES];
+    __shared__ __align__(8) uint64_t bar_empty[GM_MAX_STAGES];
+
+    constexpr int GROUPS = TC / GM_GROUP;
+    constexpr int OFF_SH = TC * 16, OFF_SC = TC * 24, OFF_X = TC * 25;
+    constexpr int STAGE_BYTES = TC * 25 + PASSES * GM_XREC;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const GemvSchedule sch = a.sch;
+    float* const yf = a.y_f32;
+    const long long n_lo = sch.lo(blockIdx.x), n_hi = sch.lo(blockIdx.x + 1);
+    const int n_iter = (int)(n_hi - n_lo);
+    int c = (int)(n_lo / sch.nb), blk = (int)(n_lo % sch.nb);
+
+    if (tid == 0) {
+        for (int s = 0; s < sch.stages; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), GM_WARPS);
+        }
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    if (warp == GM_WARPS) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 1;                       // parity of the "previous" empty phase: passes at once on a fresh barrier
+            for (int it = 0; it < n_iter; ++it) {
+                if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ph)) {
+                    atomicExch(a.status, 1);
+                    break;
+                }
+                const int o0 = c * TC, cv = min(TC, a.OUT - o0);
+                const uint32_t bar = smem_u32(&bar_full[s]);
+                const uint32_t base = smem_u32(smem) + s * STAGE_BYTES;
+                const int64_t col = (int64_t)blk * a.OUT + o0;
+                mbar_expect_tx(bar, (uint32_t)(cv * 25 + PASSES * GM_XREC));
+                bulk_g2s(base, a.upper_cm + col * 16, (uint32_t)cv * 16, bar);
+                bulk_g2s(base + OFF_SH, a.shared_cm + col * 8, (uint32_t)cv * 8, bar);
+                bulk_g2s(base + OFF_SC, a.scale_exp + col, (uint32_t)cv, bar);
+                bulk_g2s(base + OFF_X, a.xprep + (int64_t)blk * PASSES * GM_XREC, (uint32_t)(PASSES * GM_XREC), bar);
+                if (++blk == sch.nb) { blk = 0; ++c; }
+                if (++s == sch.stages) { s = 0; ph ^= 1u; }
+            }
+        }
+        return;
+    }
+
+    // -------------------------------- consumers --------------------------------
+    const int g = lane >> 2, t = lane & 3, h = t >> 1, odd = t & 1;
+    const int r0 = warp * 16 + g;                            // group-local columns r0 and r0 + 8
+    const uint32_t sel = odd ? 0x7531u : 0x6420u;            // bytes {odd, 2+odd} of both upper words
+    const uint32_t nshift = odd * 4;
+    const uint32_t sb = smem_u32(smem);
+    const uint32_t aW = sb + r0 * 16 + h * 8;                // upper words 2h, 2h+1 of column r0
+    const uint32_t aS = sb + OFF_SH + r0 * 8 + h * 4;        // shared word h
+    const uint32_t aE = sb + OFF_SC + r0;
+    const uint32_t aB = sb + OFF_X + g * 32 + t * 8;
+    const uint32_t aC = sb + OFF_X + 256 + t * 16;
+    float acc[GROUPS][PASSES][2];
+#pragma unroll
+    for (int q = 0; q < GROUPS; ++q)
+#pragma unroll
+        for (int p = 0; p < PASSES; ++p) acc[q][p][0] = acc[q][p][1] = 0.0f;
+    // A wait that gives up marks the warp aborted: it stops waiting and computing,
+    // still releases its stages, and publishes nothing (the status word is set).
+    bool aborted = false;
+
+    int s = 0;
+    uint32_t ph = 0;
+    for (int it = 0; it < n_iter; ++it) {
+        if (!aborted && !mbar_wait_bounded(smem_u32(&bar_full[s]), ph)) {
+            atomicExch(a.status, 1);
+            aborted = true;
+        }
+        const uint32_t so = s * STAGE_BYTES;
+        const int cv = min(TC, a.OUT - c * TC);
+        if (!aborted) {
+            uint2 bq[PASSES];
+            int corr[PASSES];
+            float cx[PASSES];
+#pragma unroll
+            for (int p = 0; p < PASSES; ++p) {
+                const uint32_t rb = aB + so + p * GM_XREC;
+                bq[p] = lds64<0>(rb);
+                corr[p] = (int)lds32<0>(aC + so + p * GM_XREC);
+                cx[p] = __uint_as_float(lds32<4>(aC + so + p * GM_XREC));
+            }
+            const uint32_t wb = aW + so, sbs = aS + so, eb = aE + so;
+            const int nq = (cv - warp * 16 + GM_GROUP - 1) / GM_GROUP;      // column groups this warp has in the tile
+            if (nq >= GROUPS) {
+                gemv_group_step<PASSES, 0>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[0]);
+                if (GROUPS > 1) gemv_group_step<PASSES, (GROUPS > 1 ? 1 : 0)>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[GROUPS > 1 ? 1 : 0]);
+                if (GROUPS > 2) gemv_group_step<PASSES, (GROUPS > 2 ? 2 : 0)>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[GROUPS > 2 ? 2 : 0]);
+                if (GROUPS > 3) gemv_group_step<PASSES, (GROUPS > 3 ? 3 : 0)>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[GROUPS > 3 ? 3 : 0]);
+            } else {
+                if (nq > 0) gemv_group_step<PASSES, 0>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[0]);
+                if (GROUPS > 1 && nq > 1) gemv_group_step<PASSES, (GROUPS > 1 ? 1 : 0)>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[GROUPS > 1 ? 1 : 0]);
+                if (GROUPS > 2 && nq > 2) gemv_group_step<PASSES, (GROUPS > 2 ? 2 : 0)>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[GROUPS > 2 ? 2 : 0]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_empty[s]));
+        if (++s == sch.stages) { s = 0; ph ^= 1u; }
+
+        // ---- end of this CTA's run over tile c: publish the partial, maybe finish the tile ----
+        // Each warp owns 16 columns of every 128-column group of the tile, so the hand-off is
+        // per warp: store the partial, bump the (tile, warp) counter with release semantics, and
+        // the warp that arrives last adds the slots up in slot order and writes the output.
+        const bool tile_end = (blk == sch.nb - 1);
+        if (tile_end || it == n_iter - 1) {
+            const int first = sch.first_cta(c), nslots = sch.last_cta(c) - first + 1;
+            const int slot = blockIdx.x - first, o0 = c * TC;
+            const int nq = (cv - warp * 16 + GM_GROUP - 1) / GM_GROUP;     // groups in which this warp has columns
+            if (nq > 0 && !aborted) {
+                if (nslots == 1) {
+#pragma unroll
+                    for (int q = 0; q < GROUPS; ++q) {
+                        if (q < nq) {
+#pragma unroll
+                            for (int p = 0; p < PASSES; ++p) {
+                                const int m = p * GM_MP + t;
+                                if (m < a.rows) {
+                                    const int64_t o = (int64_t)(a.m0 + m) * a.OUT + o0 + q * GM_GROUP + r0;
+                                    a.y[o] = __float2bfloat16_rn(acc[q][p][0]);
+                                    a.y[o + 8] = __float2bfloat16_rn(acc[q][p][1]);
+                                    if (yf) { yf[o] = acc[q][p][0]; yf[o + 8] = acc[q][p][1]; }
+                                }
+                            }
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int q = 0; q < GROUPS; ++q) {
+                        if (q < nq) {
+#pragma unroll
+                            for (int p = 0; p < PASSES; ++p) {
+                                const int m = p * GM_MP + t;
+                                if (m < a.rows) {
+                                    float* dst = a.partial + ((int64_t)slot * a.rows + m) * a.OUT + o0 + q * GM_GROUP + r0;
+                                    dst[0] = acc[q][p][0];
+                                    dst[8] = acc[q][p][1];
+                                }
+                            }
+                        }
+                    }
+                    {
+                    __syncwarp();
+                    int old = 0;
+                    if (lane == 0)
+                        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;"
+                                     : "=r"(old) : "l"(a.tile_counters + c * GM_WARPS + warp) : "memory");
+                    old = __shfl_sync(0xffffffffu, old, 0);
+                    if (old == nslots - 1) {
+                        __threadfence();
+                        const bool poison = __ldcg(a.status) != 0;        // a wait gave up somewhere
+                        const int ncol = nq * 16;
+                        for (int idx = lane; idx < a.rows * ncol; idx += 32) {
+                            const int m = idx / ncol, j = idx % ncol;
+                            const int col = (j >> 4) * GM_GROUP + warp * 16 + (j & 15);
+                            const float* src = a.partial + (int64_t)m * a.OUT + o0 + col;
+                            const int64_t sstride = (int64_t)a.rows * a.OUT;
+                            float sum = 0.0f;
+                            for (int k0 = 0; k0 < nslots; k0 += 8) {      // eight loads in flight, summed in slot order
+                                float v[8];
+#pragma unroll
+                                for (int k = 0; k < 8; ++k) v[k] = (k0 + k < nslots) ? __ldcg(src + (k0 + k) * sstride) : 0.0f;
+#pragma unroll
+                                for (int k = 0; k < 8; ++k) sum += v[k];
+                            }
+                            if (poison) sum = __int_as_float(0x7FC00000);
+                            const int64_t o = (int64_t)(a.m0 + m) * a.OUT + o0 + col;
+                            a.y[o] = __float2bfloat16_rn(sum);
+                            if (yf) yf[o] = sum;
+                        }
+                    }
+                    }
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < GROUPS; ++q)
+#pragma unroll
+                for (int p = 0; p < PASSES; ++p) acc[q][p][0] = acc[q][p][1] = 0.0f;
+        }
+        if (++blk == sch.nb) { blk = 0; ++c; }
+    }
+}
+
+}  // namespace msaq

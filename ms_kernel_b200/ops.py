@@ -143,14 +143,16 @@ class KVCache:
     def append(self, k_new, v_new, pos):
         """k_new, v_new [B,Hkv,D] bf16; pos an int (all sequences) or int32 tensor [B]."""
         H = self.B * self.Hkv
+        k_new = k_new.reshape(H, self.D).contiguous()
+        v_new = v_new.reshape(H, self.D).contiguous()
         if isinstance(pos, int):
             kop = _OPS.kv_append_rot if self.rotate else _OPS.kv_append
-            kop(k_new.reshape(H, self.D), *self.k, H, self.D, self.nb, pos, self.Lcap, self.u, self.gs)
-            _OPS.kv_append(v_new.reshape(H, self.D), *self.v, H, self.D, self.nb, pos, self.Lcap, self.u, self.gs)
+            kop(k_new, *self.k, H, self.D, self.nb, pos, self.Lcap, self.u, self.gs)
+            _OPS.kv_append(v_new, *self.v, H, self.D, self.nb, pos, self.Lcap, self.u, self.gs)
         else:
-            _OPS.kv_append_varlen(k_new.reshape(H, self.D), *self.k, pos, self.B, self.Hkv, self.D, self.nb,
+            _OPS.kv_append_varlen(k_new, *self.k, pos, self.B, self.Hkv, self.D, self.nb,
                                   self.Lcap, self.u, self.gs, self.rotate)
-            _OPS.kv_append_varlen(v_new.reshape(H, self.D), *self.v, pos, self.B, self.Hkv, self.D, self.nb,
+            _OPS.kv_append_varlen(v_new, *self.v, pos, self.B, self.Hkv, self.D, self.nb,
                                   self.Lcap, self.u, self.gs, False)
 
     def attend(self, q, Lk, seq_lens=None):

@@ -1,0 +1,188 @@
+"""Tensor-parallel decode step of one Llama-shaped decoder layer on packed weights.
+
+The reference has no multi-GPU code; its single-GPU wiring of a decode layer is
+tests/harness_batchsweep.py:230-243 (rmsnorm -> q/k/v -> append -> attend -> o ->
+residual -> rmsnorm -> gate/up -> SiLU*mul -> down -> residual).  This module
+shards that step the way packed tensors shard for free: every 32-block of a
+weight row and every (kv head, key) record is packed independently
+(ms_lib/pack.py:112-121, :493-496), so a slice of the planes along output rows,
+along K blocks, or along kv heads is itself a valid packed tensor.
+
+  QKV, gate, up : split by output rows (rank r owns its q/kv heads and the matching
+                  rows of gate and of up)            -> no exchange
+  O, down       : split by K blocks (rank r owns the K range its local heads / FFN
+                  rows produce)                      -> all-reduce of [B, hidden]
+  KV cache      : split by kv head                   -> no exchange
+
+One process per GPU; the two all-reduces per layer go through torch.distributed
+(NCCL on GPUs, gloo in the CPU tests).
+"""
+
+import math
+
+import numpy as np
+
+BLOCK = 32
+
+
+# --------------------------------------------------------------------------
+# shard arithmetic (pure, no device needed)
+# --------------------------------------------------------------------------
+def split_range(total, parts, idx):
+    """[lo, hi) of part `idx` when `total` items are cut into `parts` equal parts."""
+    if total % parts:
+        raise ValueError("%d does not divide into %d equal parts" % (total, parts))
+    step = total // parts
+    return idx * step, (idx + 1) * step
+
+
+def shard_rows(p, lo, hi):
+    """Rows [lo, hi) of a packed weight: a pack dict of the slice (views where possible)."""
+    out = dict(p)
+    out["scale_exp"] = p["scale_exp"][:, lo:hi]
+    out["upper"] = p["upper"][:, :, lo:hi]
+    out["shared"] = p["shared"][:, :, lo:hi]
+    out["upper_cm"] = p["upper_cm"][:, lo:hi, :]
+    out["shared_cm"] = p["shared_cm"][:, lo:hi, :]
+    out["OUT"] = hi - lo
+    return out
+
+
+def shard_kblocks(p, b_lo, b_hi):
+    """K blocks [b_lo, b_hi) of a packed weight (input features b_lo*32 .. b_hi*32)."""
+    out = dict(p)
+    for k in ("scale_exp", "upper", "shared", "upper_cm", "shared_cm"):
+        out[k] = p[k][b_lo:b_hi]
+    out["nb"] = b_hi - b_lo
+    out["K"] = (b_hi - b_lo) * BLOCK
+    return out
+
+
+def concat_rows(parts):
+    """Stack row shards of one weight back into a single pack dict (used for [q;k;v] and [gate;up])."""
+    cat = np.concatenate if isinstance(parts[0]["scale_exp"], np.ndarray) else None
+    if cat is None:
+        import torch
+        cat = torch.cat
+        kw = lambda a: dict(dim=a)
+    else:
+        kw = lambda a: dict(axis=a)
+    out = dict(parts[0])
+    out["scale_exp"] = cat([q["scale_exp"] for q in parts], **kw(1))
+    out["upper"] = cat([q["upper"] for q in parts], **kw(2))
+    out["shared"] = cat([q["shared"] for q in parts], **kw(2))
+    out["upper_cm"] = cat([q["upper_cm"] for q in parts], **kw(1))
+    out["shared_cm"] = cat([q["shared_cm"] for q in parts], **kw(1))
+    out["OUT"] = sum(int(q["OUT"]) for q in parts)
+    return out
+
+
+class LayerShape:
+    """Sizes of one decoder layer."""
+
+    def __init__(self, hidden, n_q, n_kv, head_dim, ffn):
+        self.hidden, self.n_q, self.n_kv, self.head_dim, self.ffn = hidden, n_q, n_kv, head_dim, ffn
+
+    @staticmethod
+    def llama31_70b():
+        return LayerShape(8192, 64, 8, 128, 28672)
+
+    @staticmethod
+    def llama31_8b():
+        return LayerShape(4096, 32, 8, 128, 14336)
+
+    def local(self, world):
+        """(q heads, kv heads, ffn rows) owned by one rank."""
+        if self.n_kv % world or self.n_q % world or self.ffn % world:
+            raise ValueError("layer does not divide over %d ranks" % world)
+        return self.n_q // world, self.n_kv // world, self.ffn // world
+
+    def weight_shapes_local(self, world):
+        """{name: (OUT, K)} of the four packed matrices one rank holds."""
+        q, kv, f = self.local(world)
+        d = self.head_dim
+        return {
+            "qkv": ((q + 2 * kv) * d, self.hidden),
+            "o": (self.hidden, q * d),
+            "gate_up": (2 * f, self.hidden),
+            "down": (self.hidden, f),
+        }
+
+
+def shard_layer(packs, shape, world, rank):
+    """Cut full packed weights {'q','k','v','o','gate','up','down'} into the four local
+    matrices of `rank`: qkv = [q_r; k_r; v_r], o = K-slice, gate_up = [gate_r; up_r], down = K-slice."""
+    q, kv, f = shape.local(world)
+    d = shape.head_dim
+    qr = shard_rows(packs["q"], rank * q * d, (rank + 1) * q * d)
+    kr = shard_rows(packs["k"], rank * kv * d, (rank + 1) * kv * d)
+    vr = shard_rows(packs["v"], rank * kv * d, (rank + 1) * kv * d)
+    gr = shard_rows(packs["gate"], rank * f, (rank + 1) * f)
+    ur = shard_rows(packs["up"], rank * f, (rank + 1) * f)
+    return {
+        "qkv": concat_rows([qr, kr, vr]),
+        "o": shard_kblocks(packs["o"], rank * q * d // BLOCK, (rank + 1) * q * d // BLOCK),
+        "gate_up": concat_rows([gr, ur]),
+        "down": shard_kblocks(packs["down"], rank * f // BLOCK, (rank + 1) * f // BLOCK),
+    }
+
+
+# --------------------------------------------------------------------------
+# the step
+# --------------------------------------------------------------------------
+class DecoderLayerTP:
+    """One rank's share of a decoder layer decode step.
+
+    linears : {'qkv','o','gate_up','down'} objects with .fwd(x[B,K]) -> [B,OUT]
+    cache   : object with .append(k[B,kv,D], v[B,kv,D], pos) and .attend(q[B,q,D], Lk, seq_lens)
+    all_reduce : callable(tensor) summing in place over the ranks (identity when world == 1)
+    """
+
+    def __init__(self, shape, world, linears, cache, all_reduce=None, eps=1e-5):
+        self.shape, self.world = shape, world
+        self.q_heads, self.kv_heads, self.ffn_rows = shape.local(world)
+        self.lin, self.cache, self.eps = linears, cache, eps
+        self.all_reduce = all_reduce if all_reduce is not None else (lambda t: t)
+
+    @staticmethod
+    def _rmsnorm(x, eps):
+        import torch
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+
+    def step(self, h, pos, Lk, seq_lens=None):
+        """h [B, hidden] bf16 (replicated on every rank) -> new h [B, hidden] bf16 (replicated).
+
+        pos: slot the new token's K/V go to (int, or int32 tensor [B]); Lk: keys attended
+        after the append (seq_lens[b] per sequence if given)."""
+        import torch
+        B = h.shape[0]
+        d = self.shape.head_dim
+        x = self._rmsnorm(h, self.eps)
+        qkv = self.lin["qkv"].fwd(x)                                   # [B, (q + 2kv) * d], rows local
+        q = qkv[:, : self.q_heads * d].reshape(B, self.q_heads, d)
+        k = qkv[:, self.q_heads * d:(self.q_heads + self.kv_heads) * d].reshape(B, self.kv_heads, d)
+        v = qkv[:, (self.q_heads + self.kv_heads) * d:].reshape(B, self.kv_heads, d)
+        self.cache.append(k, v, pos)
+        a = self.cache.attend(q.contiguous(), Lk, seq_lens)            # [B, q, d], heads local
+        o = self.lin["o"].fwd(a.reshape(B, self.q_heads * d))          # partial over the local K range
+        o = self.all_reduce(o.float()) if self.world > 1 else o
+        h = (h.float() + o.float()).to(h.dtype)
+        x = self._rmsnorm(h, self.eps)
+        gu = self.lin["gate_up"].fwd(x)                                # [B, 2 * ffn_rows]
+        act = (torch.nn.functional.silu(gu[:, : self.ffn_rows].float()) * gu[:, self.ffn_rows:].float()).to(h.dtype)
+        dn = self.lin["down"].fwd(act)
+        dn = self.all_reduce(dn.float()) if self.world > 1 else dn
+        return (h.float() + dn.float()).to(h.dtype)
+
+    # ---- bookkeeping for the benchmark --------------------------------------
+    def algorithmic_bytes(self, B, seq_lens_sum, u, gs):
+        """Packed weight + cache + activation bytes one step of this rank must move."""
+        ub, sb = BLOCK * (8 - u) // 8, ((BLOCK // gs) * u + 7) // 8
+        per_block = ub + sb + 1
+        total = 0
+        for OUT, K in self.shape.weight_shapes_local(self.world).values():
+            total += OUT * (K // BLOCK) * per_block + 2 * K * B + 2 * OUT * B
+        nb = self.shape.head_dim // BLOCK
+        total += self.kv_heads * seq_lens_sum * 2 * nb * per_block + 4 * B * self.q_heads * self.shape.head_dim
+        return total

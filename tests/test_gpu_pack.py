@@ -19,7 +19,8 @@ def test_pack_weight_bytes(rng, golden, u, gs):
     import cabi
     OUT, K = 96, 256
     W = (rng.standard_normal((OUT, K)) * rng.uniform(0.005, 0.08, (OUT, 1))).astype(np.float32)
-    W[:OUT, :32] = golden["dec_blocks"][:OUT]                 # edge blocks: zeros, ties, saturation, tiny, huge
+    edge = golden["dec_blocks"][:OUT]                          # edge blocks: zeros, ties, saturation, tiny, huge
+    W[:len(edge), :32] = edge
     for as_bf16 in (True, False):
         Wd = cabi.bf16_dev(W) if as_bf16 else cabi.dev(W)
         ref = orc.pack_weight(Wd.float().cpu().numpy(), u, gs)
