@@ -120,45 +120,6 @@ struct GemvMmaArgs {
     GemvSchedule sch;
 };
 
-// Shared-memory loads with a register base and a compile-time byte offset, so
-// that one address register per plane serves a whole stage.
-template <int OFF>
-__device__ __forceinline__ uint2 lds64(uint32_t base) {
-    uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(base), "n"(OFF));
-    return v;
-}
-template <int OFF>
-__device__ __forceinline__ uint32_t lds32(uint32_t base) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(base), "n"(OFF));
-    return v;
-}
-template <int OFF>
-__device__ __forceinline__ int lds_s8(uint32_t base) {
-    int v;
-    asm volatile("ld.shared.s8 %0, [%1+%2];" : "=r"(v) : "r"(base), "n"(OFF));
-    return v;
-}
-
-// Explicit single-instruction logic ops: the compiler otherwise splits these
-// three-input expressions.
-__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t c) {      // (a & mask) | c
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(c));
-    return r;
-}
-__device__ __forceinline__ uint32_t and_xor(uint32_t a, uint32_t mask, uint32_t c) {     // (a & mask) ^ c
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(a), "r"(mask), "r"(c));
-    return r;
-}
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t r;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
-    return r;
-}
-
 // One 16-column x 32-element step of a warp: decode both columns' codes into the
 // int8 operand, one integer MMA per activation pass, scale and accumulate.
 template <int PASSES, int Q>

@@ -2,6 +2,7 @@
 // plan, kernel selection.  Replaces the launchers at
 // csrc/kv_attention.cu:1875-2122 of the reference.
 #include "kv_decode_generic.cuh"
+#include "kv_decode_mma.cuh"
 
 namespace msaq {
 namespace {
@@ -23,6 +24,72 @@ KvPlan plan_generic(int64_t B, int64_t H, int64_t Lk) {
     p.key_tile = (int)tile;
     p.S = (int)((Lk + tile - 1) / tile);
     return p;
+}
+
+// ---- tuned path: u4/gs2, D = 128, G in {1,2,4,8}, capacity a multiple of 16 ----------------
+bool mma_eligible(int64_t H, int64_t Hkv, int64_t D, int u, int gs, int64_t Lcap) {
+    const int64_t G = H / Hkv;
+    return u == 4 && gs == 2 && D == 128 && (G == 1 || G == 2 || G == 4 || G == 8) && Lcap % 16 == 0;
+}
+
+struct KvMmaPlan {
+    int S, key_tile;
+    size_t status_off, total;
+};
+
+KvMmaPlan plan_mma(int64_t B, int64_t H, int64_t Hkv, int64_t Lk) {
+    KvMmaPlan p;
+    const int64_t pairs = B * Hkv;
+    int64_t want = (4LL * sm_count() + pairs - 1) / pairs;             // about two waves of two CTAs per SM
+    const int64_t max_tiles = (Lk + KVM_TK - 1) / KVM_TK;
+    if (want > max_tiles) want = max_tiles;
+    if (want < 1) want = 1;
+    int64_t tile = (Lk + want - 1) / want;
+    tile = (tile + KVM_TK - 1) / KVM_TK * KVM_TK;
+    p.key_tile = (int)tile;
+    p.S = (int)((Lk + tile - 1) / tile);
+    const size_t part = (((size_t)B * H * p.S * 130 * sizeof(float)) + 255) & ~(size_t)255;
+    p.status_off = part;
+    p.total = part + 256;
+    return p;
+}
+
+template <int G>
+int launch_kv_mma(const KvMmaArgs& a, int S, int Hkv, int B, cudaStream_t st) {
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(kv_decode_u4gs2_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, KVM_SMEM) !=
+            cudaSuccess)
+            return fail(MSAQ_ERR_CUDA, "cannot reserve %d bytes of shared memory", KVM_SMEM);
+        configured[dev] = true;
+    }
+    kv_decode_u4gs2_kernel<G><<<dim3((unsigned)S, (unsigned)Hkv, (unsigned)B), KVM_THREADS, KVM_SMEM, st>>>(a);
+    count_launch();
+    return check_launch("kv_decode_u4gs2");
+}
+
+int run_mma(const __nv_bfloat16* q, KvPlanes kp, KvPlanes vp, void* out, float* out_f32, const int32_t* seq_lens,
+            int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t Lcap, int qrot, void* ws, cudaStream_t st) {
+    const KvMmaPlan p = plan_mma(B, H, Hkv, Lk);
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    int* status = reinterpret_cast<int*>(base + p.status_off);
+    if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return fail(MSAQ_ERR_CUDA, "memset failed");
+    KvMmaArgs a{q, kp, vp, reinterpret_cast<float*>(base), seq_lens, status, (int)H, (int)Hkv, (int)Lk, (int)Lcap,
+                p.key_tile, p.S, qrot, (float)(1.4426950408889634 / sqrt(128.0))};
+    int rc;
+    switch (H / Hkv) {
+        case 1: rc = launch_kv_mma<1>(a, p.S, (int)Hkv, (int)B, st); break;
+        case 2: rc = launch_kv_mma<2>(a, p.S, (int)Hkv, (int)B, st); break;
+        case 4: rc = launch_kv_mma<4>(a, p.S, (int)Hkv, (int)B, st); break;
+        default: rc = launch_kv_mma<8>(a, p.S, (int)Hkv, (int)B, st); break;
+    }
+    if (rc) return rc;
+    kv_decode_combine2_kernel<<<dim3((unsigned)H, (unsigned)B), 128, 0, st>>>(
+        reinterpret_cast<const float*>(base), static_cast<__nv_bfloat16*>(out), out_f32, (int)H, p.S);
+    count_launch();
+    return check_launch("kv_decode_combine2");
 }
 
 int decode_dispatch(const void* q, KvPlanes kp, KvPlanes vp, void* out, float* out_f32, const int32_t* seq_lens,
@@ -48,6 +115,11 @@ int decode_dispatch(const void* q, KvPlanes kp, KvPlanes vp, void* out, float* o
         return fail(MSAQ_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", need, ws ? ws_bytes : (size_t)0);
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (mma_eligible(H, Hkv, D, u, gs, Lcap) &&
+        !((reinterpret_cast<uintptr_t>(kp.s) | reinterpret_cast<uintptr_t>(kp.u) | reinterpret_cast<uintptr_t>(kp.h) |
+           reinterpret_cast<uintptr_t>(vp.s) | reinterpret_cast<uintptr_t>(vp.u) | reinterpret_cast<uintptr_t>(vp.h)) & 15))
+        return run_mma(static_cast<const __nv_bfloat16*>(q), kp, vp, out, out_f32, seq_lens, B, H, Hkv, Lk, Lcap, qrot,
+                       ws, st);
     const KvPlan p = plan_generic(B, H, Lk);
     const float sm_scale = (float)(1.0 / sqrt((double)D));
     float* partial = static_cast<float*>(ws);
@@ -73,11 +145,15 @@ int decode_dispatch(const void* q, KvPlanes kp, KvPlanes vp, void* out, float* o
 using namespace msaq;
 
 extern "C" size_t msaq_kv_decode_workspace(int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D) {
-    (void)Hkv;
     if (B <= 0 || H <= 0 || Lk <= 0 || D <= 0) return 0;
     const KvPlan p = plan_generic(B, H, Lk);
-    const size_t bytes = (size_t)B * H * p.S * kv_partial_stride((int)D) * sizeof(float);
-    return (bytes + 255) & ~(size_t)255;
+    size_t bytes = (size_t)B * H * p.S * kv_partial_stride((int)D) * sizeof(float);
+    bytes = (bytes + 255) & ~(size_t)255;
+    if (D == 128 && Hkv > 0 && H % Hkv == 0) {
+        const size_t tuned = plan_mma(B, H, Hkv, Lk).total;
+        if (tuned > bytes) bytes = tuned;
+    }
+    return bytes;
 }
 
 extern "C" int msaq_kv_decode_attention(const void* q, const int8_t* ks, const uint8_t* ku, const uint8_t* kh,

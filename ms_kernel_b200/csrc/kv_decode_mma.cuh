@@ -1,0 +1,425 @@
+// Tuned split-KV flash-decode for u = 4, gs = 2, head_dim 128, G = Hq/Hkv in {1,2,4,8}.
+//
+// One CTA = (key tile, kv head, sequence) and serves all G query heads of that kv
+// head, so every packed code is fetched and decoded once.
+//   * A producer thread streams 128-key stages of the K and V planes (upper codes,
+//     shared codes, scale bytes) into a shared-memory ring with TMA bulk copies.
+//   * Four consumer warps take 32 keys of each stage.  Q.K^T is the GEMV data flow:
+//     nibbles become int8 MMA operands with three logic ops per word, the query is
+//     staged once per CTA as 16-bit block fixed point, one m16n8k32 integer MMA
+//     gives the exact integer dot of 16 keys x one 32-block against four heads.
+//   * Online softmax per warp in the exp2 domain; probabilities go through shared
+//     memory once to change from the (key, head) to the (head, key) register layout.
+//   * P.V contracts over keys: ldmatrix.m16n16.trans.b8 delivers V bytes with four
+//     keys per register (one d-pair per byte), the probabilities -- pre-multiplied by
+//     each key's block scale relative to the chunk maximum -- are 16-bit fixed-point
+//     A operands, and the integer result is rescaled once per 32 keys and block.
+//   * Each warp keeps its own (m, l, acc); the warps of a CTA merge through shared
+//     memory, the tiles of a head through the combine kernel.
+//
+// Algorithm replaced: csrc/kv_attention.cu:450-829 (kv_decode_wide_kernel) of the
+// reference, including its fused query rotation (:485-498).
+#pragma once
+
+#include "kv_decode_generic.cuh"
+#include "sm100_ptx.cuh"
+
+namespace msaq {
+
+constexpr int KVM_WARPS = 4;
+constexpr int KVM_THREADS = (KVM_WARPS + 1) * 32;
+constexpr int KVM_TK = 128;                 // keys per stage
+constexpr int KVM_CHUNK = 32;               // keys per warp per stage
+constexpr int KVM_STAGES = 3;
+constexpr int KVM_UP = KVM_TK * 16, KVM_SH = KVM_TK * 8, KVM_SC = KVM_TK;
+constexpr int KVM_K_UP = 0, KVM_K_SH = 4 * KVM_UP, KVM_K_SC = KVM_K_SH + 4 * KVM_SH;
+constexpr int KVM_V_UP = KVM_K_SC + 4 * KVM_SC, KVM_V_SH = KVM_V_UP + 4 * KVM_UP, KVM_V_SC = KVM_V_SH + 4 * KVM_SH;
+constexpr int KVM_STAGE_BYTES = KVM_V_SC + 4 * KVM_SC;            // 25600
+constexpr int KVM_QREC = 320;               // staged query record per (block, pass); layout as in gemv_mma.cuh
+constexpr int KVM_PSTRIDE = 40;             // floats per head row of the probability exchange buffer
+constexpr int KVM_OFF_Q = KVM_STAGES * KVM_STAGE_BYTES;
+constexpr int KVM_OFF_P = KVM_OFF_Q + 4 * 2 * KVM_QREC;
+constexpr int KVM_OFF_R = KVM_OFF_P + KVM_WARPS * 8 * KVM_PSTRIDE * 4;      // per-warp 2^-shift table [4][32] floats
+constexpr int KVM_SMEM = KVM_OFF_R + KVM_WARPS * 4 * 32 * 4;
+
+struct KvMmaArgs {
+    const __nv_bfloat16* q;     // [B][Hq][128]
+    KvPlanes k, v;
+    float* partial;             // [B][Hq][S][130]
+    const int32_t* seq_lens;    // optional
+    int* status;
+    int Hq, Hkv, Lk, Lcap, key_tile, S, qrot;
+    float sm_scale_log2;        // log2(e) / sqrt(D)
+};
+
+template <int G>
+__global__ void __launch_bounds__(KVM_THREADS, 2)
+kv_decode_u4gs2_kernel(const KvMmaArgs a) {
+    constexpr int PASSES = (G + 3) / 4;
+    extern __shared__ __align__(128) uint8_t kvm_smem[];
+    uint8_t* const smem = kvm_smem;
+    __shared__ __align__(8) uint64_t bar_full[KVM_STAGES];
+    __shared__ __align__(8) uint64_t bar_empty[KVM_STAGES];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int len = a.seq_lens ? min(a.seq_lens[b], a.Lk) : a.Lk;
+    const int j0 = tile * a.key_tile, j1 = min(j0 + a.key_tile, len);
+    const int n_stage = j1 > j0 ? (j1 - j0 + KVM_TK - 1) / KVM_TK : 0;
+    const uint32_t sb = smem_u32(smem);
+
+    if (tid == 0) {
+        for (int s = 0; s < KVM_STAGES; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), KVM_WARPS);
+        }
+        mbar_init_fence();
+    }
+    for (int i = tid; i < 4 * 2 * KVM_QREC / 4; i += KVM_THREADS) reinterpret_cast<uint32_t*>(smem + KVM_OFF_Q)[i] = 0u;
+    __syncthreads();
+
+    if (warp == KVM_WARPS) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 1;
+            const int64_t head_row = ((int64_t)b * a.Hkv + hk) * 4;
+            for (int it = 0; it < n_stage; ++it) {
+                if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ph)) {
+                    atomicExch(a.status, 1);
+                    break;
+                }
+                const int j = j0 + it * KVM_TK;
+                const int nk = min(KVM_TK, (j1 - j + 15) & ~15);       // whole 16-key groups (capacity is a multiple of 16)
+                const uint32_t bar = smem_u32(&bar_full[s]);
+                const uint32_t base = sb + s * KVM_STAGE_BYTES;
+                mbar_expect_tx(bar, (uint32_t)(2 * 4 * nk * 25));
+#pragma unroll
+                for (int blk = 0; blk < 4; ++blk) {
+                    const int64_t row = (head_row + blk) * a.Lcap + j;
+                    bulk_g2s(base + KVM_K_UP + blk * KVM_UP, a.k.u + row * 16, (uint32_t)nk * 16, bar);
+                    bulk_g2s(base + KVM_K_SH + blk * KVM_SH, a.k.h + row * 8, (uint32_t)nk * 8, bar);
+                    bulk_g2s(base + KVM_K_SC + blk * KVM_SC, a.k.s + row, (uint32_t)nk, bar);
+                    bulk_g2s(base + KVM_V_UP + blk * KVM_UP, a.v.u + row * 16, (uint32_t)nk * 16, bar);
+                    bulk_g2s(base + KVM_V_SH + blk * KVM_SH, a.v.h + row * 8, (uint32_t)nk * 8, bar);
+                    bulk_g2s(base + KVM_V_SC + blk * KVM_SC, a.v.s + row, (uint32_t)nk, bar);
+                }
+                if (++s == KVM_STAGES) { s = 0; ph ^= 1u; }
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers: stage the query (rotate, 16-bit block fixed point) ----------------
+    const int g = lane >> 2, t = lane & 3, h2 = t >> 1, odd = t & 1;
+    for (int hh = warp; hh < G; hh += KVM_WARPS) {
+        const __nv_bfloat16* qp = a.q + ((int64_t)b * a.Hq + hk * G + hh) * 128 + lane * 4;
+        float v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = __bfloat162float(qp[i]);
+        if (a.qrot) {
+            fwht_warp<4>(v, lane);
+            const float inv = 0.08838834764831845f;                       // 1/sqrt(128)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] *= inv;
+        }
+        uint32_t ax = 0u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ax = max(ax, __float_as_uint(v[i]) & 0x7FFFFFFFu);
+#pragma unroll
+        for (int o = 1; o <= 4; o <<= 1) ax = max(ax, __shfl_xor_sync(0xffffffffu, ax, o));
+        int E = (int)(ax >> 23) - 127;
+        E = ax == 0u ? 0 : max(-100, min(127, E));
+        const float up = __int_as_float((14 - E + 127) << 23);
+        const int blk = lane >> 3, pass = hh >> 2, mm = hh & 3;
+        uint8_t* rec = smem + KVM_OFF_Q + (blk * PASSES + pass) * KVM_QREC;
+        int sum = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            int xi = min(__float2int_rn(v[i] * up), 32639);
+            const int lo = (int)(int8_t)(xi & 0xFF), hi = (xi - lo) >> 8;
+            sum += xi;
+            const int e = (lane & 7) * 4 + i;
+            const int ts = 2 * (e >> 4) + ((e >> 1) & 1), jj = (e & 1) * 4 + ((e & 15) >> 2);
+            rec[(2 * mm) * 32 + ts * 8 + jj] = (uint8_t)hi;
+            rec[(2 * mm + 1) * 32 + ts * 8 + jj] = (uint8_t)lo;
+        }
+#pragma unroll
+        for (int o = 1; o <= 4; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if ((lane & 7) == 0) {
+            int* tc = reinterpret_cast<int*>(rec + 256 + mm * 16);
+            tc[0] = -8 * sum;
+            tc[1] = __float_as_int(ldexpf(a.sm_scale_log2, E - 14));     // scores come out in the exp2 domain
+        }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(KVM_WARPS * 32) : "memory");
+
+    // ------------------------------------ main loop ------------------------------------
+    const uint32_t sel = odd ? 0x7531u : 0x6420u;
+    const uint32_t nshift = odd * 4;
+    const int ck = warp * KVM_CHUNK;                            // first key of this warp's chunk in a stage
+    float* Pw = reinterpret_cast<float*>(smem + KVM_OFF_P) + warp * 8 * KVM_PSTRIDE;
+    float* Rw = reinterpret_cast<float*>(smem + KVM_OFF_R) + warp * 4 * 32;
+    float m_run[PASSES], l_run[PASSES];                         // QK layout: head 4p + t (replicated over g)
+#pragma unroll
+    for (int p = 0; p < PASSES; ++p) { m_run[p] = -INFINITY; l_run[p] = 0.0f; }
+    float acc[4][4][2];                                         // PV layout: head g; [block][n-tile][column 2t, 2t+1]
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int n = 0; n < 4; ++n) acc[i][n][0] = acc[i][n][1] = 0.0f;
+    bool aborted = false;
+
+    int s = 0;
+    uint32_t ph = 0;
+    for (int it = 0; it < n_stage; ++it) {
+        if (!aborted && !mbar_wait_bounded(smem_u32(&bar_full[s]), ph)) {
+            atomicExch(a.status, 1);
+            aborted = true;
+        }
+        const uint32_t so = sb + s * KVM_STAGE_BYTES;
+        const int jbase = j0 + it * KVM_TK + ck;                // global index of this warp's first key
+        if (!aborted && jbase < j1) {
+            // ---- scores: 2 key groups of 16 x 4 blocks, all heads ----
+            float S[PASSES][2][2];
+#pragma unroll
+            for (int p = 0; p < PASSES; ++p) S[p][0][0] = S[p][0][1] = S[p][1][0] = S[p][1][1] = 0.0f;
+#pragma unroll
+            for (int blk = 0; blk < 4; ++blk) {
+                uint2 bq[PASSES];
+                int corr[PASSES];
+                float cx[PASSES];
+#pragma unroll
+                for (int p = 0; p < PASSES; ++p) {
+                    const uint32_t rb = sb + KVM_OFF_Q + (blk * PASSES + p) * KVM_QREC;
+                    bq[p] = lds64<0>(rb + g * 32 + t * 8);
+                    corr[p] = (int)lds32<0>(rb + 256 + t * 16);
+                    cx[p] = __uint_as_float(lds32<4>(rb + 256 + t * 16));
+                }
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    const int kk = ck + mt * 16 + g;
+                    const uint2 w0 = lds64<0>(so + KVM_K_UP + blk * KVM_UP + kk * 16 + h2 * 8);
+                    const uint2 w1 = lds64<128>(so + KVM_K_UP + blk * KVM_UP + kk * 16 + h2 * 8);
+                    const uint32_t s0 = lds32<0>(so + KVM_K_SH + blk * KVM_SH + kk * 8 + h2 * 4);
+                    const uint32_t s1 = lds32<64>(so + KVM_K_SH + blk * KVM_SH + kk * 8 + h2 * 4);
+                    const int e0 = lds_s8<0>(so + KVM_K_SC + blk * KVM_SC + kk);
+                    const int e1 = lds_s8<8>(so + KVM_K_SC + blk * KVM_SC + kk);
+                    const uint32_t m0 = and_xor(s0 >> nshift, 0x0F0F0F0Fu, 0x08080808u);
+                    const uint32_t m1 = and_xor(s1 >> nshift, 0x0F0F0F0Fu, 0x08080808u);
+                    const uint32_t x0 = prmt(w0.x, w0.y, sel), x1 = prmt(w1.x, w1.y, sel);
+                    uint32_t A[4];
+                    A[0] = and_or(x0 << 4, 0xF0F0F0F0u, m0);
+                    A[1] = and_or(x1 << 4, 0xF0F0F0F0u, m1);
+                    A[2] = and_or(x0, 0xF0F0F0F0u, m0);
+                    A[3] = and_or(x1, 0xF0F0F0F0u, m1);
+                    const float sw0 = __int_as_float(e0 * (1 << 23) + (127 << 23));
+                    const float sw1 = __int_as_float(e1 * (1 << 23) + (127 << 23));
+#pragma unroll
+                    for (int p = 0; p < PASSES; ++p) {
+                        const uint32_t B[2] = {bq[p].x, bq[p].y};
+                        int Dm[4];
+                        mma_s8_16832_z(Dm, A, B);
+                        const float f0 = (float)(Dm[0] * 256 + Dm[1] + corr[p]) * cx[p];
+                        const float f1 = (float)(Dm[2] * 256 + Dm[3] + corr[p]) * cx[p];
+                        S[p][mt][0] = fmaf(f0, sw0, S[p][mt][0]);
+                        S[p][mt][1] = fmaf(f1, sw1, S[p][mt][1]);
+                    }
+                }
+            }
+            // ---- online softmax (exp2 domain); thread (g,t): head 4p+t, keys ck + {g, g+8, 16+g, 24+g} ----
+            float alpha[PASSES];
+#pragma unroll
+            for (int p = 0; p < PASSES; ++p) {
+                float mx = -INFINITY;
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        if (jbase + mt * 16 + r * 8 + g >= j1) S[p][mt][r] = -INFINITY;      // key beyond the sequence
+                        mx = fmaxf(mx, S[p][mt][r]);
+                    }
+#pragma unroll
+                for (int o = 4; o <= 16; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                const float m_new = fmaxf(m_run[p], mx);
+                const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+                alpha[p] = exp2f(m_run[p] - m_use);                                          // 0 when nothing was seen before
+                float ps = 0.0f;
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        const float pv = exp2f(S[p][mt][r] - m_use);
+                        ps += pv;
+                        Pw[(4 * p + t) * KVM_PSTRIDE + mt * 16 + r * 8 + g] = pv;
+                    }
+#pragma unroll
+                for (int o = 4; o <= 16; o <<= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+                l_run[p] = l_run[p] * alpha[p] + ps;
+                m_run[p] = m_new;
+            }
+            // ---- value scales of the chunk: E_max per block, and 2^-(E_max - e) per key ----
+            int emax[4];
+#pragma unroll
+            for (int blk = 0; blk < 4; ++blk) {
+                const int ev = lds_s8<0>(so + KVM_V_SC + blk * KVM_SC + ck + lane);
+                const int evm = (jbase + lane < j1) ? ev : -128;
+                emax[blk] = __reduce_max_sync(0xffffffffu, evm);
+                const int sh = min(emax[blk] - ev, 31);
+                Rw[blk * 32 + lane] = (jbase + lane < j1) ? __int_as_float((127 - sh) << 23) : 0.0f;
+            }
+            __syncwarp();
+            // rescale of the running output of head g (PV layout) by that head's alpha
+            float al = __shfl_sync(0xffffffffu, alpha[0], g & 3);
+            if (PASSES > 1) {
+                const float al1 = __shfl_sync(0xffffffffu, alpha[PASSES - 1], g & 3);
+                al = (g < 4) ? al : al1;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int n = 0; n < 4; ++n) { acc[i][n][0] *= al; acc[i][n][1] *= al; }
+            // probabilities of head g for the keys 8t..8t+7 of the chunk, as 16-bit fixed point
+            float pf[8];
+            {
+                const float4 p0 = *reinterpret_cast<const float4*>(Pw + g * KVM_PSTRIDE + 8 * t);
+                const float4 p1 = *reinterpret_cast<const float4*>(Pw + g * KVM_PSTRIDE + 8 * t + 4);
+                pf[0] = p0.x; pf[1] = p0.y; pf[2] = p0.z; pf[3] = p0.w;
+                pf[4] = p1.x; pf[5] = p1.y; pf[6] = p1.z; pf[7] = p1.w;
+            }
+            if (G < 8 && g >= G) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) pf[i] = 0.0f;
+            }
+            // ---- P.V: per block 4 n-tiles of 8 channels (+ one all-ones MMA for the code offset) ----
+            const int lrow = lane & 15;
+            const int vkey = 8 * (lrow >> 2) + 2 * (lrow & 3) + (lane >> 4);      // even keys -> matrix 0, odd -> matrix 1
+#pragma unroll
+            for (int blk = 0; blk < 4; ++blk) {
+                // P' = p * 2^(e - E_max) as u16, bytes split into the hi (row g) and lo (row g+8) operand planes
+                uint32_t pv16[8];
+                {
+                    const float4 r0 = *reinterpret_cast<const float4*>(Rw + blk * 32 + 8 * t);
+                    const float4 r1 = *reinterpret_cast<const float4*>(Rw + blk * 32 + 8 * t + 4);
+                    const float rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) pv16[i] = __float2uint_rn(pf[i] * rr[i] * 65535.0f);
+                }
+                uint32_t PA[4];
+                {
+                    const uint32_t t1 = prmt(pv16[0], pv16[2], 0x5140u), t2 = prmt(pv16[4], pv16[6], 0x5140u);
+                    const uint32_t u1 = prmt(pv16[1], pv16[3], 0x5140u), u2 = prmt(pv16[5], pv16[7], 0x5140u);
+                    PA[0] = prmt(t1, t2, 0x7632u);      // hi bytes, even keys  (row g,   k 4t..4t+3)
+                    PA[1] = prmt(t1, t2, 0x5410u);      // lo bytes, even keys  (row g+8, k 4t..4t+3)
+                    PA[2] = prmt(u1, u2, 0x7632u);      // hi bytes, odd keys   (row g,   k 16+4t..)
+                    PA[3] = prmt(u1, u2, 0x5410u);      // lo bytes, odd keys
+                }
+                uint32_t vr[4], sr[2];
+                ldmatrix_t8_x2(vr, so + KVM_V_UP + blk * KVM_UP + (ck + vkey) * 16);
+                ldmatrix_t8_x1(sr, so + KVM_V_SH + blk * KVM_SH + (ck + 2 * lrow) * 8);
+                // shared codes of group g (nibble g%2 of byte g/2) and group g+8 (byte 4 + g/2): held by lanes g/2 and 4+g/2
+                const int la = (g >> 1) * 4 + t, lb = (4 + (g >> 1)) * 4 + t;
+                const uint32_t gs4 = (g & 1) * 4;
+                const uint32_t me0 = and_xor(__shfl_sync(0xffffffffu, sr[0], la) >> gs4, 0x0F0F0F0Fu, 0x08080808u);
+                const uint32_t me1 = and_xor(__shfl_sync(0xffffffffu, sr[0], lb) >> gs4, 0x0F0F0F0Fu, 0x08080808u);
+                const uint32_t mo0 = and_xor(__shfl_sync(0xffffffffu, sr[1], la) >> gs4, 0x0F0F0F0Fu, 0x08080808u);
+                const uint32_t mo1 = and_xor(__shfl_sync(0xffffffffu, sr[1], lb) >> gs4, 0x0F0F0F0Fu, 0x08080808u);
+                int Dc[4];
+                {
+                    const uint32_t ones[2] = {0x01010101u, 0x01010101u};
+                    mma_u8s8_16832_z(Dc, PA, ones);
+                }
+                const int corr = -8 * (Dc[0] * 256 + Dc[2]);                   // every shared code carries +8
+                const float osc = __int_as_float((emax[blk] + 127) << 23) * (1.0f / 65535.0f);
+                // n-tile 0: channel 2n+1 (high nibbles of byte column g), 1: channel 2n, 2: 17+2n, 3: 16+2n
+#pragma unroll
+                for (int n = 0; n < 4; ++n) {
+                    const uint32_t ve = (n < 2) ? vr[0] : vr[1], vo = (n < 2) ? vr[2] : vr[3];
+                    const uint32_t me = (n < 2) ? me0 : me1, mo = (n < 2) ? mo0 : mo1;
+                    uint32_t Bv[2];
+                    if ((n & 1) == 0) { Bv[0] = and_or(ve, 0xF0F0F0F0u, me); Bv[1] = and_or(vo, 0xF0F0F0F0u, mo); }
+                    else { Bv[0] = and_or(ve << 4, 0xF0F0F0F0u, me); Bv[1] = and_or(vo << 4, 0xF0F0F0F0u, mo); }
+                    int Dv[4];
+                    mma_u8s8_16832_z(Dv, PA, Bv);
+                    acc[blk][n][0] = fmaf((float)(Dv[0] * 256 + Dv[2] + corr), osc, acc[blk][n][0]);
+                    acc[blk][n][1] = fmaf((float)(Dv[1] * 256 + Dv[3] + corr), osc, acc[blk][n][1]);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_empty[s]));
+        if (++s == KVM_STAGES) { s = 0; ph ^= 1u; }
+    }
+
+    // ---------------- merge the four warps, write the tile's partial (acc, m, l) ----------------
+    asm volatile("bar.sync 1, %0;" ::"n"(KVM_WARPS * 32) : "memory");          // ring memory is free to reuse
+    float* mb = reinterpret_cast<float*>(smem);                                // [warp][G][130]
+    // m, l of head 4p+t live in the QK layout (lanes with g == 0 write them)
+    if (g == 0) {
+#pragma unroll
+        for (int p = 0; p < PASSES; ++p) {
+            const int hh = 4 * p + t;
+            if (hh < G) {
+                mb[(warp * G + hh) * 130 + 128] = m_run[p];
+                mb[(warp * G + hh) * 130 + 129] = l_run[p];
+            }
+        }
+    }
+    if (g < G) {
+#pragma unroll
+        for (int blk = 0; blk < 4; ++blk)
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int col = 2 * t + c;                                  // B column = byte column of the V tile
+                    const int d = blk * 32 + ((n < 2) ? 0 : 16) + 2 * col + ((n & 1) ? 0 : 1);
+                    mb[(warp * G + g) * 130 + d] = acc[blk][n][c];
+                }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(KVM_WARPS * 32) : "memory");
+    float* out = a.partial + (((int64_t)b * a.Hq + hk * G) * a.S + tile) * 130;
+    for (int idx = tid; idx < G * 130; idx += KVM_WARPS * 32) {
+        const int hh = idx / 130, d = idx % 130;
+        float mg = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < KVM_WARPS; ++w) mg = fmaxf(mg, mb[(w * G + hh) * 130 + 128]);
+        float r;
+        if (d == 128) r = aborted ? __int_as_float(0x7FC00000) : mg;
+        else {
+            r = 0.0f;
+#pragma unroll
+            for (int w = 0; w < KVM_WARPS; ++w) {
+                const float mw = mb[(w * G + hh) * 130 + 128];
+                const float wgt = (mw == -INFINITY) ? 0.0f : exp2f(mw - mg);
+                r = fmaf(mb[(w * G + hh) * 130 + (d == 129 ? 129 : d)], wgt, r);
+            }
+        }
+        out[(int64_t)hh * a.S * 130 + d] = r;
+    }
+}
+
+// Merge of tile partials kept in the exp2 domain (m is a base-2 exponent).
+__global__ void kv_decode_combine2_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
+                                          float* __restrict__ out_f32, int H, int S) {
+    const int h = blockIdx.x, b = blockIdx.y;
+    const float* base = partial + ((int64_t)b * H + h) * S * 130;
+    float mg = -INFINITY;
+    for (int s = 0; s < S; ++s) mg = fmaxf(mg, base[s * 130 + 128]);
+    for (int d = threadIdx.x; d < 128; d += blockDim.x) {
+        float num = 0.0f, den = 0.0f;
+        for (int s = 0; s < S; ++s) {
+            const float* p = base + s * 130;
+            const float m = p[128];
+            const float w = (m == -INFINITY) ? 0.0f : exp2f(m - mg);
+            num = fmaf(p[d], w, num);
+            den = fmaf(p[129], w, den);
+        }
+        const float r = den > 0.0f ? num / den : (mg != mg ? mg : 0.0f);
+        const int64_t o = ((int64_t)b * H + h) * 128 + d;
+        out[o] = __float2bfloat16_rn(r);
+        if (out_f32) out_f32[o] = r;
+    }
+}
+
+}  // namespace msaq

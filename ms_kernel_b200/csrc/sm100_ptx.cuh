@@ -79,4 +79,63 @@ __device__ __forceinline__ void mma_s8_16832_z(int (&d)[4], const uint32_t (&a)[
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "r"(0));
 }
 
+// Shared-memory loads with a register base and a compile-time byte offset, so
+// that one address register per plane serves a whole stage.
+template <int OFF>
+__device__ __forceinline__ uint2 lds64(uint32_t base) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(base), "n"(OFF));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32(uint32_t base) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(base), "n"(OFF));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ int lds_s8(uint32_t base) {
+    int v;
+    asm volatile("ld.shared.s8 %0, [%1+%2];" : "=r"(v) : "r"(base), "n"(OFF));
+    return v;
+}
+
+// Explicit single-instruction logic ops: the compiler otherwise splits these
+// three-input expressions.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t c) {      // (a & mask) | c
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(c));
+    return r;
+}
+__device__ __forceinline__ uint32_t and_xor(uint32_t a, uint32_t mask, uint32_t c) {     // (a & mask) ^ c
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(a), "r"(mask), "r"(c));
+    return r;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+
+// Unsigned A (u8) x signed B (s8), zero accumulator input.
+__device__ __forceinline__ void mma_u8s8_16832_z(int (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "r"(0));
+}
+
+// Transposing 8-bit matrix loads: lane (g = lane/4, t = lane%4) receives, for each 16x16-byte
+// matrix whose row addresses the lanes supply (lanes 0-15 matrix 0, lanes 16-31 matrix 1),
+// the bytes of rows 4t..4t+3 in column g and in column g+8.
+__device__ __forceinline__ void ldmatrix_t8_x2(uint32_t (&r)[4], uint32_t row_addr) {
+    asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(row_addr));
+}
+__device__ __forceinline__ void ldmatrix_t8_x1(uint32_t (&r)[2], uint32_t row_addr) {
+    asm volatile("ldmatrix.sync.aligned.m16n16.x1.trans.shared.b8 {%0,%1}, [%2];"
+                 : "=r"(r[0]), "=r"(r[1]) : "r"(row_addr));
+}
+
 }  // namespace msaq

@@ -27,7 +27,7 @@ def _dev_planes(p):
     return tuple(cabi.dev(p[k]) for k in KEYS)
 
 
-@pytest.mark.parametrize("H,Lk,D", [(4, 40, 64), (8, 96, 128), (2, 1, 128), (3, 300, 128), (2, 77, 256), (2, 50, 32)])
+@pytest.mark.parametrize("H,Lk,D", [(4, 40, 64), (8, 96, 128), (2, 1, 128), (3, 300, 128), (8, 272, 128), (16, 1040, 128), (2, 77, 256), (2, 50, 32)])
 def test_decode_mha_vs_oracle(rng, cfg, H, Lk, D):
     import cabi
     u, gs = cfg
@@ -43,7 +43,7 @@ def test_decode_mha_vs_oracle(rng, cfg, H, Lk, D):
 def test_decode_gqa_vs_oracle(rng, cfg, Hq, Hkv):
     import cabi
     u, gs = cfg
-    Lk, D = 200, 128
+    Lk, D = 208, 128
     K, V = _kv(rng, Hkv, Lk, D)
     q = orc.to_bf16((rng.standard_normal((Hq, D)) * 0.5).astype(np.float32))
     pK, pV = orc.pack_kv(K, u, gs), orc.pack_kv(V, u, gs)
@@ -101,21 +101,24 @@ def test_decode_with_rotation_vs_oracle(rng, u, gs):
     """Cache built by append-with-rotation, query rotated in the kernel prologue."""
     import cabi
     Hq, Hkv, Lk, D = 16, 4, 130, 128
+    Lcap = 144                                             # capacity a multiple of 16, more than the keys attended
     K = rng.standard_normal((Hkv, Lk, D)).astype(np.float32)
     K[:, :, [3, 40, 77, 120]] *= 20
     K = orc.to_bf16(K)
     V = orc.to_bf16(rng.standard_normal((Hkv, Lk, D)).astype(np.float32))
     q = orc.to_bf16(rng.standard_normal((1, Hq, D)).astype(np.float32))
-    kp = cabi.empty_cache(Hkv, D // 32, Lk, u, gs)
-    vp = cabi.empty_cache(Hkv, D // 32, Lk, u, gs)
-    cabi.kv_write(cabi.bf16_dev(K), kp, Hkv, Lk, D, 0, Lk, u, gs, rot=True)
-    cabi.kv_write(cabi.bf16_dev(V), vp, Hkv, Lk, D, 0, Lk, u, gs)
+    kp = cabi.empty_cache(Hkv, D // 32, Lcap, u, gs, fill=0x6B)
+    vp = cabi.empty_cache(Hkv, D // 32, Lcap, u, gs, fill=0x6B)
+    cabi.kv_write(cabi.bf16_dev(K), kp, Hkv, Lk, D, 0, Lcap, u, gs, rot=True)
+    cabi.kv_write(cabi.bf16_dev(V), vp, Hkv, Lk, D, 0, Lcap, u, gs)
     kpn = tuple(t.cpu().numpy()[None] for t in kp)
     vpn = tuple(t.cpu().numpy()[None] for t in vp)
     ref = orc.decode_attention_batched(q, kpn, vpn, u, gs, [Lk], qrot=True)
-    got, gotf = cabi.decode(cabi.bf16_dev(q), kp, vp, 1, Hq, Hkv, Lk, D, u, gs, qrot=1)
-    # the in-kernel rotation is an fp32 butterfly, the oracle's a float64 product
-    _check(got, gotf, ref, f32_tol=5e-5)
+    got, gotf = cabi.decode(cabi.bf16_dev(q), kp, vp, 1, Hq, Hkv, Lk, D, u, gs, Lcap=Lcap, qrot=1)
+    # Outlier channels give scores of magnitude ~50, so the 16-bit block fixed point in which the
+    # tuned kernel stages the query and the probabilities shows up at the 1e-4 level before the
+    # bf16 rounding (the bf16 output itself is held to the usual tolerance).
+    _check(got, gotf, ref, f32_tol=3e-4)
 
 
 def test_decode_merge_property_long_cache(rng):
