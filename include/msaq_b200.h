@@ -82,6 +82,29 @@ int msaq_wonly_gemv_batched(const void* X, const int8_t* scale_exp, const uint8_
                             int64_t M, int64_t OUT, int64_t NB, int u, int gs,
                             void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * The wide GEMV for callers that may not allocate device memory: a plugin running under a
+ * host whose memory pool it must not touch, a real-time or safety-reviewed loop where
+ * cudaMalloc is forbidden after start-up, a library entered from a context that owns no
+ * allocator.  Same result as msaq_wonly_gemv_wide, but the split-K scratch (staged
+ * activations, partial sums, counters) is a fixed array of MSAQ_STATIC_SCRATCH_BYTES inside
+ * the library image; every GPU that loads the library holds that array until the process
+ * exits.  The call allocates nothing and calls no allocating routine.
+ *   - The first call on each device looks the array's device address up (one host-side query,
+ *     no allocation); make that first call before starting a stream capture.
+ *   - All calls on one device share the array and it keeps the previous call's contents: the
+ *     kernels reset the words that must start at zero, but two calls that overlap on the GPU
+ *     (different streams, or graphs replayed concurrently) race on it.  Serialise them.
+ *   - A problem whose scratch need (msaq_wonly_gemv_workspace(1, OUT, NB, u, gs)) exceeds the
+ *     array is refused with MSAQ_ERR_WORKSPACE; nothing is launched.
+ * This entry point has no counterpart in the reference.
+ */
+#define MSAQ_STATIC_SCRATCH_BYTES (8u << 20)
+size_t msaq_static_scratch_bytes(void);
+int msaq_wonly_gemv_wide_static(const void* x, const int8_t* scale_exp, const uint8_t* upper_cm,
+                                const uint8_t* shared_cm, void* y, float* y_f32,
+                                int64_t OUT, int64_t NB, int u, int gs, void* stream);
+
 /* -------------------------------------------------------- KV cache write -- */
 
 /*

@@ -21,6 +21,8 @@ SIGNATURES = {
     "msaq_wonly_gemv": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _int, _int, _p, _sz, _p]),
     "msaq_wonly_gemv_wide": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _int, _int, _p, _sz, _p]),
     "msaq_wonly_gemv_batched": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _int, _int, _p, _sz, _p]),
+    "msaq_static_scratch_bytes": (_sz, []),
+    "msaq_wonly_gemv_wide_static": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _int, _int, _p]),
     "msaq_kv_append": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _int, _int, _p]),
     "msaq_kv_append_rot": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _int, _int, _p]),
     "msaq_kv_append_varlen": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _p, _i64, _int, _int, _int, _p]),

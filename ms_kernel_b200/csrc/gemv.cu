@@ -1,6 +1,8 @@
 // Host side of the weight-only GEMV entry points: argument checks, the split-K
 // plan, kernel selection.  Replaces the launchers at csrc/w_gemv.cu:1410-1570
 // of the reference.
+#include <mutex>
+
 #include "gemv_mma.cuh"
 
 namespace msaq {
@@ -170,4 +172,49 @@ extern "C" int msaq_wonly_gemv_batched(const void* X, const int8_t* scale_exp, c
                                        void* stream) {
     return gemv_dispatch(X, scale_exp, upper_cm, shared_cm, Y, Y_f32, M, OUT, NB, u, gs, true, workspace,
                          workspace_bytes, stream);
+}
+
+// ---- GEMV without any allocation ---------------------------------------------------------
+// Scratch for msaq_wonly_gemv_wide_static lives in the library image: one array per GPU that
+// loads the library, held until the process exits.
+namespace {
+static __device__ __align__(256) unsigned char g_static_scratch[MSAQ_STATIC_SCRATCH_BYTES];
+std::mutex g_static_mutex;
+void* g_static_ptr[64] = {};
+
+// Device address of the array on the current device.  The array's name is only a host-side
+// handle; the address a kernel can use comes from cudaGetSymbolAddress, asked once per device
+// while that device is current.
+int static_scratch(void** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+        return msaq::fail(MSAQ_ERR_CUDA, "no usable current device for the static scratch");
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p)
+            return msaq::fail(MSAQ_ERR_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return MSAQ_OK;
+}
+}  // namespace
+
+extern "C" size_t msaq_static_scratch_bytes(void) { return MSAQ_STATIC_SCRATCH_BYTES; }
+
+extern "C" int msaq_wonly_gemv_wide_static(const void* x, const int8_t* scale_exp, const uint8_t* upper_cm,
+                                           const uint8_t* shared_cm, void* y, float* y_f32, int64_t OUT, int64_t NB,
+                                           int u, int gs, void* stream) {
+    const size_t need = msaq_wonly_gemv_workspace(1, OUT, NB, u, gs);
+    if (need == 0) return msaq::fail(MSAQ_ERR_ARG, "OUT and NB must be positive");
+    if (need > MSAQ_STATIC_SCRATCH_BYTES)
+        return msaq::fail(MSAQ_ERR_WORKSPACE,
+                          "this GEMV needs %zu bytes of scratch, the built-in scratch holds %zu: use "
+                          "msaq_wonly_gemv_wide with a caller-owned workspace", need, (size_t)MSAQ_STATIC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    if (int rc = static_scratch(&scratch)) return rc;
+    return msaq_wonly_gemv_wide(x, scale_exp, upper_cm, shared_cm, y, y_f32, OUT, NB, u, gs, scratch,
+                                MSAQ_STATIC_SCRATCH_BYTES, stream);
 }
