@@ -48,6 +48,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-detail", action="store_true")
+    ap.add_argument("--case", default=None, choices=["gemv", "kv"],
+                    help="run a few launches of one op only (small driver for ncu captures)")
     return ap.parse_args()
 
 
@@ -190,7 +192,7 @@ class LayerSet:
         for i, (name, (OUT, K)) in enumerate(shape.weight_shapes_local(world).items()):
             lin[name] = make_linear(OUT, K, U, GS, seed * 16 + i + 1000 * rank, dev)
         q, kv, f = shape.local(world)
-        self.Lcap = LK + 8
+        self.Lcap = LK + 16                    # capacity a multiple of 16: the tuned decode path
         self.cache = ops.KVCache(B, kv, shape.head_dim, self.Lcap, U, GS, dev, rotate=True)
         g = torch.Generator(device=dev).manual_seed(seed + 77)
         chunk = 2048
@@ -233,7 +235,8 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
 
     def all_reduce(t):
         dist.all_reduce(t)
@@ -332,7 +335,13 @@ def run_ours(args):
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Tearing the NCCL communicator down after CUDA-graph captured collectives can block for
+        # minutes; every rank is past its last collective here, so leave without the teardown.
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 # --------------------------------------------------------------------------
@@ -379,7 +388,7 @@ def single_gpu_detail(dev, peak, peak_kind):
         caches = []
         g = torch.Generator(device=dev).manual_seed(9)
         for _ in range(copies):
-            c = ops.KVCache(B, Hkv, D, Lk + 8, U, GS, dev, rotate=True)
+            c = ops.KVCache(B, Hkv, D, Lk + 16, U, GS, dev, rotate=True)
             for k0 in range(0, Lk, 4096):
                 n = min(4096, Lk - k0)
                 Kt = torch.randn((B, Hkv, n, D), generator=g, device=dev).to(torch.bfloat16)
@@ -506,9 +515,40 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_case(args):
+    """A handful of launches of one op on cuda:0: the 28672x4096 u4/gs2 M=1 GEMV (92 MB per launch) or
+    the GQA 32/8 flash-decode at Lk=16384, B=8 (157 MB per launch).  Meant to be run under ncu."""
+    import torch
+    from ms_kernel_b200 import ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    g = torch.Generator(device=dev).manual_seed(1)
+    if args.case == "gemv":
+        lins = [make_linear(28672, 4096, U, GS, 3 + i, dev) for i in range(4)]
+        x = torch.randn(4096, generator=g, device=dev).to(torch.bfloat16)
+        for i in range(6):
+            y = lins[i % 4].fwd(x)
+    else:
+        B, Hq, Hkv, Lk, D = 8, 32, 8, 16384, 128
+        caches = []
+        for _ in range(2):
+            c = ops.KVCache(B, Hkv, D, Lk, U, GS, dev, rotate=True)
+            for k0 in range(0, Lk, 4096):
+                c.fill(torch.randn((B, Hkv, 4096, D), generator=g, device=dev).to(torch.bfloat16),
+                       torch.randn((B, Hkv, 4096, D), generator=g, device=dev).to(torch.bfloat16), key0=k0)
+            caches.append(c)
+        q = torch.randn((B, Hq, D), generator=g, device=dev).to(torch.bfloat16)
+        for i in range(6):
+            y = caches[i % 2].attend(q, Lk)
+    torch.cuda.synchronize()
+    print(json.dumps({"case": args.case, "checksum": float(y.float().abs().sum())}))
+
+
 if __name__ == "__main__":
     a = parse()
-    if a.impl == "reference":
+    if a.case:
+        run_case(a)
+    elif a.impl == "reference":
         run_reference(a)
     else:
         run_ours(a)

@@ -40,7 +40,13 @@ struct KvMmaPlan {
 KvMmaPlan plan_mma(int64_t B, int64_t H, int64_t Hkv, int64_t Lk) {
     KvMmaPlan p;
     const int64_t pairs = B * Hkv;
-    int64_t want = (4LL * sm_count() + pairs - 1) / pairs;             // about two waves of two CTAs per SM
+    // Tiles per (sequence, kv head): as many as fit in whole waves of resident CTAs (the last,
+    // partly filled wave of a larger grid would run at a fraction of the machine), at most two waves.
+    const int64_t slots = (int64_t)KVM_CTAS_PER_SM * sm_count();
+    int64_t want = (2 * slots) / pairs;
+    if (want * pairs > slots && want * pairs < 2 * slots && (slots / pairs) >= 1 &&
+        (want * pairs - slots) * 4 < slots)                             // second wave under a quarter full: use one wave
+        want = slots / pairs;
     const int64_t max_tiles = (Lk + KVM_TK - 1) / KVM_TK;
     if (want > max_tiles) want = max_tiles;
     if (want < 1) want = 1;

@@ -31,6 +31,7 @@ constexpr int KVM_THREADS = (KVM_WARPS + 1) * 32;
 constexpr int KVM_TK = 128;                 // keys per stage
 constexpr int KVM_CHUNK = 32;               // keys per warp per stage
 constexpr int KVM_STAGES = 3;
+constexpr int KVM_CTAS_PER_SM = 2;
 constexpr int KVM_UP = KVM_TK * 16, KVM_SH = KVM_TK * 8, KVM_SC = KVM_TK;
 constexpr int KVM_K_UP = 0, KVM_K_SH = 4 * KVM_UP, KVM_K_SC = KVM_K_SH + 4 * KVM_SH;
 constexpr int KVM_V_UP = KVM_K_SC + 4 * KVM_SC, KVM_V_SH = KVM_V_UP + 4 * KVM_UP, KVM_V_SC = KVM_V_SH + 4 * KVM_SH;
@@ -53,7 +54,7 @@ struct KvMmaArgs {
 };
 
 template <int G>
-__global__ void __launch_bounds__(KVM_THREADS, 2)
+__global__ void __launch_bounds__(KVM_THREADS, KVM_CTAS_PER_SM)
 kv_decode_u4gs2_kernel(const KvMmaArgs a) {
     constexpr int PASSES = (G + 3) / 4;
     extern __shared__ __align__(128) uint8_t kvm_smem[];
