@@ -199,6 +199,19 @@ int msaq_kv_decode_attention_batched(const void* q,
                                      int64_t NB, int u, int gs, int64_t Lcap, int qrot,
                                      void* workspace, size_t workspace_bytes, void* stream);
 
+/* ------------------------------------------------------- layer-step glue -- */
+
+/*
+ * Fused element-wise steps between the packed GEMVs of a decoder-layer decode step; the
+ * reference leaves them to PyTorch (tests/harness_batchsweep.py:230-243) and has no op for them.
+ *   msaq_rmsnorm      out[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps)          bf16 in/out, fp32 math
+ *   msaq_silu_mul     out[r,j] = silu(gate_up[r,j]) * gate_up[r,F+j]           bf16 in/out
+ *   msaq_add_residual out = bf16(h + delta), delta fp32 (delta_is_f32 != 0) or bf16
+ */
+int msaq_rmsnorm(const void* x, void* out, int64_t rows, int64_t n, float eps, void* stream);
+int msaq_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t F, void* stream);
+int msaq_add_residual(const void* h, const void* delta, int delta_is_f32, void* out, int64_t n, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -34,6 +34,9 @@ SIGNATURES = {
                                                      _p, _sz, _p]),
     "msaq_kv_decode_attention_batched": (_int, [_p] * 7 + [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64,
                                                              _int, _int, _i64, _int, _p, _sz, _p]),
+    "msaq_rmsnorm": (_int, [_p, _p, _i64, _i64, C.c_float, _p]),
+    "msaq_silu_mul": (_int, [_p, _p, _i64, _i64, _p]),
+    "msaq_add_residual": (_int, [_p, _p, _int, _p, _i64, _p]),
 }
 
 _LIB = None

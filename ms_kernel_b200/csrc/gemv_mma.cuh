@@ -319,23 +319,36 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
                         __threadfence();
                         const bool poison = __ldcg(a.status) != 0;        // a wait gave up somewhere
                         const int ncol = nq * 16;
-                        for (int idx = lane; idx < a.rows * ncol; idx += 32) {
-                            const int m = idx / ncol, j = idx % ncol;
-                            const int col = (j >> 4) * GM_GROUP + warp * 16 + (j & 15);
-                            const float* src = a.partial + (int64_t)m * a.OUT + o0 + col;
-                            const int64_t sstride = (int64_t)a.rows * a.OUT;
-                            float sum = 0.0f;
-                            for (int k0 = 0; k0 < nslots; k0 += 8) {      // eight loads in flight, summed in slot order
-                                float v[8];
+                        const int64_t sstride = (int64_t)a.rows * a.OUT;
+                        const int total = a.rows * ncol;
+                        // two outputs per lane at a time, eight slots each in flight, summed in slot order
+                        for (int i0 = lane; i0 < total; i0 += 64) {
+                            const int i1 = min(i0 + 32, total - 1);
+                            const int m0 = i0 / ncol, j0 = i0 % ncol, m1 = i1 / ncol, j1 = i1 % ncol;
+                            const int64_t e0 = (int64_t)m0 * a.OUT + o0 + (j0 >> 4) * GM_GROUP + warp * 16 + (j0 & 15);
+                            const int64_t e1 = (int64_t)m1 * a.OUT + o0 + (j1 >> 4) * GM_GROUP + warp * 16 + (j1 & 15);
+                            const float* s0 = a.partial + e0;
+                            const float* s1 = a.partial + e1;
+                            float sum0 = 0.0f, sum1 = 0.0f;
+                            for (int k0 = 0; k0 < nslots; k0 += 8) {
+                                float v[8], w[8];
 #pragma unroll
-                                for (int k = 0; k < 8; ++k) v[k] = (k0 + k < nslots) ? __ldcg(src + (k0 + k) * sstride) : 0.0f;
+                                for (int k = 0; k < 8; ++k) {
+                                    const bool in = k0 + k < nslots;
+                                    v[k] = in ? __ldcg(s0 + (k0 + k) * sstride) : 0.0f;
+                                    w[k] = in ? __ldcg(s1 + (k0 + k) * sstride) : 0.0f;
+                                }
 #pragma unroll
-                                for (int k = 0; k < 8; ++k) sum += v[k];
+                                for (int k = 0; k < 8; ++k) { sum0 += v[k]; sum1 += w[k]; }
                             }
-                            if (poison) sum = __int_as_float(0x7FC00000);
-                            const int64_t o = (int64_t)(a.m0 + m) * a.OUT + o0 + col;
-                            a.y[o] = __float2bfloat16_rn(sum);
-                            if (yf) yf[o] = sum;
+                            if (poison) sum0 = sum1 = __int_as_float(0x7FC00000);
+                            const int64_t y0 = (int64_t)a.m0 * a.OUT + e0, y1 = (int64_t)a.m0 * a.OUT + e1;
+                            a.y[y0] = __float2bfloat16_rn(sum0);
+                            if (yf) yf[y0] = sum0;
+                            if (i0 + 32 < total) {
+                                a.y[y1] = __float2bfloat16_rn(sum1);
+                                if (yf) yf[y1] = sum1;
+                            }
                         }
                     }
                     }

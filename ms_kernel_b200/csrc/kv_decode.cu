@@ -40,15 +40,17 @@ struct KvMmaPlan {
 KvMmaPlan plan_mma(int64_t B, int64_t H, int64_t Hkv, int64_t Lk) {
     KvMmaPlan p;
     const int64_t pairs = B * Hkv;
-    // Tiles per (sequence, kv head): as many as fit in whole waves of resident CTAs (the last,
-    // partly filled wave of a larger grid would run at a fraction of the machine), at most two waves.
+    // Tiles per (sequence, kv head).  Enough CTAs for about four waves of resident CTAs, so that
+    // the pipeline fill and the tail of one CTA overlap with the steady state of others -- but no
+    // tile shorter than 1024 keys (query staging, pipeline fill and merge are fixed costs per tile),
+    // except to fill one wave when the whole problem is small.
     const int64_t slots = (int64_t)KVM_CTAS_PER_SM * sm_count();
-    int64_t want = (2 * slots) / pairs;
-    if (want * pairs > slots && want * pairs < 2 * slots && (slots / pairs) >= 1 &&
-        (want * pairs - slots) * 4 < slots)                             // second wave under a quarter full: use one wave
-        want = slots / pairs;
-    const int64_t max_tiles = (Lk + KVM_TK - 1) / KVM_TK;
-    if (want > max_tiles) want = max_tiles;
+    int64_t want = (4 * slots + pairs - 1) / pairs;
+    const int64_t by_size = Lk / 1024;
+    int64_t one_wave = slots / pairs;
+    if (one_wave > (Lk + KVM_TK - 1) / KVM_TK) one_wave = (Lk + KVM_TK - 1) / KVM_TK;
+    const int64_t cap = by_size > one_wave ? by_size : one_wave;
+    if (want > cap) want = cap;
     if (want < 1) want = 1;
     int64_t tile = (Lk + want - 1) / want;
     tile = (tile + KVM_TK - 1) / KVM_TK * KVM_TK;

@@ -400,27 +400,45 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
     }
 }
 
-// Merge of tile partials kept in the exp2 domain (m is a base-2 exponent).
+// Merge of tile partials kept in the exp2 domain (m is a base-2 exponent).  One thread per
+// channel; tiles are read eight at a time so that the loads overlap.
 __global__ void kv_decode_combine2_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
                                           float* __restrict__ out_f32, int H, int S) {
-    const int h = blockIdx.x, b = blockIdx.y;
+    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const float* base = partial + ((int64_t)b * H + h) * S * 130;
     float mg = -INFINITY;
-    for (int s = 0; s < S; ++s) mg = fmaxf(mg, base[s * 130 + 128]);
-    for (int d = threadIdx.x; d < 128; d += blockDim.x) {
-        float num = 0.0f, den = 0.0f;
-        for (int s = 0; s < S; ++s) {
-            const float* p = base + s * 130;
-            const float m = p[128];
-            const float w = (m == -INFINITY) ? 0.0f : exp2f(m - mg);
-            num = fmaf(p[d], w, num);
-            den = fmaf(p[129], w, den);
-        }
-        const float r = den > 0.0f ? num / den : (mg != mg ? mg : 0.0f);
-        const int64_t o = ((int64_t)b * H + h) * 128 + d;
-        out[o] = __float2bfloat16_rn(r);
-        if (out_f32) out_f32[o] = r;
+    for (int s0 = 0; s0 < S; s0 += 8) {
+        float mv[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mv[k] = (s0 + k < S) ? base[(s0 + k) * 130 + 128] : -INFINITY;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mg = fmaxf(mg, mv[k]);            // fmaxf ignores a NaN marker; it is detected below
     }
+    bool poisoned = false;
+    float num = 0.0f, den = 0.0f;
+    for (int s0 = 0; s0 < S; s0 += 8) {
+        float mv[8], pv[8], lv[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const bool ok = s0 + k < S;
+            const float* p = base + (s0 + k) * 130;
+            mv[k] = ok ? p[128] : -INFINITY;
+            pv[k] = ok ? p[d] : 0.0f;
+            lv[k] = ok ? p[129] : 0.0f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            poisoned = poisoned || (mv[k] != mv[k]);
+            const float w = (mv[k] == -INFINITY) ? 0.0f : exp2f(mv[k] - mg);
+            num = fmaf(pv[k], w, num);
+            den = fmaf(lv[k], w, den);
+        }
+    }
+    float r = den > 0.0f ? num / den : 0.0f;
+    if (poisoned) r = __int_as_float(0x7FC00000);                      // a wait gave up in some tile
+    const int64_t o = ((int64_t)b * H + h) * 128 + d;
+    out[o] = __float2bfloat16_rn(r);
+    if (out_f32) out_f32[o] = r;
 }
 
 }  // namespace msaq

@@ -271,6 +271,38 @@ Tensor kv_decode_attention_varlen(const Tensor& q, const Tensor& ks, const Tenso
     return decode_common(q, ks, ku, kh, vs, vu, vh, seq_lens, B, H, Hkv, Lk, D, NB, u, gs, Lcap, qrot ? 1 : 0, true);
 }
 
+// ---- layer-step glue ----------------------------------------------------------
+Tensor rmsnorm(const Tensor& x, double eps) {
+    check_act(x, "x");
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor out = at::empty_like(x);
+    const int64_t n = x.size(-1);
+    check_rc(msaq_rmsnorm(x.data_ptr(), out.data_ptr(), x.numel() / n, n, (float)eps, stream_of(x)), "rmsnorm");
+    return out;
+}
+
+Tensor silu_mul(const Tensor& gate_up) {
+    check_act(gate_up, "gate_up");
+    TORCH_CHECK(gate_up.dim() == 2 && gate_up.size(1) % 2 == 0, "gate_up must be [rows, 2F]");
+    c10::cuda::CUDAGuard guard(gate_up.device());
+    const int64_t rows = gate_up.size(0), F = gate_up.size(1) / 2;
+    Tensor out = at::empty({rows, F}, gate_up.options());
+    check_rc(msaq_silu_mul(gate_up.data_ptr(), out.data_ptr(), rows, F, stream_of(gate_up)), "silu_mul");
+    return out;
+}
+
+Tensor add_residual(const Tensor& h, const Tensor& delta) {
+    check_act(h, "h");
+    TORCH_CHECK(delta.is_cuda() && delta.is_contiguous() && delta.numel() == h.numel() &&
+                (delta.scalar_type() == at::kFloat || delta.scalar_type() == at::kBFloat16),
+                "delta must be a contiguous CUDA fp32 or bf16 tensor of h's size");
+    c10::cuda::CUDAGuard guard(h.device());
+    Tensor out = at::empty_like(h);
+    check_rc(msaq_add_residual(h.data_ptr(), delta.data_ptr(), delta.scalar_type() == at::kFloat, out.data_ptr(),
+                               h.numel(), stream_of(h)), "add_residual");
+    return out;
+}
+
 int64_t launch_count() { return (int64_t)msaq_launch_count(); }
 
 }  // namespace
@@ -307,6 +339,9 @@ TORCH_LIBRARY(msaq, m) {
           "int B, int H, int Hkv, int Lk, int D, int NB, int u, int gs, int Lcap, bool qrot) -> Tensor",
           &kv_decode_attention_varlen);
     m.def("pack_weight(Tensor W, int u, int gs) -> Tensor[]", &pack_weight);
+    m.def("rmsnorm(Tensor x, float eps) -> Tensor", &rmsnorm);
+    m.def("silu_mul(Tensor gate_up) -> Tensor", &silu_mul);
+    m.def("add_residual(Tensor h, Tensor delta) -> Tensor", &add_residual);
     m.def("launch_count() -> int", &launch_count);
 }
 

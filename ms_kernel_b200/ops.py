@@ -129,6 +129,7 @@ class KVCache:
                     torch.zeros((B, Hkv, self.nb, Lcap, self.SB), dtype=torch.uint8, device=device))
 
         self.k, self.v = planes(), planes()
+        self._full_lens = {}
 
     def nbytes_per_key(self):
         return 2 * self.Hkv * self.nb * (self.UB + self.SB + 1)
@@ -159,6 +160,8 @@ class KVCache:
         """q [B,Hq,D] bf16 -> [B,Hq,D] bf16 over the first Lk keys (seq_lens[b] if given)."""
         Hq = int(q.shape[1])
         if seq_lens is None:
-            seq_lens = torch.full((self.B,), Lk, dtype=torch.int32, device=q.device)
+            seq_lens = self._full_lens.get(Lk)
+            if seq_lens is None:
+                seq_lens = self._full_lens[Lk] = torch.full((self.B,), Lk, dtype=torch.int32, device=q.device)
         return _OPS.kv_decode_attention_varlen(q, *self.k, *self.v, seq_lens, self.B, Hq, self.Hkv, Lk, self.D,
                                                self.nb, self.u, self.gs, self.Lcap, self.rotate)

@@ -145,17 +145,42 @@ class DecoderLayerTP:
         self.all_reduce = all_reduce if all_reduce is not None else (lambda t: t)
 
     @staticmethod
-    def _rmsnorm(x, eps):
+    def _fused(x):
+        """The fused glue ops of this library, when x lives on a GPU and they are registered."""
         import torch
+        if x.is_cuda and hasattr(torch.ops, "msaq") and hasattr(torch.ops.msaq, "rmsnorm"):
+            return torch.ops.msaq
+        return None
+
+    @classmethod
+    def _rmsnorm(cls, x, eps):
+        import torch
+        f = cls._fused(x)
+        if f is not None:
+            return f.rmsnorm(x.contiguous(), eps)
         xf = x.float()
         return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+
+    @classmethod
+    def _add(cls, h, delta):
+        f = cls._fused(h)
+        if f is not None:
+            return f.add_residual(h.contiguous(), delta.contiguous())
+        return (h.float() + delta.float()).to(h.dtype)
+
+    @classmethod
+    def _silu_mul(cls, gu, F):
+        import torch
+        f = cls._fused(gu)
+        if f is not None:
+            return f.silu_mul(gu.contiguous())
+        return (torch.nn.functional.silu(gu[:, :F].float()) * gu[:, F:].float()).to(gu.dtype)
 
     def step(self, h, pos, Lk, seq_lens=None):
         """h [B, hidden] bf16 (replicated on every rank) -> new h [B, hidden] bf16 (replicated).
 
         pos: slot the new token's K/V go to (int, or int32 tensor [B]); Lk: keys attended
         after the append (seq_lens[b] per sequence if given)."""
-        import torch
         B = h.shape[0]
         d = self.shape.head_dim
         x = self._rmsnorm(h, self.eps)
@@ -167,13 +192,13 @@ class DecoderLayerTP:
         a = self.cache.attend(q.contiguous(), Lk, seq_lens)            # [B, q, d], heads local
         o = self.lin["o"].fwd(a.reshape(B, self.q_heads * d))          # partial over the local K range
         o = self.all_reduce(o.float()) if self.world > 1 else o
-        h = (h.float() + o.float()).to(h.dtype)
+        h = self._add(h, o)
         x = self._rmsnorm(h, self.eps)
         gu = self.lin["gate_up"].fwd(x)                                # [B, 2 * ffn_rows]
-        act = (torch.nn.functional.silu(gu[:, : self.ffn_rows].float()) * gu[:, self.ffn_rows:].float()).to(h.dtype)
+        act = self._silu_mul(gu, self.ffn_rows)
         dn = self.lin["down"].fwd(act)
         dn = self.all_reduce(dn.float()) if self.world > 1 else dn
-        return (h.float() + dn.float()).to(h.dtype)
+        return self._add(h, dn)
 
     # ---- bookkeeping for the benchmark --------------------------------------
     def algorithmic_bytes(self, B, seq_lens_sum, u, gs):

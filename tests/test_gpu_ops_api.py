@@ -169,3 +169,23 @@ def test_ops_capture_in_cuda_graph(rng):
     g.replay()
     torch.cuda.synchronize()
     assert torch.equal(y, eager)
+
+
+def test_layer_glue_ops(rng):
+    """Fused rmsnorm / SiLU*mul / residual add against plain float64 formulas."""
+    B, H, F = 3, 1024, 768
+    x = _bf(rng.standard_normal((B, H)) * 3)
+    xf = x.float().cpu().numpy().astype(np.float64)
+    ref = xf / np.sqrt((xf ** 2).mean(-1, keepdims=True) + 1e-5)
+    got = torch.ops.msaq.rmsnorm(x, 1e-5).float().cpu().numpy()
+    assert orc.rel_fro(got, orc.to_bf16(ref.astype(np.float32))) < 1e-3
+    gu = _bf(rng.standard_normal((B, 2 * F)) * 2)
+    g64 = gu.float().cpu().numpy().astype(np.float64)
+    ref = g64[:, :F] / (1 + np.exp(-g64[:, :F])) * g64[:, F:]
+    got = torch.ops.msaq.silu_mul(gu).float().cpu().numpy()
+    assert orc.rel_fro(got, orc.to_bf16(ref.astype(np.float32))) < 1e-3
+    d32 = torch.from_numpy(rng.standard_normal((B, H)).astype(np.float32)).cuda()
+    got = torch.ops.msaq.add_residual(x, d32).float().cpu().numpy()
+    assert np.array_equal(got, orc.to_bf16(x.float().cpu().numpy() + d32.cpu().numpy()))
+    got = torch.ops.msaq.add_residual(x, d32.to(torch.bfloat16)).float().cpu().numpy()
+    assert np.array_equal(got, orc.to_bf16(x.float().cpu().numpy() + d32.to(torch.bfloat16).float().cpu().numpy()))
