@@ -46,6 +46,17 @@ const char* msaq_last_error(void);
 /* Number of kernels this library has launched in the calling process. */
 unsigned long long msaq_launch_count(void);
 
+/* Process-wide options (no reference counterpart; the reference reads MS_* environment flags per call,
+ * csrc/kv_attention.cu:2082-2083).  msaq_set_option returns MSAQ_OK or MSAQ_ERR_ARG; msaq_get_option the value.
+ *
+ * MSAQ_OPT_CHAINED_LAUNCH (default 1; MSAQ_CHAINED_LAUNCH=0 in the environment turns it off): kernels are
+ *   launched with programmatic stream serialisation, so the launch and prologue of one kernel overlap the
+ *   tail of the kernel before it.  Results do not change: every kernel waits for its predecessor before it
+ *   reads or writes anything another kernel produces or consumes. */
+#define MSAQ_OPT_CHAINED_LAUNCH 1
+int msaq_set_option(int option, int value);
+int msaq_get_option(int option);
+
 /* ------------------------------------------------------------------ GEMV -- */
 
 /* Bytes of workspace the three GEMV entry points need for these sizes. */

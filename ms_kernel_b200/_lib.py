@@ -17,6 +17,8 @@ SIGNATURES = {
     "msaq_version": (_int, []),
     "msaq_last_error": (C.c_char_p, []),
     "msaq_launch_count": (C.c_ulonglong, []),
+    "msaq_set_option": (_int, [_int, _int]),
+    "msaq_get_option": (_int, [_int]),
     "msaq_wonly_gemv_workspace": (_sz, [_i64, _i64, _i64, _int, _int]),
     "msaq_wonly_gemv": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _int, _int, _p, _sz, _p]),
     "msaq_wonly_gemv_wide": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _int, _int, _p, _sz, _p]),

@@ -2,6 +2,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 #include "msaq_common.cuh"
 
@@ -27,6 +28,20 @@ int check_launch(const char* what) {
         return fail(MSAQ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
     }
     return MSAQ_OK;
+}
+
+namespace {
+std::atomic<int> g_opt_chained{-1};
+}  // namespace
+
+bool option_chained_launch() {
+    int v = g_opt_chained.load(std::memory_order_relaxed);
+    if (v < 0) {                                  // first use: MSAQ_CHAINED_LAUNCH=0 in the environment turns it off
+        const char* e = getenv("MSAQ_CHAINED_LAUNCH");
+        v = (e && e[0] == '0') ? 0 : 1;
+        g_opt_chained.store(v, std::memory_order_relaxed);
+    }
+    return v != 0;
 }
 
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
@@ -65,4 +80,16 @@ int require_sm100() {
 
 extern "C" int msaq_version(void) { return 1000; }
 extern "C" const char* msaq_last_error(void) { return msaq::g_err; }
+extern "C" int msaq_set_option(int option, int value) {
+    switch (option) {
+        case MSAQ_OPT_CHAINED_LAUNCH: msaq::g_opt_chained.store(value ? 1 : 0, std::memory_order_relaxed); return MSAQ_OK;
+        default: return msaq::fail(MSAQ_ERR_ARG, "unknown option %d", option);
+    }
+}
+extern "C" int msaq_get_option(int option) {
+    switch (option) {
+        case MSAQ_OPT_CHAINED_LAUNCH: return msaq::option_chained_launch() ? 1 : 0;
+        default: return msaq::fail(MSAQ_ERR_ARG, "unknown option %d", option);
+    }
+}
 extern "C" unsigned long long msaq_launch_count(void) { return msaq::g_launches.load(std::memory_order_relaxed); }

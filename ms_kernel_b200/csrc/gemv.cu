@@ -67,7 +67,7 @@ int launch_mma(const GemvMmaArgs& a, cudaStream_t st) {
             return fail(MSAQ_ERR_CUDA, "cannot reserve %d bytes of shared memory", smem);
         configured[dev] = smem;
     }
-    gemv_u4gs2_mma_kernel<PASSES, TC><<<a.sch.grid, GM_THREADS, smem, st>>>(a);
+    launch_chained(gemv_u4gs2_mma_kernel<PASSES, TC>, dim3(a.sch.grid), dim3(GM_THREADS), smem, st, a);
     count_launch();
     return check_launch("gemv_u4gs2_mma");
 }
@@ -93,9 +93,8 @@ int run_mma(const __nv_bfloat16* X, const int8_t* se, const uint8_t* up, const u
         const int rows = (int)(M - m0 < tile_rows ? M - m0 : tile_rows);
         const int passes = (rows + GM_MP - 1) / GM_MP;
         const int warps = (int)NB * passes * GM_MP;
-        gemv_xprep_kernel<<<(warps * 32 + 127) / 128, 128, 0, st>>>(X + m0 * NB * BLOCK, base, status, counters,
-                                                                     p.sch.col_tiles * GM_WARPS, m0 == 0 ? 1 : 0, rows, (int)NB,
-                                                                     passes);
+        launch_chained(gemv_xprep_kernel, dim3((warps * 32 + 127) / 128), dim3(128), 0, st, X + m0 * NB * BLOCK, base, status,
+                       counters, p.sch.col_tiles * GM_WARPS, m0 == 0 ? 1 : 0, rows, (int)NB, passes);
         count_launch();
         if (int rc = check_launch("gemv_xprep")) return rc;
         GemvMmaArgs a{se, up, sh, base, partial, counters, status, static_cast<__nv_bfloat16*>(Y), Yf,

@@ -33,7 +33,7 @@ template <int U, bool CM>
 void launch_generic(const GemvPlan& p, const __nv_bfloat16* X, const int8_t* se, const uint8_t* up,
                     const uint8_t* sh, float* partial, int M, int OUT, int NB, const Fmt& f, cudaStream_t st) {
     dim3 grid(p.colblocks, p.splits, p.mtiles);
-#define MSAQ_GO(MR) gemv_generic_kernel<U, CM, MR><<<grid, GEMV_COLS, 0, st>>>( \
+#define MSAQ_GO(MR) launch_chained(gemv_generic_kernel<U, CM, MR>, dim3(grid), dim3(GEMV_COLS), 0, st, \
         X, se, up, sh, partial, M, OUT, NB, f.lg_gs, f.UB, f.SB, p.blocks_per_split)
     switch (p.mr) {
         case 1: MSAQ_GO(1); break;
@@ -70,7 +70,7 @@ int gemv_run_generic(const __nv_bfloat16* x, const int8_t* se, const uint8_t* up
     count_launch();
     if (int rc = check_launch("gemv_generic")) return rc;
     const int64_t n = M * OUT;
-    splitk_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(partial, static_cast<__nv_bfloat16*>(Y), Yf, n,
+    launch_chained(splitk_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, partial, static_cast<__nv_bfloat16*>(Y), Yf, n,
                                                                        p.splits);
     count_launch();
     return check_launch("splitk_combine");

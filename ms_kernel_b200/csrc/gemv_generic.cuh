@@ -8,6 +8,7 @@
 #pragma once
 
 #include "msaq_common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace msaq {
 
@@ -43,6 +44,7 @@ gemv_generic_kernel(const __nv_bfloat16* __restrict__ X, const int8_t* __restric
                     const uint8_t* __restrict__ upper, const uint8_t* __restrict__ shared,
                     float* __restrict__ partial, int M, int OUT, int NB, int lg_gs, int UB, int SB,
                     int blocks_per_split) {
+    chain_wait();
     __shared__ float xs[GEMV_XCHUNK][MR][BLOCK];
     const int o = blockIdx.x * GEMV_COLS + threadIdx.x;
     const int m0 = blockIdx.z * MR;
@@ -99,6 +101,8 @@ gemv_generic_kernel(const __nv_bfloat16* __restrict__ X, const int8_t* __restric
 __global__ void __launch_bounds__(256)
 splitk_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ y,
                       float* __restrict__ y_f32, int64_t n, int splits) {
+    chain_release();
+    chain_wait();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     float s = 0.0f;

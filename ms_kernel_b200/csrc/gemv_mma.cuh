@@ -69,6 +69,8 @@ struct GemvSchedule {
 __global__ void __launch_bounds__(128)
 gemv_xprep_kernel(const __nv_bfloat16* __restrict__ X, uint8_t* __restrict__ xprep, int* __restrict__ status,
                   int* __restrict__ tile_counters, int n_counters, int reset_status, int M, int NB, int passes) {
+    chain_release();
+    chain_wait();
     const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
     const int warp = gtid >> 5, lane = threadIdx.x & 31;
     if (reset_status && gtid == 0) *status = 0;
@@ -187,6 +189,7 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
     if (warp == GM_WARPS) {
         // ------------------------------ producer ------------------------------
         if (lane == 0) {
+            chain_wait();                          // the staged activations come from the kernel before this one
             int s = 0;
             uint32_t ph = 1;                       // parity of the "previous" empty phase: passes at once on a fresh barrier
             for (int it = 0; it < n_iter; ++it) {
@@ -229,6 +232,7 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
     // A wait that gives up marks the warp aborted: it stops waiting and computing,
     // still releases its stages, and publishes nothing (the status word is set).
     bool aborted = false;
+    chain_wait();
 
     int s = 0;
     uint32_t ph = 0;
@@ -308,7 +312,6 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
                             }
                         }
                     }
-                    {
                     __syncwarp();
                     int old = 0;
                     if (lane == 0)
@@ -350,7 +353,6 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
                                 if (yf) yf[y1] = sum1;
                             }
                         }
-                    }
                     }
                 }
             }

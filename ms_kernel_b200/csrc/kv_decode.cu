@@ -73,7 +73,7 @@ int launch_kv_mma(const KvMmaArgs& a, int S, int Hkv, int B, cudaStream_t st) {
             return fail(MSAQ_ERR_CUDA, "cannot reserve %d bytes of shared memory", KVM_SMEM);
         configured[dev] = true;
     }
-    kv_decode_u4gs2_kernel<G><<<dim3((unsigned)S, (unsigned)Hkv, (unsigned)B), KVM_THREADS, KVM_SMEM, st>>>(a);
+    launch_chained(kv_decode_u4gs2_kernel<G>, dim3((unsigned)S, (unsigned)Hkv, (unsigned)B), dim3(KVM_THREADS), KVM_SMEM, st, a);
     count_launch();
     return check_launch("kv_decode_u4gs2");
 }
@@ -83,7 +83,6 @@ int run_mma(const __nv_bfloat16* q, KvPlanes kp, KvPlanes vp, void* out, float* 
     const KvMmaPlan p = plan_mma(B, H, Hkv, Lk);
     uint8_t* base = static_cast<uint8_t*>(ws);
     int* status = reinterpret_cast<int*>(base + p.status_off);
-    if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return fail(MSAQ_ERR_CUDA, "memset failed");
     KvMmaArgs a{q, kp, vp, reinterpret_cast<float*>(base), seq_lens, status, (int)H, (int)Hkv, (int)Lk, (int)Lcap,
                 p.key_tile, p.S, qrot, (float)(1.4426950408889634 / sqrt(128.0))};
     int rc;
@@ -94,8 +93,8 @@ int run_mma(const __nv_bfloat16* q, KvPlanes kp, KvPlanes vp, void* out, float* 
         default: rc = launch_kv_mma<8>(a, p.S, (int)Hkv, (int)B, st); break;
     }
     if (rc) return rc;
-    kv_decode_combine2_kernel<<<dim3((unsigned)H, (unsigned)B), 128, 0, st>>>(
-        reinterpret_cast<const float*>(base), static_cast<__nv_bfloat16*>(out), out_f32, (int)H, p.S);
+    launch_chained(kv_decode_combine2_kernel, dim3((unsigned)H, (unsigned)B), dim3(128), 0, st,
+                   reinterpret_cast<const float*>(base), static_cast<__nv_bfloat16*>(out), out_f32, (int)H, p.S);
     count_launch();
     return check_launch("kv_decode_combine2");
 }
@@ -134,15 +133,15 @@ int decode_dispatch(const void* q, KvPlanes kp, KvPlanes vp, void* out, float* o
     const __nv_bfloat16* qq = static_cast<const __nv_bfloat16*>(q);
     dim3 grid((unsigned)H, (unsigned)p.S, (unsigned)B);
     const size_t smem = ((size_t)D + KVG_CHUNK) * sizeof(float);
-#define MSAQ_GO(U) kv_decode_generic_kernel<U><<<grid, KVG_THREADS, smem, st>>>( \
+#define MSAQ_GO(U) launch_chained(kv_decode_generic_kernel<U>, grid, dim3(KVG_THREADS), smem, st, \
         qq, kp, vp, partial, seq_lens, (int)H, (int)Hkv, (int)Lk, (int)Lcap, (int)D, (int)NB, f, p.key_tile, p.S, \
         sm_scale, qrot)
     if (u == 4) MSAQ_GO(4); else if (u == 3) MSAQ_GO(3); else MSAQ_GO(2);
 #undef MSAQ_GO
     count_launch();
     if (int rc = check_launch("kv_decode_generic")) return rc;
-    kv_decode_combine_kernel<<<dim3((unsigned)H, (unsigned)B), 128, 0, st>>>(
-        partial, static_cast<__nv_bfloat16*>(out), out_f32, (int)H, (int)D, p.S);
+    launch_chained(kv_decode_combine_kernel, dim3((unsigned)H, (unsigned)B), dim3(128), 0, st,
+                   static_cast<const float*>(partial), static_cast<__nv_bfloat16*>(out), out_f32, (int)H, (int)D, p.S);
     count_launch();
     return check_launch("kv_decode_combine");
 }

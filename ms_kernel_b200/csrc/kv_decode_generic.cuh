@@ -9,6 +9,7 @@
 #pragma once
 
 #include "msaq_common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace msaq {
 
@@ -69,6 +70,7 @@ kv_decode_generic_kernel(const __nv_bfloat16* __restrict__ q, KvPlanes kp, KvPla
                          float* __restrict__ partial, const int32_t* __restrict__ seq_lens,
                          int H, int Hkv, int Lk, int Lcap, int D, int NB, Fmt f, int key_tile, int S,
                          float sm_scale, int qrot) {
+    chain_wait();
     extern __shared__ float smem[];
     float* q_sh = smem;                    // [D]
     float* sc = smem + D;                  // [KVG_CHUNK]
@@ -152,6 +154,8 @@ kv_decode_generic_kernel(const __nv_bfloat16* __restrict__ q, KvPlanes kp, KvPla
 // Merge the S tile partials of one (sequence, head): weights exp(m_s - max m).
 __global__ void kv_decode_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
                                          float* __restrict__ out_f32, int H, int D, int S) {
+    chain_release();
+    chain_wait();
     const int h = blockIdx.x, b = blockIdx.y;
     const float* base = partial + ((int64_t)b * H + h) * S * kv_partial_stride(D);
     float mg = -INFINITY;

@@ -3,10 +3,11 @@
 //
 // One warp owns one row of D values (D = 32*EPL): it loads the row, optionally
 // runs the Hadamard butterfly in registers, parks the fp32 row in shared
-// memory, and lanes 0..NB-1 each quantise one 32-block in float64 and store it.
+// memory, and then quantises one 32-block at a time with one lane per element.
 // Behaviour replaced: csrc/kv_attention.cu:1766-1870 (kv_write / kv_append /
 // kv_append_rot kernels) and csrc/rotate.cu:40-69 of the reference.
 #include "msaq_common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace msaq {
 namespace {
@@ -22,13 +23,20 @@ struct RowMap {
     int64_t heads_per_seq;   // Hkv, used with pos
 };
 
+// 2^k as a double, k in [-1022, 1023].
+__device__ __forceinline__ double pow2d(int k) { return __hiloint2double((1023 + k) << 20, 0); }
+
 template <int EPL, bool ROT>
 __global__ void __launch_bounds__(ROWS_PER_CTA * 32)
 quantize_rows_kernel(const __nv_bfloat16* __restrict__ X, int8_t* __restrict__ scale_exp,
                      uint8_t* __restrict__ upper, uint8_t* __restrict__ shared,
                      RowMap map, Fmt f) {
+    chain_release();
+    chain_wait();
     constexpr int D = 32 * EPL, NB = EPL;
+    constexpr int CW = 12;                                   // code words per block: 7 of upper codes, then shared codes
     __shared__ float rowbuf[ROWS_PER_CTA][D];
+    __shared__ uint32_t codes[ROWS_PER_CTA][NB][CW];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * ROWS_PER_CTA + warp;
     if (row >= map.rows) return;
@@ -45,20 +53,72 @@ quantize_rows_kernel(const __nv_bfloat16* __restrict__ X, int8_t* __restrict__ s
     }
 #pragma unroll
     for (int i = 0; i < EPL; ++i) rowbuf[warp][lane * EPL + i] = v[i];
+    for (int i = lane; i < NB * CW; i += 32) (&codes[warp][0][0])[i] = 0u;
     __syncwarp();
 
-    if (lane < NB) {
-        const int64_t head = row / map.rows_per_head;
-        int64_t key = map.key0 + row % map.rows_per_head;
-        if (map.pos) key = map.pos[head / map.heads_per_seq];
-        const int64_t slot = (head * NB + lane) * map.Lcap + key;
-        store_block(&rowbuf[warp][lane * BLOCK], f, scale_exp, upper, shared, slot);
+    const int64_t head = row / map.rows_per_head;
+    int64_t key = map.key0 + row % map.rows_per_head;
+    if (map.pos) key = map.pos[head / map.heads_per_seq];
+    const int lim = (1 << (7 - f.u)) - 1, slo = -(1 << (f.u - 1)), shi = (1 << (f.u - 1)) - 1;
+    const int g0 = lane & ~(f.gs - 1);                        // first lane of this lane's group
+
+    // One lane per element of the 32-block.  The arithmetic is the float64 sequence NumPy runs for
+    // ms_lib/pack.py:47-60 (scalings by powers of two are exact, so a multiply stands in for each
+    // divide; the group sum keeps NumPy's order), so the codes equal the reference's bit for bit.
+#pragma unroll 1
+    for (int b = 0; b < NB; ++b) {
+        const float x = rowbuf[warp][b * BLOCK + lane];
+        float amax = fmaxf(0.0f, fabsf(x));
+#pragma unroll
+        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const int e = block_exponent(amax);
+        const double xv = (double)x;
+        double q = rint(xv * pow2d(-(e + f.u)));
+        q = fmin(fmax(q, (double)-lim), (double)lim);
+        const double res = xv - q * pow2d(e + f.u);
+        double sum;
+        if (f.gs < 8) {                                       // NumPy: plain running sum below 8 terms
+            sum = 0.0;
+            for (int t = 0; t < f.gs; ++t) sum += __shfl_sync(0xffffffffu, res, g0 + t);
+        } else {                                              // NumPy: 8 interleaved partial sums, then a tree
+            double r[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) r[j] = __shfl_sync(0xffffffffu, res, g0 + j);
+            for (int t0 = 8; t0 < f.gs; t0 += 8) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) r[j] += __shfl_sync(0xffffffffu, res, g0 + t0 + j);
+            }
+            sum = ((r[0] + r[1]) + (r[2] + r[3])) + ((r[4] + r[5]) + (r[6] + r[7]));
+        }
+        double sq = rint(sum * pow2d(-f.lg_gs - e));
+        sq = fmin(fmax(sq, (double)slo), (double)shi);
+
+        uint32_t* cw = codes[warp][b];
+        {
+            const uint32_t c = (uint32_t)(int)q & ((1u << f.wbits) - 1u);
+            const int bit = lane * f.wbits, wi = bit >> 5, off = bit & 31;
+            atomicOr(&cw[wi], c << off);
+            if (off + f.wbits > 32) atomicOr(&cw[wi + 1], c >> (32 - off));
+        }
+        if (lane == g0) {
+            const uint32_t c = (uint32_t)(int)sq & ((1u << f.u) - 1u);
+            const int bit = (lane >> f.lg_gs) * f.u, wi = bit >> 5, off = bit & 31;
+            atomicOr(&cw[7 + wi], c << off);
+            if (off + f.u > 32) atomicOr(&cw[7 + wi + 1], c >> (32 - off));
+        }
+        __syncwarp();
+        const int64_t slot = (head * NB + b) * map.Lcap + key;
+        if (lane < f.UB / 4) reinterpret_cast<uint32_t*>(upper + slot * f.UB)[lane] = cw[lane];   // UB is a multiple of 4
+        if (lane < f.SB) shared[slot * f.SB + lane] = (uint8_t)(cw[7 + (lane >> 2)] >> ((lane & 3) * 8));
+        if (lane == 0) scale_exp[slot] = (int8_t)e;
     }
 }
 
 template <int EPL>
 __global__ void __launch_bounds__(ROWS_PER_CTA * 32)
 hadamard_rotate_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int64_t N) {
+    chain_release();
+    chain_wait();
     constexpr int D = 32 * EPL;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * ROWS_PER_CTA + warp;
@@ -79,6 +139,8 @@ pack_weight_kernel(const void* __restrict__ W, int w_is_bf16, int8_t* __restrict
                    uint8_t* __restrict__ upper, uint8_t* __restrict__ shared,
                    uint8_t* __restrict__ upper_cm, uint8_t* __restrict__ shared_cm,
                    int64_t OUT, int64_t nb, Fmt f) {
+    chain_release();
+    chain_wait();
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= OUT * nb) return;
     const int64_t blk = t / OUT, o = t % OUT;      // consecutive threads -> consecutive columns
@@ -118,10 +180,10 @@ int launch_rows(const void* X, int8_t* se, uint8_t* up, uint8_t* sh, const RowMa
     const unsigned grid = (unsigned)((map.rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA);
     const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
     switch (D) {
-        case 32:  quantize_rows_kernel<1, ROT><<<grid, ROWS_PER_CTA * 32, 0, st>>>(x, se, up, sh, map, f); break;
-        case 64:  quantize_rows_kernel<2, ROT><<<grid, ROWS_PER_CTA * 32, 0, st>>>(x, se, up, sh, map, f); break;
-        case 128: quantize_rows_kernel<4, ROT><<<grid, ROWS_PER_CTA * 32, 0, st>>>(x, se, up, sh, map, f); break;
-        case 256: quantize_rows_kernel<8, ROT><<<grid, ROWS_PER_CTA * 32, 0, st>>>(x, se, up, sh, map, f); break;
+        case 32:  launch_chained(quantize_rows_kernel<1, ROT>, dim3(grid), dim3(ROWS_PER_CTA * 32), 0, st, x, se, up, sh, map, f); break;
+        case 64:  launch_chained(quantize_rows_kernel<2, ROT>, dim3(grid), dim3(ROWS_PER_CTA * 32), 0, st, x, se, up, sh, map, f); break;
+        case 128: launch_chained(quantize_rows_kernel<4, ROT>, dim3(grid), dim3(ROWS_PER_CTA * 32), 0, st, x, se, up, sh, map, f); break;
+        case 256: launch_chained(quantize_rows_kernel<8, ROT>, dim3(grid), dim3(ROWS_PER_CTA * 32), 0, st, x, se, up, sh, map, f); break;
         default: return fail(MSAQ_ERR_UNSUPPORTED, "head_dim %lld: must be 32, 64, 128 or 256", (long long)D);
     }
     count_launch();
@@ -185,10 +247,10 @@ extern "C" int msaq_hadamard_rotate(const void* x, void* out, int64_t N, int64_t
     const __nv_bfloat16* xi = static_cast<const __nv_bfloat16*>(x);
     __nv_bfloat16* xo = static_cast<__nv_bfloat16*>(out);
     switch (D) {
-        case 32:  hadamard_rotate_kernel<1><<<grid, ROWS_PER_CTA * 32, 0, st>>>(xi, xo, N); break;
-        case 64:  hadamard_rotate_kernel<2><<<grid, ROWS_PER_CTA * 32, 0, st>>>(xi, xo, N); break;
-        case 128: hadamard_rotate_kernel<4><<<grid, ROWS_PER_CTA * 32, 0, st>>>(xi, xo, N); break;
-        case 256: hadamard_rotate_kernel<8><<<grid, ROWS_PER_CTA * 32, 0, st>>>(xi, xo, N); break;
+        case 32:  launch_chained(hadamard_rotate_kernel<1>, dim3(grid), dim3(ROWS_PER_CTA * 32), 0, st, xi, xo, N); break;
+        case 64:  launch_chained(hadamard_rotate_kernel<2>, dim3(grid), dim3(ROWS_PER_CTA * 32), 0, st, xi, xo, N); break;
+        case 128: launch_chained(hadamard_rotate_kernel<4>, dim3(grid), dim3(ROWS_PER_CTA * 32), 0, st, xi, xo, N); break;
+        case 256: launch_chained(hadamard_rotate_kernel<8>, dim3(grid), dim3(ROWS_PER_CTA * 32), 0, st, xi, xo, N); break;
         default: return fail(MSAQ_ERR_UNSUPPORTED, "rotate: last dim %lld must be 32, 64, 128 or 256", (long long)D);
     }
     count_launch();
@@ -203,8 +265,7 @@ extern "C" int msaq_pack_weight(const void* W, int w_is_bf16, int8_t* scale_exp,
     if (!W) return fail(MSAQ_ERR_ARG, "W is null");
     if (OUT <= 0 || K <= 0 || K % BLOCK) return fail(MSAQ_ERR_ARG, "K must be a positive multiple of 32");
     const int64_t nb = K / BLOCK, total = OUT * nb;
-    pack_weight_kernel<<<(unsigned)((total + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        W, w_is_bf16, scale_exp, upper, shared, upper_cm, shared_cm, OUT, nb, f);
+    launch_chained(pack_weight_kernel, dim3((unsigned)((total + 127) / 128)), dim3(128), 0, static_cast<cudaStream_t>(stream), W, w_is_bf16, scale_exp, upper, shared, upper_cm, shared_cm, OUT, nb, f);
     count_launch();
     return check_launch("pack_weight");
 }

@@ -3,6 +3,7 @@
 // framework kernels.  The reference leaves these to PyTorch (tests/harness_batchsweep.py:
 // 230-243: rmsnorm, SiLU*mul, residual adds); they are not part of its operator surface.
 #include "msaq_common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace msaq {
 namespace {
@@ -10,6 +11,8 @@ namespace {
 // out[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps), fp32 math, bf16 in/out.  One CTA per row.
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int n, float eps) {
+    chain_release();
+    chain_wait();
     __shared__ float red[8];
     const __nv_bfloat16* xr = x + (int64_t)blockIdx.x * n;
     __nv_bfloat16* orow = out + (int64_t)blockIdx.x * n;
@@ -29,6 +32,8 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ 
 // out[r,j] = silu(gu[r,j]) * gu[r,F+j]
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int64_t rows, int F) {
+    chain_release();
+    chain_wait();
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= rows * F) return;
     const int64_t r = i / F, j = i % F;
@@ -40,6 +45,8 @@ silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict_
 template <typename T>
 __global__ void __launch_bounds__(256)
 add_residual_kernel(const __nv_bfloat16* __restrict__ h, const T* __restrict__ d, __nv_bfloat16* __restrict__ out, int64_t n) {
+    chain_release();
+    chain_wait();
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= n) return;
     out[i] = __float2bfloat16_rn(__bfloat162float(h[i]) + (float)d[i]);
@@ -52,8 +59,7 @@ using namespace msaq;
 
 extern "C" int msaq_rmsnorm(const void* x, void* out, int64_t rows, int64_t n, float eps, void* stream) {
     if (!x || !out || rows <= 0 || n <= 0 || n > INT32_MAX) return fail(MSAQ_ERR_ARG, "rmsnorm: bad argument");
-    rmsnorm_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), (int)n, eps);
+    launch_chained(rmsnorm_kernel, dim3((unsigned)rows), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), (int)n, eps);
     count_launch();
     return check_launch("rmsnorm");
 }
@@ -61,8 +67,7 @@ extern "C" int msaq_rmsnorm(const void* x, void* out, int64_t rows, int64_t n, f
 extern "C" int msaq_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t F, void* stream) {
     if (!gate_up || !out || rows <= 0 || F <= 0 || F > INT32_MAX) return fail(MSAQ_ERR_ARG, "silu_mul: bad argument");
     const int64_t n = rows * F;
-    silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, (int)F);
+    launch_chained(silu_mul_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, (int)F);
     count_launch();
     return check_launch("silu_mul");
 }
@@ -72,10 +77,10 @@ extern "C" int msaq_add_residual(const void* h, const void* delta, int delta_is_
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const unsigned grid = (unsigned)((n + 255) / 256);
     if (delta_is_f32)
-        add_residual_kernel<float><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(h), static_cast<const float*>(delta),
+        launch_chained(add_residual_kernel<float>, dim3(grid), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(h), static_cast<const float*>(delta),
                                                         static_cast<__nv_bfloat16*>(out), n);
     else
-        add_residual_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(h),
+        launch_chained(add_residual_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(h),
                                                                  static_cast<const __nv_bfloat16*>(delta),
                                                                  static_cast<__nv_bfloat16*>(out), n);
     count_launch();

@@ -4,6 +4,8 @@
 // reference; the bit layout follows ms_lib/pack.py:82-98.
 #pragma once
 
+#include <utility>
+
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -38,6 +40,25 @@ int check_launch(const char* what);
 void count_launch(int n = 1);
 int sm_count();               // SM count of the current device (cached per device)
 int require_sm100();          // MSAQ_OK or MSAQ_ERR_DEVICE
+bool option_chained_launch(); // kernels are launched with programmatic stream serialisation
+
+// Launch `kernel` so that it may begin while the previous kernel in the stream drains (see
+// chain_wait / chain_release): every kernel of this library executes chain_wait() before it
+// touches memory another kernel produces or consumes.
+template <typename... P, typename... A>
+inline cudaError_t launch_chained(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = option_chained_launch() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<A>(args)...);
+}
 
 // ---- small device helpers ---------------------------------------------------
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }

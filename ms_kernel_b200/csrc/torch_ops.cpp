@@ -304,6 +304,8 @@ Tensor add_residual(const Tensor& h, const Tensor& delta) {
 }
 
 int64_t launch_count() { return (int64_t)msaq_launch_count(); }
+void set_option(int64_t option, int64_t value) { check_rc(msaq_set_option((int)option, (int)value), "set_option"); }
+int64_t get_option(int64_t option) { return (int64_t)msaq_get_option((int)option); }
 
 }  // namespace
 
@@ -343,6 +345,8 @@ TORCH_LIBRARY(msaq, m) {
     m.def("silu_mul(Tensor gate_up) -> Tensor", &silu_mul);
     m.def("add_residual(Tensor h, Tensor delta) -> Tensor", &add_residual);
     m.def("launch_count() -> int", &launch_count);
+    m.def("set_option(int option, int value) -> ()", &set_option);
+    m.def("get_option(int option) -> int", &get_option);
 }
 
 // An importable, otherwise empty Python module: `import ms_cuda` loads this

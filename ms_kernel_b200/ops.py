@@ -29,6 +29,15 @@ def available() -> bool:
     return _AVAILABLE
 
 
+OPT_CHAINED_LAUNCH = 1   # overlap each kernel's launch and prologue with the tail of the one before it (default on)
+
+
+def set_option(option: int, value: bool) -> None:
+    """Process-wide switch of the library (include/msaq_b200.h: msaq_set_option)."""
+    _require()
+    _OPS.set_option(int(option), int(bool(value)))
+
+
 def _require():
     if not _AVAILABLE:
         raise RuntimeError(

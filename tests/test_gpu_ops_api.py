@@ -189,3 +189,59 @@ def test_layer_glue_ops(rng):
     assert np.array_equal(got, orc.to_bf16(x.float().cpu().numpy() + d32.cpu().numpy()))
     got = torch.ops.msaq.add_residual(x, d32.to(torch.bfloat16)).float().cpu().numpy()
     assert np.array_equal(got, orc.to_bf16(x.float().cpu().numpy() + d32.to(torch.bfloat16).float().cpu().numpy()))
+
+
+@pytest.mark.parametrize("chained", [0, 1])
+def test_chained_launch_modes_agree(rng, chained):
+    """Overlapped launches change timing only: a chain of dependent ops (GEMV -> glue -> GEMV ->
+    append -> decode), each consuming the previous one's output and sharing scratch, gives the
+    same bits in every launch mode, eagerly and replayed from a CUDA graph."""
+    from ms_kernel_b200 import ops
+    u, gs, Hd, Hq, Hkv, D, Lk = 4, 2, 1024, 8, 2, 128, 700
+    Lcap = 704
+    W1 = (rng.standard_normal(((Hq + 2 * Hkv) * D, Hd)) * 0.05).astype(np.float32)
+    W2 = (rng.standard_normal((Hd, Hq * D)) * 0.05).astype(np.float32)
+    l1 = ops.PackedLinear(orc.pack_weight(W1, u, gs), "cuda")
+    l2 = ops.PackedLinear(orc.pack_weight(W2, u, gs), "cuda")
+    Kc = _bf(rng.standard_normal((1, Hkv, Lk - 1, D)))
+    Vc = _bf(rng.standard_normal((1, Hkv, Lk - 1, D)))
+    h = _bf(rng.standard_normal((1, Hd)))
+
+    def chain(cache):
+        x = torch.ops.msaq.rmsnorm(h, 1e-5)
+        qkv = l1.fwd(x)
+        q = qkv[:, : Hq * D].reshape(1, Hq, D)
+        k = qkv[:, Hq * D:(Hq + Hkv) * D].reshape(1, Hkv, D)
+        v = qkv[:, (Hq + Hkv) * D:].reshape(1, Hkv, D)
+        cache.append(k, v, Lk - 1)
+        a = cache.attend(q.contiguous(), Lk)
+        o = l2.fwd(a.reshape(1, Hq * D))
+        return torch.ops.msaq.add_residual(h, o)
+
+    def fresh_cache():
+        c = ops.KVCache(1, Hkv, D, Lcap, u, gs, "cuda", rotate=True)
+        c.fill(Kc, Vc, 0)
+        return c
+
+    ops.set_option(ops.OPT_CHAINED_LAUNCH, False)
+    want = chain(fresh_cache()).clone()
+    try:
+        ops.set_option(ops.OPT_CHAINED_LAUNCH, bool(chained))
+        cache = fresh_cache()
+        for _ in range(3):
+            got = chain(cache)
+            assert torch.equal(got, want)
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            chain(cache)
+        torch.cuda.current_stream().wait_stream(s)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            y = chain(cache)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y, want)
+    finally:
+        ops.set_option(ops.OPT_CHAINED_LAUNCH, True)
