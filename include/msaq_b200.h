@@ -94,6 +94,29 @@ int msaq_wonly_gemv_batched(const void* X, const int8_t* scale_exp, const uint8_
                             void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * GEMV with the decoder-layer glue that precedes it folded into the activation staging (no reference
+ * counterpart: the reference runs these steps as separate torch ops, tests/harness_batchsweep.py:230-243).
+ *   MSAQ_PRO_NONE         y = W x                                      x [M][K]
+ *   MSAQ_PRO_RMSNORM      y = W bf16(rmsnorm(x, eps))                  x [M][K]
+ *   MSAQ_PRO_SILU_MUL     y = W bf16(silu(x[:, :K]) * x[:, K:])        x [M][2K]
+ *   MSAQ_PRO_ADD_RMSNORM  h_out = bf16(x + addend); y = W bf16(rmsnorm(h_out, eps))
+ *                         x [M][K] bf16, addend [M][K] bf16 or fp32 (addend_is_f32), h_out [M][K] bf16
+ * rmsnorm(v) = v * rsqrt(mean(v^2) + eps), no gain vector.  Each intermediate is rounded to bf16 exactly as the
+ * separate entry points msaq_rmsnorm / msaq_silu_mul / msaq_add_residual round it.  Column-major planes, any
+ * (u, gs); formats outside the tuned path run the glue as separate kernels into the workspace tail.
+ */
+#define MSAQ_PRO_NONE 0
+#define MSAQ_PRO_RMSNORM 1
+#define MSAQ_PRO_SILU_MUL 2
+#define MSAQ_PRO_ADD_RMSNORM 3
+size_t msaq_wonly_gemv_fused_workspace(int64_t M, int64_t OUT, int64_t NB, int u, int gs);
+int msaq_wonly_gemv_fused(const void* x, int prologue, const void* addend, int addend_is_f32, float eps,
+                          void* h_out, const int8_t* scale_exp, const uint8_t* upper_cm,
+                          const uint8_t* shared_cm, void* y, float* y_f32,
+                          int64_t M, int64_t OUT, int64_t NB, int u, int gs,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * The wide GEMV for callers that may not allocate device memory: a plugin running under a
  * host whose memory pool it must not touch, a real-time or safety-reviewed loop where
  * cudaMalloc is forbidden after start-up, a library entered from a context that owns no

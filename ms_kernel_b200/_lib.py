@@ -23,6 +23,9 @@ SIGNATURES = {
     "msaq_wonly_gemv": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _int, _int, _p, _sz, _p]),
     "msaq_wonly_gemv_wide": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _int, _int, _p, _sz, _p]),
     "msaq_wonly_gemv_batched": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _int, _int, _p, _sz, _p]),
+    "msaq_wonly_gemv_fused_workspace": (_sz, [_i64, _i64, _i64, _int, _int]),
+    "msaq_wonly_gemv_fused": (_int, [_p, _int, _p, _int, C.c_float, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _int,
+                                     _int, _p, _sz, _p]),
     "msaq_static_scratch_bytes": (_sz, []),
     "msaq_wonly_gemv_wide_static": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _int, _int, _p]),
     "msaq_kv_append": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _int, _int, _p]),

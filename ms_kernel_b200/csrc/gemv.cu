@@ -81,22 +81,55 @@ int launch_mma_tc(const GemvMmaArgs& a, cudaStream_t st) {
     }
 }
 
-int run_mma(const __nv_bfloat16* X, const int8_t* se, const uint8_t* up, const uint8_t* sh, void* Y, float* Yf,
-            int64_t M, int64_t OUT, int64_t NB, void* ws, cudaStream_t st) {
+// Glue fused in front of the GEMV (see XprepMode); mode XP_PLAIN when absent.
+struct Prologue {
+    int mode;
+    const void* r;       // XP_ADD_NORM: addend [M][K]
+    int r_is_f32;
+    void* h_out;         // XP_ADD_NORM: the sum, bf16 [M][K]
+    float eps;
+};
+
+int launch_xprep(const XprepArgs& xa, int mode, unsigned grid, cudaStream_t st) {
+    switch (mode) {
+        case XP_RMSNORM: launch_chained(gemv_xprep_kernel<XP_RMSNORM>, dim3(grid), dim3(128), 0, st, xa); break;
+        case XP_SILU_MUL: launch_chained(gemv_xprep_kernel<XP_SILU_MUL>, dim3(grid), dim3(128), 0, st, xa); break;
+        case XP_ADD_NORM: launch_chained(gemv_xprep_kernel<XP_ADD_NORM>, dim3(grid), dim3(128), 0, st, xa); break;
+        default: launch_chained(gemv_xprep_kernel<XP_PLAIN>, dim3(grid), dim3(128), 0, st, xa); break;
+    }
+    count_launch();
+    return check_launch("gemv_xprep");
+}
+
+int run_mma(const __nv_bfloat16* X, const Prologue& pro, const int8_t* se, const uint8_t* up, const uint8_t* sh,
+            void* Y, float* Yf, int64_t M, int64_t OUT, int64_t NB, void* ws, cudaStream_t st) {
     const MmaPlan p = plan_mma(M, OUT, NB);
     uint8_t* base = static_cast<uint8_t*>(ws);
     int* status = reinterpret_cast<int*>(base + p.ctl_off);
     int* counters = status + 64;
     float* partial = reinterpret_cast<float*>(base + p.partial_off);
-    const int64_t tile_rows = GM_MP * GM_MAX_PASSES;
+    const int64_t tile_rows = GM_MP * GM_MAX_PASSES, K = NB * BLOCK;
+    const int64_t ldx = pro.mode == XP_SILU_MUL ? 2 * K : K;
     for (int64_t m0 = 0; m0 < M; m0 += tile_rows) {        // more than 16 rows: one launch per 16-row tile
         const int rows = (int)(M - m0 < tile_rows ? M - m0 : tile_rows);
         const int passes = (rows + GM_MP - 1) / GM_MP;
         const int warps = (int)NB * passes * GM_MP;
-        launch_chained(gemv_xprep_kernel, dim3((warps * 32 + 127) / 128), dim3(128), 0, st, X + m0 * NB * BLOCK, base, status,
-                       counters, p.sch.col_tiles * GM_WARPS, m0 == 0 ? 1 : 0, rows, (int)NB, passes);
-        count_launch();
-        if (int rc = check_launch("gemv_xprep")) return rc;
+        XprepArgs xa{};
+        xa.X = X + m0 * ldx;
+        xa.R = pro.r ? static_cast<const uint8_t*>(pro.r) + m0 * K * (pro.r_is_f32 ? 4 : 2) : nullptr;
+        xa.h_out = pro.h_out ? static_cast<__nv_bfloat16*>(pro.h_out) + m0 * K : nullptr;
+        xa.xprep = base;
+        xa.status = status;
+        xa.tile_counters = counters;
+        xa.n_counters = p.sch.col_tiles * GM_WARPS;
+        xa.reset_status = m0 == 0 ? 1 : 0;
+        xa.M = rows;
+        xa.NB = (int)NB;
+        xa.passes = passes;
+        xa.ldx = (int)ldx;
+        xa.r_is_f32 = pro.r_is_f32;
+        xa.eps = pro.eps;
+        if (int rc = launch_xprep(xa, pro.mode, (unsigned)((warps * 32 + 127) / 128), st)) return rc;
         GemvMmaArgs a{se, up, sh, base, partial, counters, status, static_cast<__nv_bfloat16*>(Y), Yf,
                       (int)m0, rows, (int)OUT, p.sch};
         // the ring depth was planned for the first tile's pass count; a last, smaller tile may go deeper but need not
@@ -110,6 +143,13 @@ int run_mma(const __nv_bfloat16* X, const int8_t* se, const uint8_t* up, const u
         if (rc) return rc;
     }
     return MSAQ_OK;
+}
+
+bool mma_usable(const int8_t* se, const uint8_t* up, const uint8_t* sh, const void* ws, int64_t OUT, int u, int gs,
+                bool cm) {
+    return mma_eligible(OUT, u, gs, cm) &&
+           !((reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(sh) | reinterpret_cast<uintptr_t>(se) |
+              reinterpret_cast<uintptr_t>(ws)) & 15);
 }
 
 int gemv_dispatch(const void* X, const int8_t* se, const uint8_t* up, const uint8_t* sh, void* Y, float* Yf,
@@ -128,10 +168,8 @@ int gemv_dispatch(const void* X, const int8_t* se, const uint8_t* up, const uint
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
 
-    if (mma_eligible(OUT, u, gs, cm) &&
-        !((reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(sh) | reinterpret_cast<uintptr_t>(se) |
-           reinterpret_cast<uintptr_t>(ws)) & 15))
-        return run_mma(x, se, up, sh, Y, Yf, M, OUT, NB, ws, st);
+    if (mma_usable(se, up, sh, ws, OUT, u, gs, cm))
+        return run_mma(x, Prologue{XP_PLAIN, nullptr, 0, nullptr, 0.0f}, se, up, sh, Y, Yf, M, OUT, NB, ws, st);
 
     return gemv_run_generic(x, se, up, sh, Y, Yf, M, OUT, NB, f, cm, ws, st);
 }
@@ -171,6 +209,57 @@ extern "C" int msaq_wonly_gemv_batched(const void* X, const int8_t* scale_exp, c
                                        void* stream) {
     return gemv_dispatch(X, scale_exp, upper_cm, shared_cm, Y, Y_f32, M, OUT, NB, u, gs, true, workspace,
                          workspace_bytes, stream);
+}
+
+// ---- GEMV with the layer glue in front of it fused into the activation staging ---------------
+extern "C" size_t msaq_wonly_gemv_fused_workspace(int64_t M, int64_t OUT, int64_t NB, int u, int gs) {
+    const size_t g = msaq_wonly_gemv_workspace(M, OUT, NB, u, gs);
+    if (g == 0) return 0;
+    return ((g + 255) & ~(size_t)255) + (((size_t)M * NB * BLOCK * 2 + 255) & ~(size_t)255);
+}
+
+extern "C" int msaq_wonly_gemv_fused(const void* x, int prologue, const void* addend, int addend_is_f32, float eps,
+                                     void* h_out, const int8_t* scale_exp, const uint8_t* upper_cm,
+                                     const uint8_t* shared_cm, void* y, float* y_f32, int64_t M, int64_t OUT,
+                                     int64_t NB, int u, int gs, void* workspace, size_t workspace_bytes,
+                                     void* stream) {
+    if (prologue < MSAQ_PRO_NONE || prologue > MSAQ_PRO_ADD_RMSNORM)
+        return fail(MSAQ_ERR_ARG, "unknown prologue %d", prologue);
+    if (prologue == MSAQ_PRO_NONE)
+        return gemv_dispatch(x, scale_exp, upper_cm, shared_cm, y, y_f32, M, OUT, NB, u, gs, true, workspace,
+                             workspace_bytes, stream);
+    Fmt f;
+    if (!make_fmt(u, gs, &f)) return fail(MSAQ_ERR_UNSUPPORTED, "unsupported format u=%d gs=%d", u, gs);
+    if (!x || !scale_exp || !upper_cm || !shared_cm || !y) return fail(MSAQ_ERR_ARG, "null pointer");
+    if (prologue == MSAQ_PRO_ADD_RMSNORM && (!addend || !h_out))
+        return fail(MSAQ_ERR_ARG, "the add+rmsnorm prologue needs an addend and h_out");
+    if (M <= 0 || OUT <= 0 || NB <= 0) return fail(MSAQ_ERR_ARG, "M, OUT and NB must be positive");
+    if (M > INT32_MAX || OUT > INT32_MAX || NB * BLOCK > INT32_MAX / 2) return fail(MSAQ_ERR_ARG, "size exceeds 2^31");
+    if (int rc = require_sm100()) return rc;
+    const size_t need = msaq_wonly_gemv_fused_workspace(M, OUT, NB, u, gs);
+    if (!workspace || workspace_bytes < need)
+        return fail(MSAQ_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", need,
+                    workspace ? workspace_bytes : (size_t)0);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t K = NB * BLOCK;
+    const bool vec_ok = !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(addend)) & 15);
+    if (mma_usable(scale_exp, upper_cm, shared_cm, workspace, OUT, u, gs, true) && vec_ok) {
+        const Prologue pro{prologue, addend, addend_is_f32, h_out, eps};
+        return run_mma(static_cast<const __nv_bfloat16*>(x), pro, scale_exp, upper_cm, shared_cm, y, y_f32, M, OUT, NB,
+                       workspace, st);
+    }
+    // Other formats: the glue runs as kernels of its own into the tail of the workspace.
+    const size_t g = (msaq_wonly_gemv_workspace(M, OUT, NB, u, gs) + 255) & ~(size_t)255;
+    void* tmp = static_cast<uint8_t*>(workspace) + g;
+    int rc = MSAQ_OK;
+    if (prologue == MSAQ_PRO_RMSNORM) rc = msaq_rmsnorm(x, tmp, M, K, eps, stream);
+    else if (prologue == MSAQ_PRO_SILU_MUL) rc = msaq_silu_mul(x, tmp, M, K, stream);
+    else {
+        rc = msaq_add_residual(x, addend, addend_is_f32, h_out, M * K, stream);
+        if (!rc) rc = msaq_rmsnorm(h_out, tmp, M, K, eps, stream);
+    }
+    if (rc) return rc;
+    return gemv_dispatch(tmp, scale_exp, upper_cm, shared_cm, y, y_f32, M, OUT, NB, u, gs, true, workspace, g, stream);
 }
 
 // ---- GEMV without any allocation ---------------------------------------------------------

@@ -66,19 +66,103 @@ struct GemvSchedule {
 // 16h + 4i + 2*odd (bytes 0..3) and 16h + 4i + 2*odd + 1 (bytes 4..7): the
 // elements whose shared codes are the even (odd = 0) or odd nibbles of shared
 // word h, in the byte order the consumer builds its MMA operand in.
+// What the staging kernel computes before it splits the activations (the glue of a decoder
+// layer that would otherwise be separate launches in front of a GEMV):
+//   XP_PLAIN     x = X[m][k]
+//   XP_RMSNORM   x = bf16(X[m][k] * rsqrt(mean_k(X[m][k]^2) + eps))
+//   XP_SILU_MUL  x = bf16(silu(X[m][k]) * X[m][K + k]),  X is [M][2K]
+//   XP_ADD_NORM  h = bf16(X[m][k] + R[m][k]) is written to h_out, then x = rmsnorm(h) as above
+enum XprepMode { XP_PLAIN = 0, XP_RMSNORM = 1, XP_SILU_MUL = 2, XP_ADD_NORM = 3 };
+
+struct XprepArgs {
+    const __nv_bfloat16* X;      // rows start at X + m * ldx
+    const void* R;               // XP_ADD_NORM: the addend, bf16 or fp32, [M][K]
+    __nv_bfloat16* h_out;        // XP_ADD_NORM: the sum, [M][K]
+    uint8_t* xprep;
+    int* status;
+    int* tile_counters;
+    int n_counters, reset_status;
+    int M, NB, passes, ldx, r_is_f32;
+    float eps;
+};
+
+template <int MODE>
 __global__ void __launch_bounds__(128)
-gemv_xprep_kernel(const __nv_bfloat16* __restrict__ X, uint8_t* __restrict__ xprep, int* __restrict__ status,
-                  int* __restrict__ tile_counters, int n_counters, int reset_status, int M, int NB, int passes) {
+gemv_xprep_kernel(const XprepArgs a) {
     chain_release();
     chain_wait();
+    __shared__ float red[GM_MP][4];
     const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
-    const int warp = gtid >> 5, lane = threadIdx.x & 31;
-    if (reset_status && gtid == 0) *status = 0;
-    for (int i = gtid; i < n_counters; i += gridDim.x * blockDim.x) tile_counters[i] = 0;
-    if (warp >= NB * passes * GM_MP) return;
-    const int mm = warp % GM_MP, pass = (warp / GM_MP) % passes, blk = warp / (GM_MP * passes);
+    const int warp = gtid >> 5, lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
+    if (a.reset_status && gtid == 0) *a.status = 0;
+    for (int i = gtid; i < a.n_counters; i += gridDim.x * blockDim.x) a.tile_counters[i] = 0;
+    // a CTA is the four row slots (mm = 0..3) of one (block, pass)
+    const int mm = warp % GM_MP, pass = (warp / GM_MP) % a.passes, blk = warp / (GM_MP * a.passes);
     const int m = pass * GM_MP + mm;
-    const float x = (m < M) ? __bfloat162float(X[(int64_t)m * NB * BLOCK + blk * BLOCK + lane]) : 0.0f;
+    const int K = a.NB * BLOCK;
+    const bool live = blk < a.NB;                  // uniform over the CTA
+
+    float inv_rms = 1.0f;
+    if (MODE == XP_RMSNORM || MODE == XP_ADD_NORM) {
+        // Sum of squares of each of this pass's rows, by the whole CTA, in an order that does not
+        // depend on the CTA: every CTA arrives at the same bits.
+        const float* Rf = static_cast<const float*>(a.R);
+        const __nv_bfloat16* Rh = static_cast<const __nv_bfloat16*>(a.R);
+        for (int r = 0; r < GM_MP; ++r) {
+            const int mr = pass * GM_MP + r;
+            float ss = 0.0f;
+            if (live && mr < a.M) {
+                const uint4* xr = reinterpret_cast<const uint4*>(a.X + (int64_t)mr * a.ldx);
+                for (int i = threadIdx.x; i < K / 8; i += 128) {
+                    const uint4 v = xr[i];
+                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                    float f[8];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) { f[2 * j] = bf16_lo(w[j]); f[2 * j + 1] = bf16_hi(w[j]); }
+                    if (MODE == XP_ADD_NORM) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const int64_t o = (int64_t)mr * K + i * 8 + j;
+                            const float d = a.r_is_f32 ? Rf[o] : __bfloat162float(Rh[o]);
+                            f[j] = __bfloat162float(__float2bfloat16_rn(f[j] + d));
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) red[r][wic] = ss;
+        }
+        __syncthreads();
+        const float tot = (red[mm][0] + red[mm][1]) + (red[mm][2] + red[mm][3]);
+        inv_rms = rsqrtf(tot / (float)K + a.eps);
+    }
+    if (!live) return;
+
+    float x = 0.0f;
+    if (m < a.M) {
+        const int k = blk * BLOCK + lane;
+        const __nv_bfloat16* xr = a.X + (int64_t)m * a.ldx;
+        if (MODE == XP_PLAIN) {
+            x = __bfloat162float(xr[k]);
+        } else if (MODE == XP_SILU_MUL) {
+            const float g = __bfloat162float(xr[k]), u = __bfloat162float(xr[K + k]);
+            x = __bfloat162float(__float2bfloat16_rn(g / (1.0f + __expf(-g)) * u));
+        } else {
+            float hv = __bfloat162float(xr[k]);
+            if (MODE == XP_ADD_NORM) {
+                const int64_t o = (int64_t)m * K + k;
+                const float d = a.r_is_f32 ? static_cast<const float*>(a.R)[o]
+                                           : __bfloat162float(static_cast<const __nv_bfloat16*>(a.R)[o]);
+                const __nv_bfloat16 hb = __float2bfloat16_rn(hv + d);
+                a.h_out[o] = hb;
+                hv = __bfloat162float(hb);
+            }
+            x = __bfloat162float(__float2bfloat16_rn(hv * inv_rms));
+        }
+    }
     uint32_t ax = __float_as_uint(x) & 0x7FFFFFFFu;
 #pragma unroll
     for (int o = 16; o; o >>= 1) ax = max(ax, __shfl_xor_sync(0xffffffffu, ax, o));
@@ -87,7 +171,7 @@ gemv_xprep_kernel(const __nv_bfloat16* __restrict__ X, uint8_t* __restrict__ xpr
     int xi = __float2int_rn(x * __int_as_float((14 - E + 127) << 23));
     xi = min(xi, 32639);
     const int lo = (int)(int8_t)(xi & 0xFF), hi = (xi - lo) >> 8;
-    uint8_t* rec = xprep + ((int64_t)blk * passes + pass) * GM_XREC;
+    uint8_t* rec = a.xprep + ((int64_t)blk * a.passes + pass) * GM_XREC;
     const int e = lane, t = 2 * (e >> 4) + ((e >> 1) & 1), j = (e & 1) * 4 + ((e & 15) >> 2);
     rec[(2 * mm) * 32 + t * 8 + j] = (uint8_t)hi;
     rec[(2 * mm + 1) * 32 + t * 8 + j] = (uint8_t)lo;

@@ -86,6 +86,42 @@ Tensor gemv_common(const Tensor& x, const Tensor& s, const Tensor& up, const Ten
     return y;
 }
 
+// y (and, for the add+rmsnorm prologue, the new residual stream) of a GEMV whose preceding glue is fused in.
+std::vector<Tensor> wonly_gemv_fused(const Tensor& x, const c10::optional<Tensor>& addend, int64_t prologue, double eps,
+                                     const Tensor& s, const Tensor& up, const Tensor& sh, int64_t M, int64_t OUT,
+                                     int64_t NB, int64_t u, int64_t gs) {
+    check_act(x, "x");
+    int64_t UB, SB;
+    fmt_sizes(u, gs, &UB, &SB);
+    TORCH_CHECK(M >= 1 && OUT >= 1 && NB >= 1, "M, OUT and NB must be positive");
+    const int64_t K = NB * 32;
+    TORCH_CHECK(x.numel() == M * K * (prologue == MSAQ_PRO_SILU_MUL ? 2 : 1), "x has ", x.numel(), " elements");
+    check_planes(s, up, sh, x, NB * OUT, UB, SB);
+    c10::cuda::CUDAGuard guard(x.device());
+    const void* ad = nullptr;
+    int ad_f32 = 0;
+    Tensor h_out;
+    if (prologue == MSAQ_PRO_ADD_RMSNORM) {
+        TORCH_CHECK(addend.has_value(), "the add+rmsnorm prologue needs an addend");
+        const Tensor& a = *addend;
+        TORCH_CHECK(a.is_cuda() && a.is_contiguous() && a.numel() == M * K, "addend must be a contiguous CUDA tensor [M, K]");
+        TORCH_CHECK(a.scalar_type() == at::kFloat || a.scalar_type() == at::kBFloat16, "addend must be fp32 or bf16");
+        ad = a.data_ptr();
+        ad_f32 = a.scalar_type() == at::kFloat;
+        h_out = at::empty({M, K}, x.options());
+    }
+    Tensor y = at::empty({M, OUT}, x.options());
+    const size_t wsb = msaq_wonly_gemv_fused_workspace(M, OUT, NB, (int)u, (int)gs);
+    Tensor ws = workspace(x, wsb);
+    check_rc(msaq_wonly_gemv_fused(x.data_ptr(), (int)prologue, ad, ad_f32, (float)eps,
+                                   h_out.defined() ? h_out.data_ptr() : nullptr, s.data_ptr<int8_t>(),
+                                   up.data_ptr<uint8_t>(), sh.data_ptr<uint8_t>(), y.data_ptr(), nullptr, M, OUT, NB,
+                                   (int)u, (int)gs, ws.data_ptr(), wsb, stream_of(x)),
+             "wonly_gemv_fused");
+    if (h_out.defined()) return {y, h_out};
+    return {y};
+}
+
 Tensor wonly_gemv(const Tensor& x, const Tensor& s, const Tensor& up, const Tensor& sh, int64_t OUT, int64_t NB,
                   int64_t u, int64_t gs) {
     return gemv_common(x, s, up, sh, 1, OUT, NB, u, gs, 0);
@@ -340,6 +376,8 @@ TORCH_LIBRARY(msaq, m) {
           "Tensor vs, Tensor vu, Tensor vh, Tensor seq_lens, "
           "int B, int H, int Hkv, int Lk, int D, int NB, int u, int gs, int Lcap, bool qrot) -> Tensor",
           &kv_decode_attention_varlen);
+    m.def("wonly_gemv_fused(Tensor x, Tensor? addend, int prologue, float eps, Tensor scale_exp, Tensor upper_cm, "
+          "Tensor shared_cm, int M, int OUT, int NB, int u, int gs) -> Tensor[]", &wonly_gemv_fused);
     m.def("pack_weight(Tensor W, int u, int gs) -> Tensor[]", &pack_weight);
     m.def("rmsnorm(Tensor x, float eps) -> Tensor", &rmsnorm);
     m.def("silu_mul(Tensor gate_up) -> Tensor", &silu_mul);

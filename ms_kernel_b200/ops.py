@@ -29,6 +29,7 @@ def available() -> bool:
     return _AVAILABLE
 
 
+PRO_NONE, PRO_RMSNORM, PRO_SILU_MUL, PRO_ADD_RMSNORM = 0, 1, 2, 3   # include/msaq_b200.h: MSAQ_PRO_*
 OPT_CHAINED_LAUNCH = 1   # overlap each kernel's launch and prologue with the tail of the one before it (default on)
 
 
@@ -114,6 +115,18 @@ class PackedLinear:
                                         self.OUT, self.nb, self.u, self.gs)
         return _OPS.wonly_gemv_batched(x, self.scale_exp, self.upper_cm, self.shared_cm,
                                        int(x.shape[0]), self.OUT, self.nb, self.u, self.gs)
+
+
+    def fwd_fused(self, x, prologue, addend=None, eps=1e-5):
+        """The GEMV with the layer glue in front of it done by the activation-staging kernel.
+
+        prologue: PRO_RMSNORM (x [M,K]), PRO_SILU_MUL (x [M,2K] = gate | up) or PRO_ADD_RMSNORM
+        (x [M,K] + addend [M,K] fp32/bf16).  Returns y [M,OUT]; for PRO_ADD_RMSNORM (y, x + addend)."""
+        M = int(x.shape[0])
+        out = _OPS.wonly_gemv_fused(x.contiguous(), None if addend is None else addend.contiguous(), int(prologue),
+                                    float(eps), self.scale_exp, self.upper_cm, self.shared_cm, M, self.OUT, self.nb,
+                                    self.u, self.gs)
+        return (out[0], out[1]) if prologue == PRO_ADD_RMSNORM else out[0]
 
 
 class KVCache:

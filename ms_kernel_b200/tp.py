@@ -180,11 +180,18 @@ class DecoderLayerTP:
         """h [B, hidden] bf16 (replicated on every rank) -> new h [B, hidden] bf16 (replicated).
 
         pos: slot the new token's K/V go to (int, or int32 tensor [B]); Lk: keys attended
-        after the append (seq_lens[b] per sequence if given)."""
+        after the append (seq_lens[b] per sequence if given).
+
+        Linears that offer fwd_fused (ops.PackedLinear on a GPU) take the rmsnorm, the
+        residual add + rmsnorm and the SiLU*mul inside their activation staging; any other
+        linear gets the same steps as separate ops."""
         B = h.shape[0]
         d = self.shape.head_dim
-        x = self._rmsnorm(h, self.eps)
-        qkv = self.lin["qkv"].fwd(x)                                   # [B, (q + 2kv) * d], rows local
+        fused = all(hasattr(self.lin[k], "fwd_fused") for k in ("qkv", "gate_up", "down"))
+        if fused:
+            qkv = self.lin["qkv"].fwd_fused(h, 1, None, self.eps)      # rmsnorm inside
+        else:
+            qkv = self.lin["qkv"].fwd(self._rmsnorm(h, self.eps))      # [B, (q + 2kv) * d], rows local
         q = qkv[:, : self.q_heads * d].reshape(B, self.q_heads, d)
         k = qkv[:, self.q_heads * d:(self.q_heads + self.kv_heads) * d].reshape(B, self.kv_heads, d)
         v = qkv[:, (self.q_heads + self.kv_heads) * d:].reshape(B, self.kv_heads, d)
@@ -192,11 +199,13 @@ class DecoderLayerTP:
         a = self.cache.attend(q.contiguous(), Lk, seq_lens)            # [B, q, d], heads local
         o = self.lin["o"].fwd(a.reshape(B, self.q_heads * d))          # partial over the local K range
         o = self.all_reduce(o.float()) if self.world > 1 else o
-        h = self._add(h, o)
-        x = self._rmsnorm(h, self.eps)
-        gu = self.lin["gate_up"].fwd(x)                                # [B, 2 * ffn_rows]
-        act = self._silu_mul(gu, self.ffn_rows)
-        dn = self.lin["down"].fwd(act)
+        if fused:
+            gu, h = self.lin["gate_up"].fwd_fused(h, 3, o, self.eps)   # h + o, rmsnorm inside
+            dn = self.lin["down"].fwd_fused(gu, 2)                     # SiLU(gate) * up inside
+        else:
+            h = self._add(h, o)
+            gu = self.lin["gate_up"].fwd(self._rmsnorm(h, self.eps))   # [B, 2 * ffn_rows]
+            dn = self.lin["down"].fwd(self._silu_mul(gu, self.ffn_rows))
         dn = self.all_reduce(dn.float()) if self.world > 1 else dn
         return self._add(h, dn)
 
