@@ -52,8 +52,12 @@ unsigned long long msaq_launch_count(void);
  * MSAQ_OPT_CHAINED_LAUNCH (default 1; MSAQ_CHAINED_LAUNCH=0 in the environment turns it off): kernels are
  *   launched with programmatic stream serialisation, so the launch and prologue of one kernel overlap the
  *   tail of the kernel before it.  Results do not change: every kernel waits for its predecessor before it
- *   reads or writes anything another kernel produces or consumes. */
+ *   reads or writes anything another kernel produces or consumes.
+ * MSAQ_OPT_TENSOR_MEMORY (default 1): batched GEMVs (u=4, gs=2, 9 rows and more) run on the tcgen05 tensor
+ *   cores with accumulators in tensor memory; 0 keeps them on the warp-level integer MMA path (the two paths
+ *   agree to the output tolerance, not bit for bit). */
 #define MSAQ_OPT_CHAINED_LAUNCH 1
+#define MSAQ_OPT_TENSOR_MEMORY 2
 int msaq_set_option(int option, int value);
 int msaq_get_option(int option);
 

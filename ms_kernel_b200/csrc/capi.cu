@@ -32,6 +32,7 @@ int check_launch(const char* what) {
 
 namespace {
 std::atomic<int> g_opt_chained{-1};
+std::atomic<int> g_opt_tmem{1};
 }  // namespace
 
 bool option_chained_launch() {
@@ -43,6 +44,8 @@ bool option_chained_launch() {
     }
     return v != 0;
 }
+
+bool option_tensor_memory() { return g_opt_tmem.load(std::memory_order_relaxed) != 0; }
 
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 
@@ -83,12 +86,14 @@ extern "C" const char* msaq_last_error(void) { return msaq::g_err; }
 extern "C" int msaq_set_option(int option, int value) {
     switch (option) {
         case MSAQ_OPT_CHAINED_LAUNCH: msaq::g_opt_chained.store(value ? 1 : 0, std::memory_order_relaxed); return MSAQ_OK;
+        case MSAQ_OPT_TENSOR_MEMORY: msaq::g_opt_tmem.store(value ? 1 : 0, std::memory_order_relaxed); return MSAQ_OK;
         default: return msaq::fail(MSAQ_ERR_ARG, "unknown option %d", option);
     }
 }
 extern "C" int msaq_get_option(int option) {
     switch (option) {
         case MSAQ_OPT_CHAINED_LAUNCH: return msaq::option_chained_launch() ? 1 : 0;
+        case MSAQ_OPT_TENSOR_MEMORY: return msaq::option_tensor_memory() ? 1 : 0;
         default: return msaq::fail(MSAQ_ERR_ARG, "unknown option %d", option);
     }
 }

@@ -4,6 +4,7 @@
 #include <mutex>
 
 #include "gemv_mma.cuh"
+#include "gemv_umma.cuh"
 
 namespace msaq {
 namespace {
@@ -79,6 +80,75 @@ int launch_mma_tc(const GemvMmaArgs& a, cudaStream_t st) {
         case 256: return launch_mma<PASSES, 256>(a, st);
         default: return launch_mma<PASSES, 512>(a, st);
     }
+}
+
+// ---- tensor-memory path (u4/gs2, column-major planes, OUT % 16 == 0, M >= GU_MIN_M) ----------
+constexpr int64_t GU_MIN_M = 9;
+
+struct UmmaPlan {
+    GemvSchedule sch;
+    size_t xs_bytes, ctl_off, partial_off, total;
+};
+
+UmmaPlan plan_umma(int64_t M, int64_t OUT, int64_t NB) {
+    UmmaPlan p;
+    GemvSchedule& s = p.sch;
+    const int64_t rows = M < GU_MAX_N ? M : GU_MAX_N;
+    s.tc = GU_TR;
+    s.nb = (int)NB;
+    s.col_tiles = (int)((OUT + GU_TR - 1) / GU_TR);
+    const long long units = s.units(), slots = sm_count();
+    s.grid = (int)(units < slots ? units : slots);
+    s.max_slots = (int)(((long long)s.nb * s.grid + units - 1) / units) + 1;
+    int stages = (200 * 1024 - 2 * GU_ABUF_BYTES) / GU_STAGE;
+    if (stages > GU_MAX_STAGES) stages = GU_MAX_STAGES;
+    s.stages = stages;
+    p.xs_bytes = ((size_t)NB * GU_XTILE + 255) & ~(size_t)255;
+    p.ctl_off = p.xs_bytes;                                        // status word
+    p.partial_off = p.ctl_off + 256;
+    p.total = p.partial_off + (((size_t)s.max_slots * rows * OUT * sizeof(float) + 255) & ~(size_t)255);
+    return p;
+}
+
+int run_umma(const __nv_bfloat16* X, const int8_t* se, const uint8_t* up, const uint8_t* sh, void* Y, float* Yf,
+             int64_t M, int64_t OUT, int64_t NB, void* ws, cudaStream_t st) {
+    const UmmaPlan p = plan_umma(M, OUT, NB);
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    int* status = reinterpret_cast<int*>(base + p.ctl_off);
+    float* partial = reinterpret_cast<float*>(base + p.partial_off);
+    static int configured[64] = {};                      // largest dynamic smem size set per device
+    for (int64_t m0 = 0; m0 < M; m0 += GU_MAX_N) {        // more than 128 rows: one launch pair per 128-row tile
+        const int rows = (int)(M - m0 < GU_MAX_N ? M - m0 : GU_MAX_N);
+        const int64_t threads = NB * ((rows + 7) / 8 * 8) * 4;
+        launch_chained(gemv_umma_xprep_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, st,
+                       X + m0 * NB * BLOCK, base, status, m0 == 0 ? 1 : 0, rows, (int)NB);
+        count_launch();
+        if (int rc = check_launch("gemv_umma_xprep")) return rc;
+        const GemvSchedule sch = p.sch;
+        const int smem = sch.stages * GU_STAGE + 2 * GU_ABUF_BYTES;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev >= 0 && dev < 64 && configured[dev] < smem) {
+            if (cudaFuncSetAttribute(gemv_u4gs2_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+                cudaSuccess)
+                return fail(MSAQ_ERR_CUDA, "cannot reserve %d bytes of shared memory", smem);
+            configured[dev] = smem;
+        }
+        GemvUmmaArgs a{se, up, sh, base, partial, status, static_cast<__nv_bfloat16*>(Y), Yf, (int)m0, rows, (int)OUT, sch};
+        launch_chained(gemv_u4gs2_umma_kernel, dim3(sch.grid), dim3(GU_THREADS), (size_t)smem, st, a);
+        count_launch();
+        if (int rc = check_launch("gemv_u4gs2_umma")) return rc;
+        // every CTA boundary on a tile boundary: all tiles were written directly; otherwise some tile has partials
+        if (!(sch.units() % sch.grid == 0 && (sch.units() / sch.grid) % sch.nb == 0)) {
+            const int64_t quads = (int64_t)rows * (OUT / 4);
+            launch_chained(gemv_umma_combine_kernel, dim3((unsigned)((quads + 255) / 256)), dim3(256), 0, st,
+                           static_cast<const float*>(partial), static_cast<const int*>(status),
+                           static_cast<__nv_bfloat16*>(Y), Yf, sch, (int)m0, rows, (int)OUT);
+            count_launch();
+            if (int rc = check_launch("gemv_umma_combine")) return rc;
+        }
+    }
+    return MSAQ_OK;
 }
 
 // Glue fused in front of the GEMV (see XprepMode); mode XP_PLAIN when absent.
@@ -168,8 +238,13 @@ int gemv_dispatch(const void* X, const int8_t* se, const uint8_t* up, const uint
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
 
-    if (mma_usable(se, up, sh, ws, OUT, u, gs, cm))
+    if (mma_usable(se, up, sh, ws, OUT, u, gs, cm)) {
+        // the tensor-memory epilogue stores 16 outputs at a time: Y (and Y_f32) must be 16-byte aligned for it
+        if (M >= GU_MIN_M && option_tensor_memory() &&
+            !((reinterpret_cast<uintptr_t>(Y) | reinterpret_cast<uintptr_t>(Yf)) & 15))
+            return run_umma(x, se, up, sh, Y, Yf, M, OUT, NB, ws, st);
         return run_mma(x, Prologue{XP_PLAIN, nullptr, 0, nullptr, 0.0f}, se, up, sh, Y, Yf, M, OUT, NB, ws, st);
+    }
 
     return gemv_run_generic(x, se, up, sh, Y, Yf, M, OUT, NB, f, cm, ws, st);
 }
@@ -185,6 +260,10 @@ extern "C" size_t msaq_wonly_gemv_workspace(int64_t M, int64_t OUT, int64_t NB, 
     if (mma_eligible(OUT, u, gs, true)) {
         const size_t tuned = plan_mma(M, OUT, NB).total;
         if (tuned > bytes) bytes = tuned;
+        if (M >= GU_MIN_M) {
+            const size_t tm = plan_umma(M, OUT, NB).total;
+            if (tm > bytes) bytes = tm;
+        }
     }
     return bytes;
 }
@@ -243,7 +322,9 @@ extern "C" int msaq_wonly_gemv_fused(const void* x, int prologue, const void* ad
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int64_t K = NB * BLOCK;
     const bool vec_ok = !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(addend)) & 15);
-    if (mma_usable(scale_exp, upper_cm, shared_cm, workspace, OUT, u, gs, true) && vec_ok) {
+    // fused staging belongs to the integer-MMA kernel; batches the tensor-memory kernel takes run the glue separately
+    const bool small = M < GU_MIN_M || !option_tensor_memory();
+    if (mma_usable(scale_exp, upper_cm, shared_cm, workspace, OUT, u, gs, true) && vec_ok && small) {
         const Prologue pro{prologue, addend, addend_is_f32, h_out, eps};
         return run_mma(static_cast<const __nv_bfloat16*>(x), pro, scale_exp, upper_cm, shared_cm, y, y_f32, M, OUT, NB,
                        workspace, st);

@@ -41,6 +41,7 @@ void count_launch(int n = 1);
 int sm_count();               // SM count of the current device (cached per device)
 int require_sm100();          // MSAQ_OK or MSAQ_ERR_DEVICE
 bool option_chained_launch(); // kernels are launched with programmatic stream serialisation
+bool option_tensor_memory();  // batched GEMVs of 9 rows and more run on tcgen05 with tensor-memory accumulators
 
 // Launch `kernel` so that it may begin while the previous kernel in the stream drains (see
 // chain_wait / chain_release): every kernel of this library executes chain_wait() before it

@@ -52,6 +52,30 @@ def test_gemv_batched(rng, cfg, M):
     _check(got, gotf, orc.wonly_matmul(p, X))
 
 
+@pytest.mark.parametrize("M,OUT,K", [(9, 512, 256), (16, 384, 512), (17, 1040, 2048), (64, 2048, 4096),
+                                     (100, 528, 1024), (128, 512, 512), (130, 1024, 512), (300, 400, 256)])
+def test_gemv_batched_tensor_memory_path(rng, M, OUT, K):
+    """u4/gs2 with 9 rows and more runs on tcgen05 with tensor-memory accumulators: row tiles that
+    split over several CTAs (split-K partials), ragged last tiles, more than 128 rows (several
+    launches), against the oracle -- and against the integer-MMA path with the option off."""
+    import cabi
+    from ms_kernel_b200 import _lib
+    W, X, p = _case(rng, OUT, K, 4, 2, M=M)
+    pd = cabi.planes_to_dev(p)
+    ref = orc.wonly_matmul(p, X)
+    L = _lib.lib()
+    assert L.msaq_get_option(2) == 1
+    got, gotf = cabi.gemv("batched", cabi.bf16_dev(X), pd, M=M)
+    _check(got, gotf, ref)
+    assert L.msaq_set_option(2, 0) == 0
+    try:
+        got2, gotf2 = cabi.gemv("batched", cabi.bf16_dev(X), pd, M=M)
+    finally:
+        L.msaq_set_option(2, 1)
+    _check(got2, gotf2, ref)
+    assert orc.rel_fro(gotf, gotf2) < 1e-4
+
+
 @pytest.mark.parametrize("u", (2, 3, 4))
 def test_gemv_llama_shape_vs_oracle(rng, u):
     """One full Llama-3.1-8B projection (O: 4096x4096) at gs=2, packed on the device."""

@@ -29,10 +29,14 @@ def test_fused_prologues_match_separate_ops(rng, u, gs, M):
     gu = _bf(rng.standard_normal((M, 2 * K)) * 2)
     msaq = torch.ops.msaq
 
-    # SiLU * mul: same expression element by element, so the same bits
+    # SiLU * mul: same expression element by element, so the same bits -- as long as both run the same
+    # GEMV kernel (with 9 rows and more the unfused u4/gs2 call takes the tensor-memory path)
     want = lin.fwd(msaq.silu_mul(gu))
     got = lin.fwd_fused(gu, ops.PRO_SILU_MUL)
-    assert torch.equal(got.reshape(want.shape), want)
+    if M < 9 or (u, gs) != (4, 2):
+        assert torch.equal(got.reshape(want.shape), want)
+    else:
+        assert orc.rel_fro(got.float().cpu().numpy(), want.float().cpu().numpy()) < REL_FRO_TOL
 
     # rmsnorm: the sum of squares is taken in another order, so a normalised element may round the other way
     want = lin.fwd(msaq.rmsnorm(h, 1e-5)).float().cpu().numpy()
