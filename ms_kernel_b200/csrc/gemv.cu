@@ -24,6 +24,8 @@ struct MmaPlan {
 };
 
 bool mma_eligible(int64_t OUT, int u, int gs, bool cm) { return cm && u == 4 && gs == 2 && OUT % 16 == 0; }
+// the tensor-memory kernel also decodes the 5+3 and 6+2 bit formats
+bool umma_eligible(int64_t OUT, int u, int gs, bool cm) { return cm && u >= 2 && u <= 4 && gs == 2 && OUT % 16 == 0; }
 
 MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB) {
     MmaPlan p;
@@ -90,7 +92,7 @@ struct UmmaPlan {
     size_t xs_bytes, ctl_off, partial_off, total;
 };
 
-UmmaPlan plan_umma(int64_t M, int64_t OUT, int64_t NB) {
+UmmaPlan plan_umma(int64_t M, int64_t OUT, int64_t NB, int u) {
     UmmaPlan p;
     GemvSchedule& s = p.sch;
     const int64_t rows = M < GU_MAX_N ? M : GU_MAX_N;
@@ -100,7 +102,7 @@ UmmaPlan plan_umma(int64_t M, int64_t OUT, int64_t NB) {
     const long long units = s.units(), slots = sm_count();
     s.grid = (int)(units < slots ? units : slots);
     s.max_slots = (int)(((long long)s.nb * s.grid + units - 1) / units) + 1;
-    int stages = (200 * 1024 - 2 * GU_ABUF_BYTES) / GU_STAGE;
+    int stages = (200 * 1024 - 2 * GU_ABUF_BYTES) / gu_stage(u);
     if (stages > GU_MAX_STAGES) stages = GU_MAX_STAGES;
     s.stages = stages;
     p.xs_bytes = ((size_t)NB * GU_XTILE + 255) & ~(size_t)255;
@@ -110,13 +112,27 @@ UmmaPlan plan_umma(int64_t M, int64_t OUT, int64_t NB) {
     return p;
 }
 
+template <int U>
+int launch_umma(const GemvUmmaArgs& a, int smem, cudaStream_t st) {
+    static int configured[64] = {};                      // largest dynamic smem size set per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && configured[dev] < smem) {
+        if (cudaFuncSetAttribute(gemv_umma_kernel<U>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return fail(MSAQ_ERR_CUDA, "cannot reserve %d bytes of shared memory", smem);
+        configured[dev] = smem;
+    }
+    launch_chained(gemv_umma_kernel<U>, dim3(a.sch.grid), dim3(GU_THREADS), (size_t)smem, st, a);
+    count_launch();
+    return check_launch("gemv_umma");
+}
+
 int run_umma(const __nv_bfloat16* X, const int8_t* se, const uint8_t* up, const uint8_t* sh, void* Y, float* Yf,
-             int64_t M, int64_t OUT, int64_t NB, void* ws, cudaStream_t st) {
-    const UmmaPlan p = plan_umma(M, OUT, NB);
+             int64_t M, int64_t OUT, int64_t NB, int u, void* ws, cudaStream_t st) {
+    const UmmaPlan p = plan_umma(M, OUT, NB, u);
     uint8_t* base = static_cast<uint8_t*>(ws);
     int* status = reinterpret_cast<int*>(base + p.ctl_off);
     float* partial = reinterpret_cast<float*>(base + p.partial_off);
-    static int configured[64] = {};                      // largest dynamic smem size set per device
     for (int64_t m0 = 0; m0 < M; m0 += GU_MAX_N) {        // more than 128 rows: one launch pair per 128-row tile
         const int rows = (int)(M - m0 < GU_MAX_N ? M - m0 : GU_MAX_N);
         const int64_t threads = NB * ((rows + 7) / 8 * 8) * 4;
@@ -125,19 +141,10 @@ int run_umma(const __nv_bfloat16* X, const int8_t* se, const uint8_t* up, const 
         count_launch();
         if (int rc = check_launch("gemv_umma_xprep")) return rc;
         const GemvSchedule sch = p.sch;
-        const int smem = sch.stages * GU_STAGE + 2 * GU_ABUF_BYTES;
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (dev >= 0 && dev < 64 && configured[dev] < smem) {
-            if (cudaFuncSetAttribute(gemv_u4gs2_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-                cudaSuccess)
-                return fail(MSAQ_ERR_CUDA, "cannot reserve %d bytes of shared memory", smem);
-            configured[dev] = smem;
-        }
+        const int smem = sch.stages * gu_stage(u) + 2 * GU_ABUF_BYTES;
         GemvUmmaArgs a{se, up, sh, base, partial, status, static_cast<__nv_bfloat16*>(Y), Yf, (int)m0, rows, (int)OUT, sch};
-        launch_chained(gemv_u4gs2_umma_kernel, dim3(sch.grid), dim3(GU_THREADS), (size_t)smem, st, a);
-        count_launch();
-        if (int rc = check_launch("gemv_u4gs2_umma")) return rc;
+        const int rc = u == 4 ? launch_umma<4>(a, smem, st) : u == 3 ? launch_umma<3>(a, smem, st) : launch_umma<2>(a, smem, st);
+        if (rc) return rc;
         // every CTA boundary on a tile boundary: all tiles were written directly; otherwise some tile has partials
         if (!(sch.units() % sch.grid == 0 && (sch.units() / sch.grid) % sch.nb == 0)) {
             const int64_t quads = (int64_t)rows * (OUT / 4);
@@ -238,13 +245,15 @@ int gemv_dispatch(const void* X, const int8_t* se, const uint8_t* up, const uint
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
 
-    if (mma_usable(se, up, sh, ws, OUT, u, gs, cm)) {
-        // the tensor-memory epilogue stores 16 outputs at a time: Y (and Y_f32) must be 16-byte aligned for it
-        if (M >= GU_MIN_M && option_tensor_memory() &&
-            !((reinterpret_cast<uintptr_t>(Y) | reinterpret_cast<uintptr_t>(Yf)) & 15))
-            return run_umma(x, se, up, sh, Y, Yf, M, OUT, NB, ws, st);
+    const bool aligned = !((reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(sh) |
+                            reinterpret_cast<uintptr_t>(se) | reinterpret_cast<uintptr_t>(ws)) & 15);
+    // the tensor-memory epilogue stores 16 outputs at a time: Y (and Y_f32) must be 16-byte aligned for it
+    const bool tm_ok = aligned && umma_eligible(OUT, u, gs, cm) && option_tensor_memory() &&
+                       !((reinterpret_cast<uintptr_t>(Y) | reinterpret_cast<uintptr_t>(Yf)) & 15);
+    // u = 4 keeps up to eight rows on the integer-MMA kernel; the 5+3 and 6+2 bit formats have no such kernel
+    if (tm_ok && (u != 4 || M >= GU_MIN_M)) return run_umma(x, se, up, sh, Y, Yf, M, OUT, NB, u, ws, st);
+    if (mma_usable(se, up, sh, ws, OUT, u, gs, cm))
         return run_mma(x, Prologue{XP_PLAIN, nullptr, 0, nullptr, 0.0f}, se, up, sh, Y, Yf, M, OUT, NB, ws, st);
-    }
 
     return gemv_run_generic(x, se, up, sh, Y, Yf, M, OUT, NB, f, cm, ws, st);
 }
@@ -260,10 +269,10 @@ extern "C" size_t msaq_wonly_gemv_workspace(int64_t M, int64_t OUT, int64_t NB, 
     if (mma_eligible(OUT, u, gs, true)) {
         const size_t tuned = plan_mma(M, OUT, NB).total;
         if (tuned > bytes) bytes = tuned;
-        if (M >= GU_MIN_M) {
-            const size_t tm = plan_umma(M, OUT, NB).total;
-            if (tm > bytes) bytes = tm;
-        }
+    }
+    if (umma_eligible(OUT, u, gs, true) && (u != 4 || M >= GU_MIN_M)) {
+        const size_t tm = plan_umma(M, OUT, NB, u).total;
+        if (tm > bytes) bytes = tm;
     }
     return bytes;
 }

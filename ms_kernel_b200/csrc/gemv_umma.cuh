@@ -43,10 +43,12 @@ constexpr int GU_THREADS = (GU_DEC_WARPS + 2) * 32;
 constexpr int GU_MAX_N = 128;                      // activation rows per launch: the M of the MMA
 constexpr int GU_MAX_STAGES = 8;
 constexpr int GU_ABUF_BYTES = GU_TR * 64;          // one decoded A buffer: 512 rows x 32 bf16
-constexpr int GU_PACKED = GU_TR * 25;              // packed bytes of a unit
-
 constexpr int GU_XTILE = GU_MAX_N * 64;            // activation tile of a K block: 128 rows x 32 bf16
-constexpr int GU_STAGE = GU_PACKED + GU_XTILE;
+// gs = 2 formats: upper codes 4*(8-u) bytes, shared codes 2*u bytes, one scale byte per (row, block)
+__host__ __device__ constexpr int gu_ub(int u) { return 4 * (8 - u); }
+__host__ __device__ constexpr int gu_sb(int u) { return 2 * u; }
+__host__ __device__ constexpr int gu_packed(int u) { return GU_TR * (gu_ub(u) + gu_sb(u) + 1); }   // packed bytes of a unit
+__host__ __device__ constexpr int gu_stage(int u) { return gu_packed(u) + GU_XTILE; }
 constexpr int GU_TMEM_COLS = GU_TR;                // one fp32 accumulator column per weight row of the tile
 
 // ---- tcgen05 wrappers -----------------------------------------------------------
@@ -148,6 +150,115 @@ gemv_umma_xprep_kernel(const __nv_bfloat16* __restrict__ X, uint8_t* __restrict_
     *reinterpret_cast<uint4*>(xs + (int64_t)b * N * 64 + ((n >> 3) * 4 + c) * 128 + (n & 7) * 16) = v;
 }
 
+// ---- decode of one weight row's 32-block into bf16 ---------------------------------------
+// The row's 64 bytes go to `dst` + i*128, i = 0..3 (8-value chunks of the core-matrix layout).
+//
+// v = q * 2^e with q = up * 2^u + sh.  Flipping the sign bit of a two's-complement field makes it
+// offset binary, so (up_off << u) + sh_off = q + 128 + 2^(u-1) is a non-negative integer; added to
+// the bit pattern of 2^23 it reads as the float 2^23 + q + 128 + 2^(u-1), and one FMA removes the
+// offsets and applies the scale exactly.  q * 2^e has at most 8 significant bits, so the upper half
+// of the fp32 word is the bf16 value.
+template <int U>
+__device__ __forceinline__ void gu_decode_row(uint32_t st, int r, uint32_t dst);
+
+// u = 4: nibbles.  A nibble in the high half of a byte and the shared nibble in the low half form
+// the byte q + 136 with three logic ops per eight codes; a byte permute drops it into the mantissa.
+template <>
+__device__ __forceinline__ void gu_decode_row<4>(uint32_t st, int r, uint32_t dst) {
+    const uint4 w = lds128(st + r * 16);
+    const uint2 sh = lds64<0>(st + GU_TR * 16 + r * 8);
+    const int e = lds_s8<0>(st + GU_TR * 24 + r);
+    const float sc = __int_as_float(max(0, e + 127) << 23);
+    const float off = -8388744.0f * sc;
+    const uint32_t wx[4] = {w.x ^ 0x88888888u, w.y ^ 0x88888888u, w.z ^ 0x88888888u, w.w ^ 0x88888888u};
+    const uint32_t sx[2] = {sh.x ^ 0x88888888u, sh.y ^ 0x88888888u};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        // the four shared codes of elements 8i..8i+7 (two elements each), one per byte
+        const uint32_t s16 = (i & 1) ? (sx[i >> 1] >> 16) : sx[i >> 1];
+        const uint32_t t = prmt(s16, 0u, 0x1100u);
+        const uint32_t lo = and_or(t >> 4, 0x0F000F00u, t & 0x000F000Fu);
+        const uint32_t me = and_or(wx[i] << 4, 0xF0F0F0F0u, lo);      // elements 8i + 0, 2, 4, 6
+        const uint32_t mo = and_or(wx[i], 0xF0F0F0F0u, lo);           // elements 8i + 1, 3, 5, 7
+        uint32_t o[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const float fe = __uint_as_float(prmt(me, 0x4B000000u, 0x7650u + b));
+            const float fo = __uint_as_float(prmt(mo, 0x4B000000u, 0x7650u + b));
+            const float ve = fmaf(fe, sc, off), vo = fmaf(fo, sc, off);
+            o[b] = prmt(__float_as_uint(ve), __float_as_uint(vo), 0x7632u);
+        }
+        sts128(dst + i * 128, o[0], o[1], o[2], o[3]);
+    }
+}
+
+// Bits [32*i, 32*i+32) of the pattern that has the top bit of every `width`-bit field set.
+__host__ __device__ constexpr uint32_t gu_sign_pattern(int width, int i) {
+    uint32_t p = 0;
+    for (int b = width - 1; b < 32 * (i + 1); b += width)
+        if (b >= 32 * i) p |= 1u << (b - 32 * i);
+    return p;
+}
+
+// u = 3 (5-bit upper, 3-bit shared) and u = 2 (6-bit, 2-bit): fields cut out of the dense bit runs
+// with funnel shifts.
+template <int U>
+__device__ __forceinline__ void gu_decode_row(uint32_t st, int r, uint32_t dst) {
+    constexpr int WB = 8 - U, NW = WB;                          // field width, words of the upper run
+    constexpr uint32_t UM = (1u << WB) - 1u, SM = (1u << U) - 1u;
+    uint32_t w[NW + 1];
+    if (U == 3) {
+#pragma unroll
+        for (int i = 0; i < NW; ++i) w[i] = lds32<0>(st + r * 20 + i * 4);
+    } else {
+#pragma unroll
+        for (int i = 0; i < NW; i += 2) {
+            const uint2 v = lds64<0>(st + r * 24 + i * 4);
+            w[i] = v.x;
+            w[i + 1] = v.y;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NW; ++i) w[i] ^= gu_sign_pattern(WB, i);
+    w[NW] = 0u;
+    uint32_t s0, s1 = 0u;                                       // shared run: 16 fields of U bits
+    const uint32_t sbase = st + GU_TR * gu_ub(U) + r * gu_sb(U);
+    if (U == 2) {
+        s0 = lds32<0>(sbase);
+    } else {
+        uint32_t a, b, c;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(a) : "r"(sbase));
+        asm volatile("ld.shared.u16 %0, [%1+2];" : "=r"(b) : "r"(sbase));
+        asm volatile("ld.shared.u16 %0, [%1+4];" : "=r"(c) : "r"(sbase));
+        s0 = a | (b << 16);
+        s1 = c;
+    }
+    s0 ^= gu_sign_pattern(U, 0);
+    s1 ^= gu_sign_pattern(U, 1) & 0xFFFFu;
+    const int e = lds_s8<0>(st + GU_TR * (gu_ub(U) + gu_sb(U)) + r);
+    const float sc = __int_as_float(max(0, e + 127) << 23);
+    const float off = -(8388608.0f + 128.0f + (float)(1 << (U - 1))) * sc;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t o[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int g = 4 * i + b, ps = g * U;                  // group: elements 2g, 2g+1
+            const uint32_t sf = (ps + U <= 32) ? (s0 >> ps) : (ps >= 32 ? (s1 >> (ps - 32)) : __funnelshift_r(s0, s1, ps));
+            const uint32_t shm = and_or(sf, SM, 0x4B000000u);     // shared code on top of the bits of 2^23
+            float v[2];
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                const int pk = (2 * g + t) * WB, wi = pk >> 5, po = pk & 31;
+                const uint32_t uf = (po + WB <= 32) ? (w[wi] >> po) : __funnelshift_r(w[wi], w[wi + 1], po);
+                v[t] = fmaf(__uint_as_float(((uf & UM) << U) + shm), sc, off);
+            }
+            o[b] = prmt(__float_as_uint(v[0]), __float_as_uint(v[1]), 0x7632u);
+        }
+        sts128(dst + i * 128, o[0], o[1], o[2], o[3]);
+    }
+}
+
 // ---- main kernel --------------------------------------------------------------------
 struct GemvUmmaArgs {
     const int8_t* scale_exp;
@@ -164,8 +275,10 @@ struct GemvUmmaArgs {
 };
 
 
+template <int U>
 __global__ void __launch_bounds__(GU_THREADS, 1)
-gemv_u4gs2_umma_kernel(const GemvUmmaArgs a) {
+gemv_umma_kernel(const GemvUmmaArgs a) {
+    constexpr int GU_PACKED = gu_packed(U);
     extern __shared__ __align__(128) uint8_t gu_smem[];
     __shared__ __align__(8) uint64_t bar_full[GU_MAX_STAGES];     // packed unit + activation tile landed (TMA)
     __shared__ __align__(8) uint64_t bar_empty[GU_MAX_STAGES];    // the owning team's 8 warps passed the stage on (its MMAs are done)
@@ -180,7 +293,7 @@ gemv_u4gs2_umma_kernel(const GemvUmmaArgs a) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const GemvSchedule sch = a.sch;
     const int stages = sch.stages;
-    constexpr int STAGE = GU_STAGE;
+    constexpr int STAGE = gu_stage(U);
     const uint32_t smem0 = smem_u32(gu_smem);
     const uint32_t abuf0 = smem0 + stages * STAGE;                 // two decoded weight buffers behind the ring
     constexpr uint32_t tmem_cols = GU_TMEM_COLS;
@@ -235,10 +348,10 @@ gemv_u4gs2_umma_kernel(const GemvUmmaArgs a) {
                 const uint32_t bar = smem_u32(&bar_full[s]);
                 const uint32_t base = smem0 + s * STAGE;
                 const int64_t col = (int64_t)blk * a.OUT + o0;
-                mbar_expect_tx(bar, (uint32_t)(cv * 25 + xbytes));
-                bulk_g2s(base, a.upper_cm + col * 16, (uint32_t)cv * 16, bar);
-                bulk_g2s(base + GU_TR * 16, a.shared_cm + col * 8, (uint32_t)cv * 8, bar);
-                bulk_g2s(base + GU_TR * 24, a.scale_exp + col, (uint32_t)cv, bar);
+                mbar_expect_tx(bar, (uint32_t)(cv * (gu_ub(U) + gu_sb(U) + 1) + xbytes));
+                bulk_g2s(base, a.upper_cm + col * gu_ub(U), (uint32_t)cv * gu_ub(U), bar);
+                bulk_g2s(base + GU_TR * gu_ub(U), a.shared_cm + col * gu_sb(U), (uint32_t)cv * gu_sb(U), bar);
+                bulk_g2s(base + GU_TR * (gu_ub(U) + gu_sb(U)), a.scale_exp + col, (uint32_t)cv, bar);
                 bulk_g2s(base + GU_PACKED, a.xs + (int64_t)blk * xbytes, (uint32_t)xbytes, bar);
                 if (++blk == sch.nb) { blk = 0; ++c; }
                 if (++s == stages) { s = 0; ph ^= 1u; }
@@ -389,36 +502,7 @@ gemv_u4gs2_umma_kernel(const GemvUmmaArgs a) {
 #pragma unroll 1
                 for (int half = 0; half < 2; ++half) {
                     const int r = tt + half * 256;                 // weight row within the tile
-                    const uint4 w = lds128(st + r * 16);
-                    const uint2 sh = lds64<0>(st + GU_TR * 16 + r * 8);
-                    const int e = lds_s8<0>(st + GU_TR * 24 + r);
-                    // v = q * 2^e with q = 16*up + sh: xor 0x88 turns both two's-complement nibbles into
-                    // offset binary, so the byte is q + 136; placed in the mantissa of 2^23 it reads
-                    // 2^23 + q + 136, and one FMA removes the offsets and applies the scale, exactly.
-                    const float sc = __int_as_float(max(0, e + 127) << 23);
-                    const float off = -8388744.0f * sc;
-                    const uint32_t wx[4] = {w.x ^ 0x88888888u, w.y ^ 0x88888888u, w.z ^ 0x88888888u, w.w ^ 0x88888888u};
-                    const uint32_t sx[2] = {sh.x ^ 0x88888888u, sh.y ^ 0x88888888u};
-                    const uint32_t dst = abuf0 + buf * GU_ABUF_BYTES + (r >> 3) * 512 + (r & 7) * 16;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        // the four shared codes of elements 8i..8i+7 (two elements each), one per byte
-                        const uint32_t s16 = (i & 1) ? (sx[i >> 1] >> 16) : sx[i >> 1];
-                        const uint32_t t = prmt(s16, 0u, 0x1100u);
-                        const uint32_t lo = and_or(t >> 4, 0x0F000F00u, t & 0x000F000Fu);
-                        const uint32_t me = and_or(wx[i] << 4, 0xF0F0F0F0u, lo);      // elements 8i + 0, 2, 4, 6
-                        const uint32_t mo = and_or(wx[i], 0xF0F0F0F0u, lo);           // elements 8i + 1, 3, 5, 7
-                        uint32_t o[4];
-#pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            const float fe = __uint_as_float(prmt(me, 0x4B000000u, 0x7650u + b));
-                            const float fo = __uint_as_float(prmt(mo, 0x4B000000u, 0x7650u + b));
-                            const float ve = fmaf(fe, sc, off), vo = fmaf(fo, sc, off);
-                            // q * 2^e has at most 7 significant bits: the upper half of the fp32 word is the bf16 value
-                            o[b] = prmt(__float_as_uint(ve), __float_as_uint(vo), 0x7632u);
-                        }
-                        sts128(dst + i * 128, o[0], o[1], o[2], o[3]);
-                    }
+                    gu_decode_row<U>(st, r, abuf0 + buf * GU_ABUF_BYTES + (r >> 3) * 512 + (r & 7) * 16);
                 }
                 fence_async_smem();                               // the tensor core reads the buffer through the async proxy
             }

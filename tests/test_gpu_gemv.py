@@ -76,6 +76,31 @@ def test_gemv_batched_tensor_memory_path(rng, M, OUT, K):
     assert orc.rel_fro(gotf, gotf2) < 1e-4
 
 
+@pytest.mark.parametrize("u", (2, 3))
+@pytest.mark.parametrize("M,OUT,K", [(1, 512, 256), (1, 1040, 2048), (4, 2048, 1024), (17, 528, 1024), (64, 2048, 4096),
+                                     (130, 400, 256)])
+def test_gemv_u2_u3_tensor_memory_path(rng, u, M, OUT, K):
+    """The 5+3 and 6+2 bit formats (gs = 2) run on the tensor-memory kernel at every batch size: bit fields
+    that straddle words, ragged tiles, split-K, several row tiles -- against the oracle, and against the
+    generic kernel with the option off."""
+    import cabi
+    from ms_kernel_b200 import _lib
+    W, X, p = _case(rng, OUT, K, u, 2, M=M)
+    pd = cabi.planes_to_dev(p)
+    ref = orc.wonly_matmul(p, X)
+    kind = "batched" if M > 1 else "wide"
+    xin = cabi.bf16_dev(X if M > 1 else X[0])
+    got, gotf = cabi.gemv(kind, xin, pd, M=M) if M > 1 else cabi.gemv(kind, xin, pd)
+    _check(got, gotf, ref if M > 1 else ref[0])
+    L = _lib.lib()
+    assert L.msaq_set_option(2, 0) == 0
+    try:
+        got2, gotf2 = cabi.gemv(kind, xin, pd, M=M) if M > 1 else cabi.gemv(kind, xin, pd)
+    finally:
+        L.msaq_set_option(2, 1)
+    assert orc.rel_fro(gotf, gotf2) < 1e-4
+
+
 @pytest.mark.parametrize("u", (2, 3, 4))
 def test_gemv_llama_shape_vs_oracle(rng, u):
     """One full Llama-3.1-8B projection (O: 4096x4096) at gs=2, packed on the device."""
