@@ -38,8 +38,9 @@ namespace msaq {
 constexpr int GU_TR = 512;                         // weight rows per tile
 constexpr int GU_DEC_WARPS = 16;                   // one thread per weight row
 constexpr int GU_WARP_TMA = GU_DEC_WARPS;          // warp 16: TMA producer
-constexpr int GU_WARP_MMA = GU_DEC_WARPS + 1;      // warp 17: tensor-memory owner and MMA issuer
-constexpr int GU_THREADS = (GU_DEC_WARPS + 2) * 32;
+constexpr int GU_WARP_MMA = GU_DEC_WARPS + 1;      // warps 17, 18: MMA issuers (17 also owns the tensor-memory allocation)
+constexpr int GU_ISSUERS = 2;                      // issuer g accumulates weight rows 256g..256g+255 (columns 256g.. of tensor memory)
+constexpr int GU_THREADS = (GU_DEC_WARPS + 1 + GU_ISSUERS) * 32;
 constexpr int GU_MAX_N = 128;                      // activation rows per launch: the M of the MMA
 constexpr int GU_MAX_STAGES = 8;
 constexpr int GU_ABUF_BYTES = GU_TR * 64;          // one decoded A buffer: 512 rows x 32 bf16
@@ -283,8 +284,8 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
     __shared__ __align__(8) uint64_t bar_full[GU_MAX_STAGES];     // packed unit + activation tile landed (TMA)
     __shared__ __align__(8) uint64_t bar_empty[GU_MAX_STAGES];    // the owning team's 8 warps passed the stage on (its MMAs are done)
     __shared__ __align__(8) uint64_t bar_afull[2];                // decoded weight buffer written (the 8 warps of its team)
-    __shared__ __align__(8) uint64_t bar_aempty[2];               // MMAs that read the A buffer completed (commit)
-    __shared__ __align__(8) uint64_t bar_accfull;                 // the tile's last MMA completed (commit)
+    __shared__ __align__(8) uint64_t bar_aempty[2];               // MMAs that read the buffer completed (one commit per issuer)
+    __shared__ __align__(8) uint64_t bar_accfull;                 // the tile's last MMAs completed (one commit per issuer)
     __shared__ __align__(8) uint64_t bar_accempty;                // 16 warps have read the accumulators
     __shared__ __align__(8) uint64_t bar_done;                    // teardown: every MMA issued has completed
     __shared__ uint32_t tmem_slot;
@@ -315,11 +316,11 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
         }
         for (int j = 0; j < 2; ++j) {
             mbar_init(smem_u32(&bar_afull[j]), GU_DEC_WARPS / 2);
-            mbar_init(smem_u32(&bar_aempty[j]), 1);
+            mbar_init(smem_u32(&bar_aempty[j]), GU_ISSUERS);
         }
-        mbar_init(smem_u32(&bar_accfull), 1);
+        mbar_init(smem_u32(&bar_accfull), GU_ISSUERS);
         mbar_init(smem_u32(&bar_accempty), GU_DEC_WARPS);
-        mbar_init(smem_u32(&bar_done), 1);
+        mbar_init(smem_u32(&bar_done), GU_ISSUERS);
         abort_flag = 0;
         mbar_init_fence();
     }
@@ -357,8 +358,11 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
                 if (++s == stages) { s = 0; ph ^= 1u; }
             }
         }
-    } else if (warp == GU_WARP_MMA) {
-        // --------------------------------- MMA issuer ---------------------------------
+    } else if (warp >= GU_WARP_MMA) {
+        // -------------------------------- MMA issuers --------------------------------
+        // Two threads in two warps, each with its own half of the accumulator columns: one thread's
+        // barrier polling and commit latency overlaps the other's MMAs.
+        const int g = warp - GU_WARP_MMA;                          // this issuer's 256 weight rows of every unit
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_bf16(256), desc_hi = umma_desc_hi(512);
             int c = c_first, blk = blk_first, s = 0;
@@ -381,14 +385,11 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
                 const int cv = min(GU_TR, a.OUT - c * GU_TR);
                 const uint32_t w_lo = umma_desc_lo(abuf0 + buf * GU_ABUF_BYTES, 128);     // B operand: decoded weights
                 const uint32_t x_lo = umma_desc_lo(smem0 + s * STAGE + GU_PACKED, 128);   // A operand: activation tile
+                if (g * 256 < cv) {
 #pragma unroll
-                for (int g = 0; g < 2; ++g) {                      // 256 weight rows = 256 accumulator columns each
-                    if (g * 256 < cv) {
-#pragma unroll
-                        for (int ks = 0; ks < 2; ++ks)
-                            umma_f16(tmem_base + g * 256, x_lo + ((ks * 256) >> 4), w_lo + ((g * (256 * 64) + ks * 256) >> 4),
-                                     desc_hi, idesc, (fresh && ks == 0) ? 0u : 1u);
-                    }
+                    for (int ks = 0; ks < 2; ++ks)
+                        umma_f16(tmem_base + g * 256, x_lo + ((ks * 256) >> 4), w_lo + ((g * (256 * 64) + ks * 256) >> 4),
+                                 desc_hi, idesc, (fresh && ks == 0) ? 0u : 1u);
                 }
                 fresh = false;
                 tc_commit(smem_u32(&bar_aempty[buf]));            // the decoders may overwrite this A buffer, and
@@ -518,12 +519,9 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
     // ---- teardown: nothing may still be writing tensor memory when it is returned ----
     tc_fence_before();
     __syncthreads();
+    if (warp >= GU_WARP_MMA && lane == 0) tc_commit(smem_u32(&bar_done));   // arrives once this issuer's MMAs have completed
     if (warp == GU_WARP_MMA) {
-        if (lane == 0) {
-            // all MMAs this thread issued have completed once a fresh commit arrives
-            tc_commit(smem_u32(&bar_done));
-            if (!mbar_wait_bounded(smem_u32(&bar_done), 0)) atomicExch(a.status, 1);
-        }
+        if (lane == 0 && !mbar_wait_bounded(smem_u32(&bar_done), 0)) atomicExch(a.status, 1);
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, tmem_cols);

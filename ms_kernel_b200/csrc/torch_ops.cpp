@@ -86,10 +86,31 @@ Tensor gemv_common(const Tensor& x, const Tensor& s, const Tensor& up, const Ten
     return y;
 }
 
+// The batched GEMV with its fp32 result (before the bf16 rounding): what a K-sharded linear hands to the all-reduce.
+Tensor wonly_gemv_batched_f32(const Tensor& x, const Tensor& s, const Tensor& up, const Tensor& sh, int64_t M, int64_t OUT,
+                              int64_t NB, int64_t u, int64_t gs) {
+    check_act(x, "x");
+    int64_t UB, SB;
+    fmt_sizes(u, gs, &UB, &SB);
+    TORCH_CHECK(M >= 1 && OUT >= 1 && NB >= 1, "M, OUT and NB must be positive");
+    TORCH_CHECK(x.numel() == M * NB * 32, "x has ", x.numel(), " elements, expected M*K = ", M * NB * 32);
+    check_planes(s, up, sh, x, NB * OUT, UB, SB);
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor y = at::empty({M, OUT}, x.options());
+    Tensor yf = at::empty({M, OUT}, x.options().dtype(at::kFloat));
+    const size_t wsb = msaq_wonly_gemv_workspace(M, OUT, NB, (int)u, (int)gs);
+    Tensor ws = workspace(x, wsb);
+    check_rc(msaq_wonly_gemv_batched(x.data_ptr(), s.data_ptr<int8_t>(), up.data_ptr<uint8_t>(), sh.data_ptr<uint8_t>(),
+                                     y.data_ptr(), yf.data_ptr<float>(), M, OUT, NB, (int)u, (int)gs, ws.data_ptr(), wsb,
+                                     stream_of(x)),
+             "wonly_gemv_batched_f32");
+    return yf;
+}
+
 // y (and, for the add+rmsnorm prologue, the new residual stream) of a GEMV whose preceding glue is fused in.
 std::vector<Tensor> wonly_gemv_fused(const Tensor& x, const c10::optional<Tensor>& addend, int64_t prologue, double eps,
                                      const Tensor& s, const Tensor& up, const Tensor& sh, int64_t M, int64_t OUT,
-                                     int64_t NB, int64_t u, int64_t gs) {
+                                     int64_t NB, int64_t u, int64_t gs, bool out_f32) {
     check_act(x, "x");
     int64_t UB, SB;
     fmt_sizes(u, gs, &UB, &SB);
@@ -111,15 +132,18 @@ std::vector<Tensor> wonly_gemv_fused(const Tensor& x, const c10::optional<Tensor
         h_out = at::empty({M, K}, x.options());
     }
     Tensor y = at::empty({M, OUT}, x.options());
+    Tensor yf;
+    if (out_f32) yf = at::empty({M, OUT}, x.options().dtype(at::kFloat));
     const size_t wsb = msaq_wonly_gemv_fused_workspace(M, OUT, NB, (int)u, (int)gs);
     Tensor ws = workspace(x, wsb);
     check_rc(msaq_wonly_gemv_fused(x.data_ptr(), (int)prologue, ad, ad_f32, (float)eps,
                                    h_out.defined() ? h_out.data_ptr() : nullptr, s.data_ptr<int8_t>(),
-                                   up.data_ptr<uint8_t>(), sh.data_ptr<uint8_t>(), y.data_ptr(), nullptr, M, OUT, NB,
-                                   (int)u, (int)gs, ws.data_ptr(), wsb, stream_of(x)),
+                                   up.data_ptr<uint8_t>(), sh.data_ptr<uint8_t>(), y.data_ptr(),
+                                   out_f32 ? yf.data_ptr<float>() : nullptr, M, OUT, NB, (int)u, (int)gs, ws.data_ptr(), wsb,
+                                   stream_of(x)),
              "wonly_gemv_fused");
-    if (h_out.defined()) return {y, h_out};
-    return {y};
+    if (h_out.defined()) return {out_f32 ? yf : y, h_out};
+    return {out_f32 ? yf : y};
 }
 
 Tensor wonly_gemv(const Tensor& x, const Tensor& s, const Tensor& up, const Tensor& sh, int64_t OUT, int64_t NB,
@@ -377,7 +401,9 @@ TORCH_LIBRARY(msaq, m) {
           "int B, int H, int Hkv, int Lk, int D, int NB, int u, int gs, int Lcap, bool qrot) -> Tensor",
           &kv_decode_attention_varlen);
     m.def("wonly_gemv_fused(Tensor x, Tensor? addend, int prologue, float eps, Tensor scale_exp, Tensor upper_cm, "
-          "Tensor shared_cm, int M, int OUT, int NB, int u, int gs) -> Tensor[]", &wonly_gemv_fused);
+          "Tensor shared_cm, int M, int OUT, int NB, int u, int gs, bool out_f32=False) -> Tensor[]", &wonly_gemv_fused);
+    m.def("wonly_gemv_batched_f32(Tensor x, Tensor scale_exp, Tensor upper_cm, Tensor shared_cm, "
+          "int M, int OUT, int NB, int u, int gs) -> Tensor", &wonly_gemv_batched_f32);
     m.def("pack_weight(Tensor W, int u, int gs) -> Tensor[]", &pack_weight);
     m.def("rmsnorm(Tensor x, float eps) -> Tensor", &rmsnorm);
     m.def("silu_mul(Tensor gate_up) -> Tensor", &silu_mul);

@@ -118,15 +118,23 @@ class PackedLinear:
                                        int(x.shape[0]), self.OUT, self.nb, self.u, self.gs)
 
 
-    def fwd_fused(self, x, prologue, addend=None, eps=1e-5):
+    def fwd_f32(self, x):
+        """x [M,K] bf16 -> [M,OUT] fp32, the result before its bf16 rounding (the partial sum a
+        K-sharded linear contributes to an all-reduce)."""
+        x = x.reshape(-1, self.K)
+        return _OPS.wonly_gemv_batched_f32(x.contiguous(), self.scale_exp, self.upper_cm, self.shared_cm,
+                                           int(x.shape[0]), self.OUT, self.nb, self.u, self.gs)
+
+    def fwd_fused(self, x, prologue, addend=None, eps=1e-5, out_f32=False):
         """The GEMV with the layer glue in front of it done by the activation-staging kernel.
 
         prologue: PRO_RMSNORM (x [M,K]), PRO_SILU_MUL (x [M,2K] = gate | up) or PRO_ADD_RMSNORM
-        (x [M,K] + addend [M,K] fp32/bf16).  Returns y [M,OUT]; for PRO_ADD_RMSNORM (y, x + addend)."""
+        (x [M,K] + addend [M,K] fp32/bf16).  Returns y [M,OUT] (fp32 before rounding with out_f32, else
+        bf16); for PRO_ADD_RMSNORM (y, x + addend)."""
         M = int(x.shape[0])
         out = _OPS.wonly_gemv_fused(x.contiguous(), None if addend is None else addend.contiguous(), int(prologue),
                                     float(eps), self.scale_exp, self.upper_cm, self.shared_cm, M, self.OUT, self.nb,
-                                    self.u, self.gs)
+                                    self.u, self.gs, bool(out_f32))
         return (out[0], out[1]) if prologue == PRO_ADD_RMSNORM else out[0]
 
 

@@ -176,6 +176,15 @@ class DecoderLayerTP:
             return f.silu_mul(gu.contiguous())
         return (torch.nn.functional.silu(gu[:, :F].float()) * gu[:, F:].float()).to(gu.dtype)
 
+    def _partial(self, lin, x):
+        """A K-sharded linear's contribution: fp32 when it goes into an all-reduce (straight from the
+        kernel where the linear offers it), the plain bf16 result on one rank."""
+        if self.world == 1:
+            return lin.fwd(x)
+        if hasattr(lin, "fwd_f32"):
+            return lin.fwd_f32(x)
+        return lin.fwd(x).float()
+
     def step(self, h, pos, Lk, seq_lens=None):
         """h [B, hidden] bf16 (replicated on every rank) -> new h [B, hidden] bf16 (replicated).
 
@@ -197,16 +206,16 @@ class DecoderLayerTP:
         v = qkv[:, (self.q_heads + self.kv_heads) * d:].reshape(B, self.kv_heads, d)
         self.cache.append(k, v, pos)
         a = self.cache.attend(q.contiguous(), Lk, seq_lens)            # [B, q, d], heads local
-        o = self.lin["o"].fwd(a.reshape(B, self.q_heads * d))          # partial over the local K range
-        o = self.all_reduce(o.float()) if self.world > 1 else o
+        o = self._partial(self.lin["o"], a.reshape(B, self.q_heads * d))   # partial over the local K range
+        o = self.all_reduce(o) if self.world > 1 else o
         if fused:
             gu, h = self.lin["gate_up"].fwd_fused(h, 3, o, self.eps)   # h + o, rmsnorm inside
-            dn = self.lin["down"].fwd_fused(gu, 2)                     # SiLU(gate) * up inside
+            dn = self.lin["down"].fwd_fused(gu, 2, None, self.eps, self.world > 1)   # SiLU(gate) * up inside; fp32 partial for the all-reduce
         else:
             h = self._add(h, o)
             gu = self.lin["gate_up"].fwd(self._rmsnorm(h, self.eps))   # [B, 2 * ffn_rows]
-            dn = self.lin["down"].fwd(self._silu_mul(gu, self.ffn_rows))
-        dn = self.all_reduce(dn.float()) if self.world > 1 else dn
+            dn = self._partial(self.lin["down"], self._silu_mul(gu, self.ffn_rows))
+        dn = self.all_reduce(dn) if self.world > 1 else dn
         return self._add(h, dn)
 
     # ---- bookkeeping for the benchmark --------------------------------------

@@ -135,3 +135,19 @@ def test_layer_step_matches_float64_restatement(rng, B):
     assert orc.rel_fro(got - h, ref - h) < 2e-2
     assert orc.rel_fro(got, ref) < 4 * REL_FRO_TOL
     assert np.isfinite(got).all()
+
+
+@pytest.mark.parametrize("M", [1, 5, 20])
+def test_fp32_partial_outputs_round_to_the_bf16_outputs(rng, M):
+    """K-sharded linears hand their fp32 result to the all-reduce: it must be the value the bf16 output rounds."""
+    from ms_kernel_b200 import ops
+    OUT, K = 256, 512
+    lin = ops.PackedLinear(orc.pack_weight((rng.standard_normal((OUT, K)) * 0.05).astype(np.float32), 4, 2), "cuda")
+    x = _bf(rng.standard_normal((M, K)))
+    y32 = lin.fwd_f32(x)
+    assert y32.dtype == torch.float32 and tuple(y32.shape) == (M, OUT)
+    assert torch.equal(y32.to(torch.bfloat16), lin.fwd(x).reshape(M, OUT))
+    gu = _bf(rng.standard_normal((M, 2 * K)))
+    f32 = lin.fwd_fused(gu, ops.PRO_SILU_MUL, out_f32=True)
+    assert f32.dtype == torch.float32
+    assert torch.equal(f32.to(torch.bfloat16), lin.fwd_fused(gu, ops.PRO_SILU_MUL))
