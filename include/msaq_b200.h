@@ -176,6 +176,17 @@ int msaq_kv_append_varlen(const void* X, int8_t* scale_exp, uint8_t* upper, uint
                           int64_t Lcap, int u, int gs, int rotate, void* stream);
 
 /*
+ * K and V rows of one decode step in one launch (no reference counterpart: the reference issues kv_append_rot for
+ * K and kv_append for V, tests/harness_batchsweep.py:170-180).  Xk, Xv [B*Hkv][D] bf16; planes [B*Hkv][NB][Lcap][*];
+ * slot `pos` for every sequence, or pos_per_seq[b] when that pointer is given; K is rotated when rotate_k != 0.
+ * Bytes written are those of msaq_kv_append_rot / msaq_kv_append.
+ */
+int msaq_kv_append_pair(const void* Xk, const void* Xv, int8_t* k_scale_exp, uint8_t* k_upper, uint8_t* k_shared,
+                        int8_t* v_scale_exp, uint8_t* v_upper, uint8_t* v_shared,
+                        int64_t B, int64_t Hkv, int64_t D, int64_t NB, int64_t pos, const int32_t* pos_per_seq,
+                        int64_t Lcap, int u, int gs, int rotate_k, void* stream);
+
+/*
  * Prefill pack: X[H,L,D] (bf16) -> slots [key0, key0+L) of planes with key
  * stride Lcap (Lcap = L, key0 = 0 gives the reference's freshly allocated
  * planes).  rotate != 0 applies the Hadamard rotation to every row first.

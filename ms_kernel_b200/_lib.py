@@ -31,6 +31,8 @@ SIGNATURES = {
     "msaq_kv_append": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _int, _int, _p]),
     "msaq_kv_append_rot": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _int, _int, _p]),
     "msaq_kv_append_varlen": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _p, _i64, _int, _int, _int, _p]),
+    "msaq_kv_append_pair": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p, _i64, _int, _int,
+                                   _int, _p]),
     "msaq_kv_write": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _p]),
     "msaq_hadamard_rotate": (_int, [_p, _p, _i64, _i64, _p]),
     "msaq_pack_weight": (_int, [_p, _int, _p, _p, _p, _p, _p, _i64, _i64, _int, _int, _p]),

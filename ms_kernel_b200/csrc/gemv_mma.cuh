@@ -120,12 +120,21 @@ gemv_xprep_kernel(const XprepArgs a) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) { f[2 * j] = bf16_lo(w[j]); f[2 * j + 1] = bf16_hi(w[j]); }
                     if (MODE == XP_ADD_NORM) {
+                        const int64_t o = (int64_t)mr * K + i * 8;        // 16-byte aligned: the launcher checks the bases
+                        float d[8];
+                        if (a.r_is_f32) {
+                            const float4 d0 = *reinterpret_cast<const float4*>(Rf + o);
+                            const float4 d1 = *reinterpret_cast<const float4*>(Rf + o + 4);
+                            d[0] = d0.x; d[1] = d0.y; d[2] = d0.z; d[3] = d0.w;
+                            d[4] = d1.x; d[5] = d1.y; d[6] = d1.z; d[7] = d1.w;
+                        } else {
+                            const uint4 dv = *reinterpret_cast<const uint4*>(Rh + o);
+                            const uint32_t dw[4] = {dv.x, dv.y, dv.z, dv.w};
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const int64_t o = (int64_t)mr * K + i * 8 + j;
-                            const float d = a.r_is_f32 ? Rf[o] : __bfloat162float(Rh[o]);
-                            f[j] = __bfloat162float(__float2bfloat16_rn(f[j] + d));
+                            for (int j = 0; j < 4; ++j) { d[2 * j] = bf16_lo(dw[j]); d[2 * j + 1] = bf16_hi(dw[j]); }
                         }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(__float2bfloat16_rn(f[j] + d[j]));
                     }
 #pragma unroll
                     for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);

@@ -26,13 +26,28 @@ struct RowMap {
 // 2^k as a double, k in [-1022, 1023].
 __device__ __forceinline__ double pow2d(int k) { return __hiloint2double((1023 + k) << 20, 0); }
 
-template <int EPL, bool ROT>
+// One tensor to quantise into one set of planes; blockIdx.y picks the job, so the K (rotated) and
+// V rows of a decode step go out in a single launch.
+struct QuantJob {
+    const __nv_bfloat16* X;
+    int8_t* scale_exp;
+    uint8_t* upper;
+    uint8_t* shared;
+    int rot;
+};
+struct QuantJobs { QuantJob j[2]; };
+
+template <int EPL>
 __global__ void __launch_bounds__(ROWS_PER_CTA * 32)
-quantize_rows_kernel(const __nv_bfloat16* __restrict__ X, int8_t* __restrict__ scale_exp,
-                     uint8_t* __restrict__ upper, uint8_t* __restrict__ shared,
-                     RowMap map, Fmt f) {
+quantize_rows_kernel(const QuantJobs jobs, RowMap map, Fmt f) {
     chain_release();
     chain_wait();
+    const QuantJob job = jobs.j[blockIdx.y];
+    const __nv_bfloat16* __restrict__ X = job.X;
+    int8_t* __restrict__ scale_exp = job.scale_exp;
+    uint8_t* __restrict__ upper = job.upper;
+    uint8_t* __restrict__ shared = job.shared;
+    const bool ROT = job.rot != 0;
     constexpr int D = 32 * EPL, NB = EPL;
     constexpr int CW = 12;                                   // code words per block: 7 of upper codes, then shared codes
     __shared__ float rowbuf[ROWS_PER_CTA][D];
@@ -173,35 +188,39 @@ pack_weight_kernel(const void* __restrict__ W, int w_is_bf16, int8_t* __restrict
     }
 }
 
-template <bool ROT>
-int launch_rows(const void* X, int8_t* se, uint8_t* up, uint8_t* sh, const RowMap& map, int64_t D,
-                const Fmt& f, cudaStream_t st) {
+int launch_rows(const QuantJobs& jobs, int n_jobs, const RowMap& map, int64_t D, const Fmt& f, cudaStream_t st) {
     if (map.rows == 0) return MSAQ_OK;
-    const unsigned grid = (unsigned)((map.rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA);
-    const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
+    const dim3 grid((unsigned)((map.rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA), (unsigned)n_jobs);
+    const dim3 block(ROWS_PER_CTA * 32);
     switch (D) {
-        case 32:  launch_chained(quantize_rows_kernel<1, ROT>, dim3(grid), dim3(ROWS_PER_CTA * 32), 0, st, x, se, up, sh, map, f); break;
-        case 64:  launch_chained(quantize_rows_kernel<2, ROT>, dim3(grid), dim3(ROWS_PER_CTA * 32), 0, st, x, se, up, sh, map, f); break;
-        case 128: launch_chained(quantize_rows_kernel<4, ROT>, dim3(grid), dim3(ROWS_PER_CTA * 32), 0, st, x, se, up, sh, map, f); break;
-        case 256: launch_chained(quantize_rows_kernel<8, ROT>, dim3(grid), dim3(ROWS_PER_CTA * 32), 0, st, x, se, up, sh, map, f); break;
+        case 32:  launch_chained(quantize_rows_kernel<1>, grid, block, 0, st, jobs, map, f); break;
+        case 64:  launch_chained(quantize_rows_kernel<2>, grid, block, 0, st, jobs, map, f); break;
+        case 128: launch_chained(quantize_rows_kernel<4>, grid, block, 0, st, jobs, map, f); break;
+        case 256: launch_chained(quantize_rows_kernel<8>, grid, block, 0, st, jobs, map, f); break;
         default: return fail(MSAQ_ERR_UNSUPPORTED, "head_dim %lld: must be 32, 64, 128 or 256", (long long)D);
     }
     count_launch();
     return check_launch("quantize_rows");
 }
 
-int quantize_rows(const void* X, int8_t* se, uint8_t* up, uint8_t* sh, const RowMap& map, int64_t D,
-                  int64_t NB, int u, int gs, bool rot, void* stream) {
-    Fmt f;
-    if (!make_fmt(u, gs, &f)) return fail(MSAQ_ERR_UNSUPPORTED, "unsupported format u=%d gs=%d", u, gs);
-    if (!X || !se || !up || !sh) return fail(MSAQ_ERR_ARG, "null pointer");
+int check_rows(const RowMap& map, int64_t D, int64_t NB, int u, int gs, Fmt* f) {
+    if (!make_fmt(u, gs, f)) return fail(MSAQ_ERR_UNSUPPORTED, "unsupported format u=%d gs=%d", u, gs);
     if (NB * BLOCK != D) return fail(MSAQ_ERR_ARG, "NB (%lld) must equal D/32 (D=%lld)", (long long)NB, (long long)D);
     if (map.rows < 0 || map.Lcap <= 0) return fail(MSAQ_ERR_ARG, "bad row count or capacity");
     if (!map.pos && (map.key0 < 0 || map.key0 + map.rows_per_head > map.Lcap))
         return fail(MSAQ_ERR_ARG, "slots [%lld, %lld) exceed the cache capacity %lld", (long long)map.key0,
                     (long long)(map.key0 + map.rows_per_head), (long long)map.Lcap);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return rot ? launch_rows<true>(X, se, up, sh, map, D, f, st) : launch_rows<false>(X, se, up, sh, map, D, f, st);
+    return MSAQ_OK;
+}
+
+int quantize_rows(const void* X, int8_t* se, uint8_t* up, uint8_t* sh, const RowMap& map, int64_t D,
+                  int64_t NB, int u, int gs, bool rot, void* stream) {
+    Fmt f;
+    if (!X || !se || !up || !sh) return fail(MSAQ_ERR_ARG, "null pointer");
+    if (int rc = check_rows(map, D, NB, u, gs, &f)) return rc;
+    QuantJobs jobs{};
+    jobs.j[0] = QuantJob{static_cast<const __nv_bfloat16*>(X), se, up, sh, rot ? 1 : 0};
+    return launch_rows(jobs, 1, map, D, f, static_cast<cudaStream_t>(stream));
 }
 
 }  // namespace
@@ -228,6 +247,22 @@ extern "C" int msaq_kv_append_varlen(const void* X, int8_t* scale_exp, uint8_t* 
     if (Hkv <= 0) return fail(MSAQ_ERR_ARG, "Hkv must be positive");
     RowMap m{B * Hkv, 1, 0, Lcap, pos, Hkv};
     return quantize_rows(X, scale_exp, upper, shared, m, D, NB, u, gs, rotate != 0, stream);
+}
+
+extern "C" int msaq_kv_append_pair(const void* Xk, const void* Xv, int8_t* k_scale_exp, uint8_t* k_upper,
+                                   uint8_t* k_shared, int8_t* v_scale_exp, uint8_t* v_upper, uint8_t* v_shared,
+                                   int64_t B, int64_t Hkv, int64_t D, int64_t NB, int64_t pos, const int32_t* pos_per_seq,
+                                   int64_t Lcap, int u, int gs, int rotate_k, void* stream) {
+    if (!Xk || !Xv || !k_scale_exp || !k_upper || !k_shared || !v_scale_exp || !v_upper || !v_shared)
+        return fail(MSAQ_ERR_ARG, "null pointer");
+    if (B <= 0 || Hkv <= 0) return fail(MSAQ_ERR_ARG, "B and Hkv must be positive");
+    RowMap m{B * Hkv, 1, pos_per_seq ? 0 : pos, Lcap, pos_per_seq, Hkv};
+    Fmt f;
+    if (int rc = check_rows(m, D, NB, u, gs, &f)) return rc;
+    QuantJobs jobs{};
+    jobs.j[0] = QuantJob{static_cast<const __nv_bfloat16*>(Xk), k_scale_exp, k_upper, k_shared, rotate_k ? 1 : 0};
+    jobs.j[1] = QuantJob{static_cast<const __nv_bfloat16*>(Xv), v_scale_exp, v_upper, v_shared, 0};
+    return launch_rows(jobs, 2, m, D, f, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int msaq_kv_write(const void* X, int8_t* scale_exp, uint8_t* upper, uint8_t* shared, int64_t H, int64_t L,

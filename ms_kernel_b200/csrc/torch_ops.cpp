@@ -201,6 +201,32 @@ void kv_append_varlen(const Tensor& X, Tensor s, Tensor up, Tensor sh, const Ten
              "kv_append_varlen");
 }
 
+// K (rotated when asked) and V rows of one decode step in one launch; pos_t (int32 [B]) overrides pos when given.
+void kv_append_pair(const Tensor& Xk, const Tensor& Xv, Tensor ks, Tensor ku, Tensor kh, Tensor vs, Tensor vu, Tensor vh,
+                    const c10::optional<Tensor>& pos_t, int64_t B, int64_t Hkv, int64_t D, int64_t NB, int64_t pos,
+                    int64_t Lcap, int64_t u, int64_t gs, bool rotate_k) {
+    check_act(Xk, "Xk");
+    check_act(Xv, "Xv");
+    int64_t UB, SB;
+    fmt_sizes(u, gs, &UB, &SB);
+    TORCH_CHECK(Xk.numel() == B * Hkv * D && Xv.numel() == B * Hkv * D, "Xk and Xv must hold B*Hkv*D elements");
+    const int32_t* pp = nullptr;
+    if (pos_t.has_value()) {
+        const Tensor& p = *pos_t;
+        TORCH_CHECK(p.is_cuda() && p.scalar_type() == at::kInt && p.is_contiguous() && p.numel() == B,
+                    "pos must be a contiguous CUDA int32 tensor of B elements");
+        pp = p.data_ptr<int32_t>();
+    }
+    check_planes(ks, ku, kh, Xk, B * Hkv * NB * Lcap, UB, SB);
+    check_planes(vs, vu, vh, Xv, B * Hkv * NB * Lcap, UB, SB);
+    c10::cuda::CUDAGuard guard(Xk.device());
+    check_rc(msaq_kv_append_pair(Xk.data_ptr(), Xv.data_ptr(), ks.data_ptr<int8_t>(), ku.data_ptr<uint8_t>(),
+                                 kh.data_ptr<uint8_t>(), vs.data_ptr<int8_t>(), vu.data_ptr<uint8_t>(),
+                                 vh.data_ptr<uint8_t>(), B, Hkv, D, NB, pos, pp, Lcap, (int)u, (int)gs, rotate_k ? 1 : 0,
+                                 stream_of(Xk)),
+             "kv_append_pair");
+}
+
 std::vector<Tensor> kv_write_impl(const Tensor& X, int64_t H, int64_t L, int64_t D, int64_t NB, int64_t u, int64_t gs,
                                   bool rot) {
     check_act(X, "X");
@@ -396,6 +422,9 @@ TORCH_LIBRARY(msaq, m) {
           "int H, int L, int D, int NB, int key0, int Lcap, int u, int gs, bool rotate) -> ()", &kv_write_into);
     m.def("kv_append_varlen(Tensor X, Tensor(a!) scale_exp, Tensor(b!) upper, Tensor(c!) shared, Tensor pos, "
           "int B, int Hkv, int D, int NB, int Lcap, int u, int gs, bool rotate) -> ()", &kv_append_varlen);
+    m.def("kv_append_pair(Tensor Xk, Tensor Xv, Tensor(a!) ks, Tensor(b!) ku, Tensor(c!) kh, Tensor(d!) vs, Tensor(e!) vu, "
+          "Tensor(f!) vh, Tensor? pos_t, int B, int Hkv, int D, int NB, int pos, int Lcap, int u, int gs, bool rotate_k) -> ()",
+          &kv_append_pair);
     m.def("kv_decode_attention_varlen(Tensor q, Tensor ks, Tensor ku, Tensor kh, "
           "Tensor vs, Tensor vu, Tensor vh, Tensor seq_lens, "
           "int B, int H, int Hkv, int Lk, int D, int NB, int u, int gs, int Lcap, bool qrot) -> Tensor",

@@ -177,15 +177,13 @@ class KVCache:
         H = self.B * self.Hkv
         k_new = k_new.reshape(H, self.D).contiguous()
         v_new = v_new.reshape(H, self.D).contiguous()
+        # one launch for both tensors (kv_append_rot + kv_append of the reference write the same bytes)
         if isinstance(pos, int):
-            kop = _OPS.kv_append_rot if self.rotate else _OPS.kv_append
-            kop(k_new, *self.k, H, self.D, self.nb, pos, self.Lcap, self.u, self.gs)
-            _OPS.kv_append(v_new, *self.v, H, self.D, self.nb, pos, self.Lcap, self.u, self.gs)
+            _OPS.kv_append_pair(k_new, v_new, *self.k, *self.v, None, self.B, self.Hkv, self.D, self.nb, pos,
+                                self.Lcap, self.u, self.gs, self.rotate)
         else:
-            _OPS.kv_append_varlen(k_new, *self.k, pos, self.B, self.Hkv, self.D, self.nb,
-                                  self.Lcap, self.u, self.gs, self.rotate)
-            _OPS.kv_append_varlen(v_new, *self.v, pos, self.B, self.Hkv, self.D, self.nb,
-                                  self.Lcap, self.u, self.gs, False)
+            _OPS.kv_append_pair(k_new, v_new, *self.k, *self.v, pos, self.B, self.Hkv, self.D, self.nb, 0,
+                                self.Lcap, self.u, self.gs, self.rotate)
 
     def attend(self, q, Lk, seq_lens=None):
         """q [B,Hq,D] bf16 -> [B,Hq,D] bf16 over the first Lk keys (seq_lens[b] if given)."""

@@ -111,6 +111,39 @@ def test_kv_append_varlen_positions(rng):
                 assert np.all(rest.view(np.uint8) == 0x33)
 
 
+@pytest.mark.parametrize("u,gs", [(4, 2), (3, 4), (2, 8)])
+@pytest.mark.parametrize("varlen", (False, True))
+def test_kv_append_pair_equals_the_two_appends(rng, u, gs, varlen):
+    """K (rotated) and V of a step in one launch: the same bytes as kv_append_rot + kv_append, other slots untouched."""
+    import cabi
+    from ms_kernel_b200 import _lib
+    B, Hkv, D, Lcap = 3, 2, 128, 16
+    Xk = cabi.bf16_dev(rng.standard_normal((B * Hkv, D)) * 2)
+    Xv = cabi.bf16_dev(rng.standard_normal((B * Hkv, D)))
+    pos = torch.tensor([2, 9, 15], dtype=torch.int32, device="cuda")
+    kp = cabi.empty_cache(B * Hkv, D // 32, Lcap, u, gs, fill=0x33)
+    vp = cabi.empty_cache(B * Hkv, D // 32, Lcap, u, gs, fill=0x33)
+    L = _lib.lib()
+    _lib.check(L.msaq_kv_append_pair(Xk.data_ptr(), Xv.data_ptr(), *[t.data_ptr() for t in kp], *[t.data_ptr() for t in vp],
+                                     B, Hkv, D, D // 32, 5, pos.data_ptr() if varlen else None, Lcap, u, gs, 1,
+                                     torch.cuda.current_stream().cuda_stream))
+    kr = cabi.empty_cache(B * Hkv, D // 32, Lcap, u, gs, fill=0x33)
+    vr = cabi.empty_cache(B * Hkv, D // 32, Lcap, u, gs, fill=0x33)
+    if varlen:
+        cabi.kv_append_varlen(Xk, kr, B, Hkv, D, pos, Lcap, u, gs, rot=True)
+        cabi.kv_append_varlen(Xv, vr, B, Hkv, D, pos, Lcap, u, gs, rot=False)
+    else:
+        cabi.kv_append(Xk, kr, B * Hkv, D, 5, Lcap, u, gs, rot=True)
+        cabi.kv_append(Xv, vr, B * Hkv, D, 5, Lcap, u, gs, rot=False)
+    torch.cuda.synchronize()
+    for got, ref in zip(kp + vp, kr + vr):
+        assert torch.equal(got, ref)
+    assert L.msaq_kv_append_pair(None, Xv.data_ptr(), *[t.data_ptr() for t in kp], *[t.data_ptr() for t in vp],
+                                 B, Hkv, D, D // 32, 5, None, Lcap, u, gs, 1, None) == -1
+    assert L.msaq_kv_append_pair(Xk.data_ptr(), Xv.data_ptr(), *[t.data_ptr() for t in kp], *[t.data_ptr() for t in vp],
+                                 B, Hkv, D, D // 32, Lcap, None, Lcap, u, gs, 1, None) == -1      # slot past the capacity
+
+
 @pytest.mark.parametrize("D", (32, 64, 128, 256))
 def test_hadamard_rotate_bits(rng, D):
     import cabi
