@@ -402,9 +402,9 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
 }
 
 // Merge of tile partials kept in the exp2 domain (m is a base-2 exponent).  128 threads per
-// (head, sequence).  First the tiles' (m, l) pairs are fetched in parallel, one tile per thread,
-// and turned into weights in shared memory; then each thread sums its channel over the tiles in
-// tile order, sixteen loads in flight at a time.
+// (head, sequence).  The tiles' (m, l) pairs are fetched in parallel, one tile per thread, and turned
+// into weights in shared memory; each thread sums its channel over the tiles in tile order,
+// sixteen loads in flight at a time (up to 128 tiles: all requested in one round trip).
 constexpr int KVM_MERGE_TILES = 512;           // weights held in shared memory per pass over the tiles
 
 __global__ void __launch_bounds__(128)
@@ -413,49 +413,85 @@ kv_decode_combine2_kernel(const float* __restrict__ partial, __nv_bfloat16* __re
     chain_release();
     chain_wait();
     __shared__ float wgt[KVM_MERGE_TILES];
+    __shared__ float lsm[128];
     __shared__ float red[8];
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x, warp = d >> 5, lane = d & 31;
     const float* base = partial + ((int64_t)b * H + h) * S * 130;
 
-    // global maximum of m (fmaxf ignores the NaN that marks an abandoned tile; it is detected below)
-    float mloc = -INFINITY;
-    bool bad = false;
-    for (int s = d; s < S; s += 128) {
-        const float m = base[s * 130 + 128];
-        bad = bad || (m != m);
-        mloc = fmaxf(mloc, m);
-    }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
-    const unsigned badw = __ballot_sync(0xffffffffu, bad);
-    if (lane == 0) { red[warp] = mloc; red[4 + warp] = badw ? 1.0f : 0.0f; }
-    __syncthreads();
-    const float mg = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-    const bool poisoned = (red[4] + red[5] + red[6] + red[7]) > 0.0f;
-
     float num = 0.0f, den = 0.0f;
-    for (int c0 = 0; c0 < S; c0 += KVM_MERGE_TILES) {
-        const int cn = min(KVM_MERGE_TILES, S - c0);
+    bool poisoned;
+    if (S <= 128) {
+        // Common case, one dependent round trip: this thread's tile statistics and the first sixteen
+        // tiles of its channel are requested together; the weights come out of the registers.
+        float pv[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) pv[k] = (k < S) ? base[k * 130 + d] : 0.0f;
+        const float m_own = d < S ? base[d * 130 + 128] : -INFINITY;
+        const float l_own = d < S ? base[d * 130 + 129] : 0.0f;
+        float mloc = m_own;                                            // fmaxf ignores the NaN that marks an abandoned tile
+#pragma unroll
+        for (int o = 16; o; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
+        const unsigned badw = __ballot_sync(0xffffffffu, m_own != m_own);
+        if (lane == 0) { red[warp] = mloc; red[4 + warp] = badw ? 1.0f : 0.0f; }
         __syncthreads();
-        for (int s = d; s < cn; s += 128) {
-            const float m = base[(c0 + s) * 130 + 128];
-            wgt[s] = (m == -INFINITY || m != m) ? 0.0f : exp2f(m - mg);
+        const float mg = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+        poisoned = (red[4] + red[5] + red[6] + red[7]) > 0.0f;
+        if (d < S) {
+            wgt[d] = (m_own == -INFINITY || m_own != m_own) ? 0.0f : exp2f(m_own - mg);
+            lsm[d] = l_own;
         }
         __syncthreads();
-        for (int s0 = 0; s0 < cn; s0 += 16) {
-            float pv[16], lv[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            if (k < S) { num = fmaf(pv[k], wgt[k], num); den = fmaf(lsm[k], wgt[k], den); }
+        }
+        for (int s0 = 16; s0 < S; s0 += 16) {
+#pragma unroll
+            for (int k = 0; k < 16; ++k) pv[k] = (s0 + k < S) ? base[(s0 + k) * 130 + d] : 0.0f;
 #pragma unroll
             for (int k = 0; k < 16; ++k) {
-                const bool ok = s0 + k < cn;
-                const float* p = base + (c0 + s0 + k) * 130;
-                pv[k] = ok ? p[d] : 0.0f;
-                lv[k] = ok ? p[129] : 0.0f;
+                if (s0 + k < S) { num = fmaf(pv[k], wgt[s0 + k], num); den = fmaf(lsm[s0 + k], wgt[s0 + k], den); }
             }
+        }
+    } else {
+        // global maximum of m (fmaxf ignores the NaN that marks an abandoned tile; it is detected below)
+        float mloc = -INFINITY;
+        bool bad = false;
+        for (int s = d; s < S; s += 128) {
+            const float m = base[s * 130 + 128];
+            bad = bad || (m != m);
+            mloc = fmaxf(mloc, m);
+        }
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-                const float w = (s0 + k < cn) ? wgt[s0 + k] : 0.0f;
-                num = fmaf(pv[k], w, num);
-                den = fmaf(lv[k], w, den);
+        for (int o = 16; o; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
+        const unsigned badw = __ballot_sync(0xffffffffu, bad);
+        if (lane == 0) { red[warp] = mloc; red[4 + warp] = badw ? 1.0f : 0.0f; }
+        __syncthreads();
+        const float mg = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+        poisoned = (red[4] + red[5] + red[6] + red[7]) > 0.0f;
+        for (int c0 = 0; c0 < S; c0 += KVM_MERGE_TILES) {
+            const int cn = min(KVM_MERGE_TILES, S - c0);
+            __syncthreads();
+            for (int s = d; s < cn; s += 128) {
+                const float m = base[(c0 + s) * 130 + 128];
+                wgt[s] = (m == -INFINITY || m != m) ? 0.0f : exp2f(m - mg);
+            }
+            __syncthreads();
+            for (int s0 = 0; s0 < cn; s0 += 16) {
+                float pv[16], lv[16];
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                    const bool ok = s0 + k < cn;
+                    const float* p = base + (c0 + s0 + k) * 130;
+                    pv[k] = ok ? p[d] : 0.0f;
+                    lv[k] = ok ? p[129] : 0.0f;
+                }
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                    const float w = (s0 + k < cn) ? wgt[s0 + k] : 0.0f;
+                    num = fmaf(pv[k], w, num);
+                    den = fmaf(lv[k], w, den);
+                }
             }
         }
     }
