@@ -102,7 +102,7 @@ UmmaPlan plan_umma(int64_t M, int64_t OUT, int64_t NB, int u) {
     const long long units = s.units(), slots = sm_count();
     s.grid = (int)(units < slots ? units : slots);
     s.max_slots = (int)(((long long)s.nb * s.grid + units - 1) / units) + 1;
-    int stages = (200 * 1024 - 2 * GU_ABUF_BYTES) / gu_stage(u);
+    int stages = (226 * 1024 - GU_ABUFS * GU_ABUF_BYTES) / gu_stage(u);
     if (stages > GU_MAX_STAGES) stages = GU_MAX_STAGES;
     s.stages = stages;
     p.xs_bytes = ((size_t)NB * GU_XTILE + 255) & ~(size_t)255;
@@ -141,7 +141,7 @@ int run_umma(const __nv_bfloat16* X, const int8_t* se, const uint8_t* up, const 
         count_launch();
         if (int rc = check_launch("gemv_umma_xprep")) return rc;
         const GemvSchedule sch = p.sch;
-        const int smem = sch.stages * gu_stage(u) + 2 * GU_ABUF_BYTES;
+        const int smem = sch.stages * gu_stage(u) + GU_ABUFS * GU_ABUF_BYTES;
         GemvUmmaArgs a{se, up, sh, base, partial, status, static_cast<__nv_bfloat16*>(Y), Yf, (int)m0, rows, (int)OUT, sch};
         const int rc = u == 4 ? launch_umma<4>(a, smem, st) : u == 3 ? launch_umma<3>(a, smem, st) : launch_umma<2>(a, smem, st);
         if (rc) return rc;

@@ -43,7 +43,8 @@ constexpr int GU_ISSUERS = 2;                      // issuer g accumulates weigh
 constexpr int GU_THREADS = (GU_DEC_WARPS + 1 + GU_ISSUERS) * 32;
 constexpr int GU_MAX_N = 128;                      // activation rows per launch: the M of the MMA
 constexpr int GU_MAX_STAGES = 8;
-constexpr int GU_ABUF_BYTES = GU_TR * 64;          // one decoded A buffer: 512 rows x 32 bf16
+constexpr int GU_ABUF_BYTES = GU_TR * 64;          // one decoded weight buffer: 512 rows x 32 bf16
+constexpr int GU_ABUFS = 2;                        // one per decode team (two per team measured no faster and halve the ring)
 constexpr int GU_XTILE = GU_MAX_N * 64;            // activation tile of a K block: 128 rows x 32 bf16
 // gs = 2 formats: upper codes 4*(8-u) bytes, shared codes 2*u bytes, one scale byte per (row, block)
 __host__ __device__ constexpr int gu_ub(int u) { return 4 * (8 - u); }
@@ -282,9 +283,9 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
     constexpr int GU_PACKED = gu_packed(U);
     extern __shared__ __align__(128) uint8_t gu_smem[];
     __shared__ __align__(8) uint64_t bar_full[GU_MAX_STAGES];     // packed unit + activation tile landed (TMA)
-    __shared__ __align__(8) uint64_t bar_empty[GU_MAX_STAGES];    // the owning team's 8 warps passed the stage on (its MMAs are done)
-    __shared__ __align__(8) uint64_t bar_afull[2];                // decoded weight buffer written (the 8 warps of its team)
-    __shared__ __align__(8) uint64_t bar_aempty[2];               // MMAs that read the buffer completed (one commit per issuer)
+    __shared__ __align__(8) uint64_t bar_empty[GU_MAX_STAGES];    // the owning team's 8 warps have read the packed bytes and both issuers' MMAs the activation tile
+    __shared__ __align__(8) uint64_t bar_afull[GU_ABUFS];                // decoded weight buffer written (the 8 warps of its team)
+    __shared__ __align__(8) uint64_t bar_aempty[GU_ABUFS];               // MMAs that read the buffer completed (one commit per issuer)
     __shared__ __align__(8) uint64_t bar_accfull;                 // the tile's last MMAs completed (one commit per issuer)
     __shared__ __align__(8) uint64_t bar_accempty;                // 16 warps have read the accumulators
     __shared__ __align__(8) uint64_t bar_done;                    // teardown: every MMA issued has completed
@@ -296,7 +297,7 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
     const int stages = sch.stages;
     constexpr int STAGE = gu_stage(U);
     const uint32_t smem0 = smem_u32(gu_smem);
-    const uint32_t abuf0 = smem0 + stages * STAGE;                 // two decoded weight buffers behind the ring
+    const uint32_t abuf0 = smem0 + stages * STAGE;                 // the decoded weight buffers behind the ring
     constexpr uint32_t tmem_cols = GU_TMEM_COLS;
     const long long n_lo = sch.lo(blockIdx.x), n_hi = sch.lo(blockIdx.x + 1);
     const int n_iter = (int)(n_hi - n_lo);
@@ -312,9 +313,9 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
     if (tid == 0) {
         for (int s = 0; s < stages; ++s) {
             mbar_init(smem_u32(&bar_full[s]), 1);
-            mbar_init(smem_u32(&bar_empty[s]), GU_DEC_WARPS / 2);
+            mbar_init(smem_u32(&bar_empty[s]), GU_DEC_WARPS / 2 + GU_ISSUERS);
         }
-        for (int j = 0; j < 2; ++j) {
+        for (int j = 0; j < GU_ABUFS; ++j) {
             mbar_init(smem_u32(&bar_afull[j]), GU_DEC_WARPS / 2);
             mbar_init(smem_u32(&bar_aempty[j]), GU_ISSUERS);
         }
@@ -336,27 +337,34 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
 
     if (warp == GU_WARP_TMA) {
         // -------------------------------- TMA producer --------------------------------
-        if (lane == 0) {
-            int c = c_first, blk = blk_first, s = 0;
-            uint32_t ph = 1;                        // passes at once on a fresh barrier
-            for (int it = 0; it < n_iter && !abort_flag; ++it) {
-                if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ph)) {
-                    atomicExch(a.status, 1);
-                    abort_flag = 1;
-                    break;
-                }
-                const int o0 = c * GU_TR, cv = min(GU_TR, a.OUT - o0);
-                const uint32_t bar = smem_u32(&bar_full[s]);
-                const uint32_t base = smem0 + s * STAGE;
-                const int64_t col = (int64_t)blk * a.OUT + o0;
-                mbar_expect_tx(bar, (uint32_t)(cv * (gu_ub(U) + gu_sb(U) + 1) + xbytes));
-                bulk_g2s(base, a.upper_cm + col * gu_ub(U), (uint32_t)cv * gu_ub(U), bar);
-                bulk_g2s(base + GU_TR * gu_ub(U), a.shared_cm + col * gu_sb(U), (uint32_t)cv * gu_sb(U), bar);
-                bulk_g2s(base + GU_TR * (gu_ub(U) + gu_sb(U)), a.scale_exp + col, (uint32_t)cv, bar);
-                bulk_g2s(base + GU_PACKED, a.xs + (int64_t)blk * xbytes, (uint32_t)xbytes, bar);
-                if (++blk == sch.nb) { blk = 0; ++c; }
-                if (++s == stages) { s = 0; ph ^= 1u; }
+        // The whole warp runs the loop; lanes 0..3 each issue one of a unit's four copies in the same
+        // instruction (a lone thread needed about 1000 cycles per unit for them, more than the rest
+        // of the pipeline needs to consume one).
+        const uint8_t* src_base = lane == 0 ? a.upper_cm : lane == 1 ? a.shared_cm
+                                 : lane == 2 ? reinterpret_cast<const uint8_t*>(a.scale_exp) : a.xs;
+        const int per_col = lane == 0 ? gu_ub(U) : lane == 1 ? gu_sb(U) : 1;            // bytes per (row, block) of this lane's plane
+        const uint32_t dst_off = lane == 0 ? 0u : lane == 1 ? (uint32_t)(GU_TR * gu_ub(U))
+                               : lane == 2 ? (uint32_t)(GU_TR * (gu_ub(U) + gu_sb(U))) : (uint32_t)GU_PACKED;
+        int c = c_first, blk = blk_first, s = 0;
+        uint32_t ph = 1;                            // passes at once on a fresh barrier
+        for (int it = 0; it < n_iter; ++it) {
+            bool stop = abort_flag != 0;
+            if (!stop && !mbar_wait_bounded(smem_u32(&bar_empty[s]), ph)) {
+                atomicExch(a.status, 1);
+                abort_flag = 1;
+                stop = true;
             }
+            if (__any_sync(0xffffffffu, stop)) break;
+            const int o0 = c * GU_TR, cv = min(GU_TR, a.OUT - o0);
+            const uint32_t bar = smem_u32(&bar_full[s]);
+            const uint32_t base = smem0 + s * STAGE;
+            const int64_t col = (int64_t)blk * a.OUT + o0;
+            if (lane == 0) mbar_expect_tx(bar, (uint32_t)(cv * (gu_ub(U) + gu_sb(U) + 1) + xbytes));
+            __syncwarp();
+            if (lane < 3) bulk_g2s(base + dst_off, src_base + col * per_col, (uint32_t)(cv * per_col), bar);
+            else if (lane == 3) bulk_g2s(base + dst_off, src_base + (int64_t)blk * xbytes, (uint32_t)xbytes, bar);
+            if (++blk == sch.nb) { blk = 0; ++c; }
+            if (++s == stages) { s = 0; ph ^= 1u; }
         }
     } else if (warp >= GU_WARP_MMA) {
         // -------------------------------- MMA issuers --------------------------------
@@ -369,7 +377,7 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
             uint32_t aph = 0u, accph = 1;                         // accph: "accumulators free" passes at once the first time
             bool fresh = true;                                    // next MMA starts a tile: overwrite the accumulators
             for (int it = 0; it < n_iter && !abort_flag; ++it) {
-                const int buf = it & 1;
+                const int buf = it & (GU_ABUFS - 1);
                 // The decoders arrive on the A buffer only after they saw the stage's TMA data land, so
                 // this one wait also covers the activation tile of the stage.
                 bool ok = mbar_wait_bounded(smem_u32(&bar_afull[buf]), (aph >> buf) & 1u);
@@ -392,8 +400,8 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
                                  desc_hi, idesc, (fresh && ks == 0) ? 0u : 1u);
                 }
                 fresh = false;
-                tc_commit(smem_u32(&bar_aempty[buf]));            // the decoders may overwrite this A buffer, and
-                                                                  // pass the ring stage on (see the decoder loop)
+                tc_commit(smem_u32(&bar_aempty[buf]));            // its team may overwrite this decoded buffer
+                tc_commit(smem_u32(&bar_empty[s]));               // the ring may overwrite the activation tile
                 if (blk == sch.nb - 1 || it == n_iter - 1) {
                     tc_commit(smem_u32(&bar_accfull));            // the tile's accumulators are final
                     fresh = true;
@@ -409,7 +417,6 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
         // All sixteen warps read the accumulators back at the end of a tile segment.
         const int team = warp >> 3, tt = tid & 255;
         const int cg = warp >> 2, q = warp & 3;                    // epilogue: column group, tensor-memory lane quarter
-        const int buf = team;
         bool aborted = false;
 
         // epilogue of the segment of tile `c` (this CTA's run over that tile), in unit order
@@ -479,14 +486,15 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
             seg_end = min(seg_end + sch.nb, n_iter - 1);
         };
 
-        int s = team % stages, s_prev = s;                         // ring stage of this team's current / previous unit
-        uint32_t ph = (uint32_t)((team / stages) & 1), aeph = 1u;
+        int s = team % stages;                                     // ring stage of this team's current unit
+        uint32_t ph = (uint32_t)((team / stages) & 1), aeph = 3u; // aeph: one parity bit per buffer of the team
         for (int it = team; it < n_iter; it += 2) {
+            const int buf = it & (GU_ABUFS - 1), bsel = (it >> 1) & (GU_ABUFS / 2 - 1);   // this unit's decoded buffer; which of the team's own
             while (seg_end < it) epilogue();                       // segments that ended before this unit
             if (!aborted && abort_flag) aborted = true;
             if (!aborted) {
                 bool ok = mbar_wait_bounded(smem_u32(&bar_full[s]), ph);
-                ok = ok && mbar_wait_bounded(smem_u32(&bar_aempty[buf]), aeph);
+                ok = ok && mbar_wait_bounded(smem_u32(&bar_aempty[buf]), (aeph >> bsel) & 1u);
                 if (!ok) {
                     atomicExch(a.status, 1);
                     abort_flag = 1;
@@ -494,10 +502,7 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
                 }
             }
             aborted = __any_sync(0xffffffffu, aborted);
-            aeph ^= 1u;
-            // Passing the wait on the decoded buffer meant the MMAs of this team's previous unit had
-            // completed: that unit's ring stage (its activation tile was an MMA operand) goes back to the producer.
-            if (it >= 2 && lane == 0) mbar_arrive(smem_u32(&bar_empty[s_prev]));
+            aeph ^= 1u << bsel;
             if (!aborted) {
                 const uint32_t st = smem0 + s * STAGE;
 #pragma unroll 1
@@ -508,8 +513,10 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
                 fence_async_smem();                               // the tensor core reads the buffer through the async proxy
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_afull[buf]));
-            s_prev = s;
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&bar_afull[buf]));
+                mbar_arrive(smem_u32(&bar_empty[s]));             // this team is done with the packed bytes of the stage
+            }
             s += 2;
             if (s >= stages) { s -= stages; ph ^= 1u; }
         }

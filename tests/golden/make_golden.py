@@ -71,7 +71,9 @@ def edge_blocks(rng):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <checkout of yubin-wang99/ms_kernel>")
+    ref_root = sys.argv[1]
     sys.path.insert(0, ref_root)
     from ms_lib import pack as rp
     from ms_lib import reference as rr
