@@ -16,7 +16,7 @@ U, GS = 4, 2
 SHAPE = tp.LayerShape(hidden=256, n_q=4, n_kv=2, head_dim=64, ffn=512)
 
 
-def _weights(rng):
+def _weights(rng, SHAPE=SHAPE):
     d = SHAPE.head_dim
     dims = {"q": (SHAPE.n_q * d, SHAPE.hidden), "k": (SHAPE.n_kv * d, SHAPE.hidden), "v": (SHAPE.n_kv * d, SHAPE.hidden),
             "o": (SHAPE.hidden, SHAPE.n_q * d), "gate": (SHAPE.ffn, SHAPE.hidden), "up": (SHAPE.ffn, SHAPE.hidden),
@@ -76,12 +76,13 @@ class _OracleCache:
         return torch.from_numpy(out).to(torch.bfloat16)
 
 
-def _run_rank(rank, world, port, seed, q):
+def _run_rank(rank, world, port, seed, q, shape_args=None):
     import torch.distributed as dist
     if world > 1:
         dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    SHAPE = tp.LayerShape(*shape_args) if shape_args else globals()["SHAPE"]
     rng = np.random.default_rng(seed)
-    W, P = _weights(rng)
+    W, P = _weights(rng, SHAPE)
     B, L = 2, 12
     sh = tp.shard_layer(P, SHAPE, world, rank)
     lin = {k: _OracleLinear(v) for k, v in sh.items()}
@@ -114,14 +115,16 @@ def _free_port():
     return p
 
 
-def test_two_rank_gloo_step_matches_single_rank():
+@pytest.mark.parametrize("worlds,shape_args", [((1, 2), None), ((1, 4), (256, 8, 4, 64, 512))],
+                         ids=["two_ranks", "four_ranks"])
+def test_gloo_step_matches_single_rank(worlds, shape_args):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     results = []
-    for world in (1, 2):
+    for world in worlds:
         q = ctx.Queue()
         port = _free_port()
-        procs = [ctx.Process(target=_run_rank, args=(r, world, port, 123, q)) for r in range(world)]
+        procs = [ctx.Process(target=_run_rank, args=(r, world, port, 123, q, shape_args)) for r in range(world)]
         for p in procs:
             p.start()
         results.append(q.get(timeout=120))
