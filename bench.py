@@ -245,6 +245,15 @@ def run_ours(args):
 
     shape = tp.LayerShape.llama31_70b()
     B = args.batch
+    exchange = "none"
+    if world > 1:
+        exchange = "nccl all-reduce"
+        if os.environ.get("MSAQ_BENCH_EXCHANGE", "peer") == "peer":
+            try:
+                all_reduce = tp.peer_all_reduce(dist.group.WORLD, B * shape.hidden, torch.float32, dev)
+                exchange = "one-shot all-reduce over NVLink peer memory (torch symmetric memory)"
+            except Exception as e:                              # keep NCCL, say why
+                exchange = "nccl all-reduce (symmetric memory unavailable: %s)" % str(e).splitlines()[0][:80]
     probe = LayerSet(shape, world, rank, B, dev, 1, all_reduce)
     per_rank_bytes = probe.layer.algorithmic_bytes(B, B * LK, U, GS)
     # rotate over enough distinct weight + cache sets that a step never finds its bytes in L2
@@ -338,6 +347,7 @@ def run_ours(args):
             "workload": "llama-3.1-70b-shaped decoder layer, one decode step, u4/gs2 packed weights and KV cache, "
                         "hidden 8192, Hq 64, Hkv 8, D 128, FFN 28672, Lk %d, B %d" % (LK, B),
             "parallelism": "tp%d (rows of QKV/gate/up, K blocks of O/down, kv heads; 2 all-reduces per layer)" % world,
+            "exchange": exchange,
             "l2": "rotating over %d distinct weight+cache sets (%.0f MB per GPU per set)" % (n_sets, per_rank_bytes / 1e6),
             "timing": "CUDA-graph replay per step, CUDA events on the launching stream, max over ranks",
             "algorithmic_bytes_per_step": int(total_bytes),

@@ -128,6 +128,36 @@ def shard_layer(packs, shape, world, rank):
 
 
 # --------------------------------------------------------------------------
+# the exchange step
+# --------------------------------------------------------------------------
+def peer_all_reduce(group, numel, dtype, device, slots=2):
+    """All-reduce for the two small [B, hidden] partial sums of a step over NVLink peer memory.
+
+    The message is 32 KB at B = 1, so the cost is latency: NCCL's all-reduce measured 16.5 us at two
+    ranks inside a CUDA graph.  torch's symmetric-memory one-shot all-reduce has every rank copy its
+    partial into a buffer its peers can load from and sum all copies itself (plain peer loads, no
+    multicast).  Returns a callable t -> sum over ranks (a new tensor); consecutive calls rotate over
+    `slots` buffers so that a rank still reading the previous message never sees the next one.
+    Raises if symmetric memory cannot be set up; the caller then keeps NCCL."""
+    import torch
+    import torch.distributed._symmetric_memory as symm
+    name = group.group_name
+    bufs = []
+    for _ in range(slots):
+        b = symm.empty(numel, dtype=dtype, device=device)
+        symm.rendezvous(b, name)
+        bufs.append(b)
+    state = {"i": 0}
+
+    def all_reduce(t):
+        b = bufs[state["i"] % slots]
+        state["i"] += 1
+        return torch.ops.symm_mem.one_shot_all_reduce_copy(b, t.reshape(-1), "sum", name).reshape(t.shape)
+
+    return all_reduce
+
+
+# --------------------------------------------------------------------------
 # the step
 # --------------------------------------------------------------------------
 class DecoderLayerTP:
