@@ -417,31 +417,40 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
                         const int ncol = nq * 16;
                         const int64_t sstride = (int64_t)a.rows * a.OUT;
                         const int total = a.rows * ncol;
-                        // two outputs per lane at a time, eight slots each in flight, summed in slot order
+                        // Sixteen loads in flight per lane, summed in slot order: two outputs x eight slots, or --
+                        // when this lane has a single output left -- sixteen slots of that one output.
                         for (int i0 = lane; i0 < total; i0 += 64) {
-                            const int i1 = min(i0 + 32, total - 1);
+                            const bool single = i0 + 32 >= total;
+                            const int i1 = single ? i0 : i0 + 32;
                             const int m0 = i0 / ncol, j0 = i0 % ncol, m1 = i1 / ncol, j1 = i1 % ncol;
                             const int64_t e0 = (int64_t)m0 * a.OUT + o0 + (j0 >> 4) * GM_GROUP + warp * 16 + (j0 & 15);
                             const int64_t e1 = (int64_t)m1 * a.OUT + o0 + (j1 >> 4) * GM_GROUP + warp * 16 + (j1 & 15);
                             const float* s0 = a.partial + e0;
-                            const float* s1 = a.partial + e1;
+                            const float* s1 = a.partial + e1 + (single ? 8 * sstride : 0);
+                            const int step = single ? 16 : 8, lim1 = single ? nslots - 8 : nslots;
                             float sum0 = 0.0f, sum1 = 0.0f;
-                            for (int k0 = 0; k0 < nslots; k0 += 8) {
+                            for (int k0 = 0; k0 < nslots; k0 += step) {
                                 float v[8], w[8];
 #pragma unroll
                                 for (int k = 0; k < 8; ++k) {
-                                    const bool in = k0 + k < nslots;
-                                    v[k] = in ? __ldcg(s0 + (k0 + k) * sstride) : 0.0f;
-                                    w[k] = in ? __ldcg(s1 + (k0 + k) * sstride) : 0.0f;
+                                    v[k] = (k0 + k < nslots) ? __ldcg(s0 + (k0 + k) * sstride) : 0.0f;
+                                    w[k] = (k0 + k < lim1) ? __ldcg(s1 + (k0 + k) * sstride) : 0.0f;
                                 }
 #pragma unroll
-                                for (int k = 0; k < 8; ++k) { sum0 += v[k]; sum1 += w[k]; }
+                                for (int k = 0; k < 8; ++k) sum0 += v[k];
+                                if (single) {
+#pragma unroll
+                                    for (int k = 0; k < 8; ++k) sum0 += w[k];
+                                } else {
+#pragma unroll
+                                    for (int k = 0; k < 8; ++k) sum1 += w[k];
+                                }
                             }
                             if (poison) sum0 = sum1 = __int_as_float(0x7FC00000);
                             const int64_t y0 = (int64_t)a.m0 * a.OUT + e0, y1 = (int64_t)a.m0 * a.OUT + e1;
                             a.y[y0] = __float2bfloat16_rn(sum0);
                             if (yf) yf[y0] = sum0;
-                            if (i0 + 32 < total) {
+                            if (!single) {
                                 a.y[y1] = __float2bfloat16_rn(sum1);
                                 if (yf) yf[y1] = sum1;
                             }
