@@ -113,31 +113,50 @@ gemv_xprep_kernel(const XprepArgs a) {
             float ss = 0.0f;
             if (live && mr < a.M) {
                 const uint4* xr = reinterpret_cast<const uint4*>(a.X + (int64_t)mr * a.ldx);
-                for (int i = threadIdx.x; i < K / 8; i += 128) {
-                    const uint4 v = xr[i];
-                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-                    float f[8];
+                // four 16-byte chunks per thread at a time, every load of the batch issued before the first use
+                for (int i0 = threadIdx.x; i0 < K / 8; i0 += 4 * 128) {
+                    uint4 hv[4], dv[4], dv2[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) { f[2 * j] = bf16_lo(w[j]); f[2 * j + 1] = bf16_hi(w[j]); }
-                    if (MODE == XP_ADD_NORM) {
-                        const int64_t o = (int64_t)mr * K + i * 8;        // 16-byte aligned: the launcher checks the bases
-                        float d[8];
-                        if (a.r_is_f32) {
-                            const float4 d0 = *reinterpret_cast<const float4*>(Rf + o);
-                            const float4 d1 = *reinterpret_cast<const float4*>(Rf + o + 4);
-                            d[0] = d0.x; d[1] = d0.y; d[2] = d0.z; d[3] = d0.w;
-                            d[4] = d1.x; d[5] = d1.y; d[6] = d1.z; d[7] = d1.w;
-                        } else {
-                            const uint4 dv = *reinterpret_cast<const uint4*>(Rh + o);
-                            const uint32_t dw[4] = {dv.x, dv.y, dv.z, dv.w};
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) { d[2 * j] = bf16_lo(dw[j]); d[2 * j + 1] = bf16_hi(dw[j]); }
+                    for (int b = 0; b < 4; ++b) {
+                        const int i = i0 + b * 128;
+                        const bool in = i < K / 8;
+                        hv[b] = in ? xr[i] : make_uint4(0u, 0u, 0u, 0u);
+                        dv[b] = dv2[b] = make_uint4(0u, 0u, 0u, 0u);
+                        if (MODE == XP_ADD_NORM && in) {
+                            const int64_t o = (int64_t)mr * K + i * 8;    // 16-byte aligned: the launcher checks the bases
+                            if (a.r_is_f32) {
+                                dv[b] = *reinterpret_cast<const uint4*>(Rf + o);
+                                dv2[b] = *reinterpret_cast<const uint4*>(Rf + o + 4);
+                            } else {
+                                dv[b] = *reinterpret_cast<const uint4*>(Rh + o);
+                            }
                         }
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(__float2bfloat16_rn(f[j] + d[j]));
                     }
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+                    for (int b = 0; b < 4; ++b) {
+                        const uint32_t w[4] = {hv[b].x, hv[b].y, hv[b].z, hv[b].w};
+                        float f[8];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) { f[2 * j] = bf16_lo(w[j]); f[2 * j + 1] = bf16_hi(w[j]); }
+                        if (MODE == XP_ADD_NORM) {
+                            float d[8];
+                            if (a.r_is_f32) {
+                                d[0] = __uint_as_float(dv[b].x); d[1] = __uint_as_float(dv[b].y);
+                                d[2] = __uint_as_float(dv[b].z); d[3] = __uint_as_float(dv[b].w);
+                                d[4] = __uint_as_float(dv2[b].x); d[5] = __uint_as_float(dv2[b].y);
+                                d[6] = __uint_as_float(dv2[b].z); d[7] = __uint_as_float(dv2[b].w);
+                            } else {
+                                const uint32_t dw[4] = {dv[b].x, dv[b].y, dv[b].z, dv[b].w};
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) { d[2 * j] = bf16_lo(dw[j]); d[2 * j + 1] = bf16_hi(dw[j]); }
+                            }
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(__float2bfloat16_rn(f[j] + d[j]));
+                        }
+                        // chunks past the end of the row are zero and add nothing
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+                    }
                 }
             }
 #pragma unroll
