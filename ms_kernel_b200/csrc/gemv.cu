@@ -7,10 +7,8 @@
 #include "gemv_umma.cuh"
 
 namespace msaq {
-namespace {
 
 // generic path, defined in gemv_generic.cu
-}  // namespace
 size_t gemv_generic_workspace(int64_t M, int64_t OUT, int64_t NB);
 int gemv_run_generic(const __nv_bfloat16* X, const int8_t* se, const uint8_t* up, const uint8_t* sh, void* Y,
                      float* Yf, int64_t M, int64_t OUT, int64_t NB, const Fmt& f, bool cm, void* ws,

@@ -1,17 +1,19 @@
-// Batched weight-only GEMV (9 <= M, tiles of up to 128 activation rows) for u = 4, gs = 2
-// on the fifth-generation tensor cores: Y[M][OUT] = X[M][K] * dequant(W)^T.
+// Weight-only GEMV on the fifth-generation tensor cores, Y[M][OUT] = X[M][K] * dequant(W)^T, in
+// tiles of up to 128 activation rows: u = 4, gs = 2 from nine rows up, and the 5+3 and 6+2 bit
+// formats (u = 3, u = 2 at gs = 2) at every batch size.
 //
 // At these batch sizes the work is a real contraction, so it goes to tcgen05.mma with the
-// accumulator in tensor memory.  The weights stay packed in HBM (25 bytes per 32-block)
+// accumulator in tensor memory.  The weights stay packed in HBM (25 to 29 bytes per 32-block)
 // and are widened on the way:
-//   * a producer thread streams the packed bytes of a (512 weight rows x one K block)
+//   * a producer warp streams the packed bytes of a (512 weight rows x one K block)
 //     unit, and the matching bf16 activation tile, into a shared-memory ring with TMA
 //     bulk copies (cp.async.bulk + mbarrier);
 //   * sixteen decode warps in two teams that take alternate units, two weight rows per
-//     thread, turn the 32 codes of a row's block into the exact bf16 values q * 2^e (q = 16*up + sh is a 8-bit integer, so the
-//     product is representable) and store them as the A operand in the core-matrix
-//     layout tcgen05 reads (K-major, no swizzle);
-//   * one thread issues, per unit, 2 row groups x 2 K steps of
+//     thread, turn the 32 codes of a row's block into the exact bf16 values q * 2^e
+//     (q = up * 2^u + sh is an 8-bit integer, so the product is representable) and store them
+//     as the B operand in the core-matrix layout tcgen05 reads (K-major, no swizzle);
+//   * two issuing threads, each owning 256 weight rows (256 accumulator columns) of every
+//     unit, issue 2 K steps each of
 //     tcgen05.mma.cta_group::1.kind::f16  D[128 x 256] += A[128 x 16] * B[256 x 16]^T
 //     with A = activations (rows beyond M are zero) and B = 256 weight rows -- an MMA costs
 //     about 135 cycles to issue whatever its N, so the weights take the wide side -- fp32
