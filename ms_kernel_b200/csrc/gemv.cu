@@ -34,7 +34,10 @@ MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB) {
     const long long slots = (long long)GM_CTAS_PER_SM * sm_count();
     // Widest tile (fewest, largest TMA copies) that keeps the number of CTAs sharing one tile --
     // and with it the partial sums the finishing warp has to add up -- at or below 32.
-    for (int tc = GM_MAX_TC; tc >= GM_GROUP; tc >>= 1) {
+    // The 1024-column tile (16 accumulators per thread, half as many barrier hand-offs per byte) pays for a
+    // single row: 57344x8192 77 -> 68 us; with four rows it measured slower than 512 columns (41.7 against 32.7 us
+    // on 28672x4096).
+    for (int tc = M == 1 ? GM_MAX_TC : GM_MAX_TC / 2; tc >= GM_GROUP; tc >>= 1) {
         s.tc = tc;
         s.col_tiles = (int)((OUT + tc - 1) / tc);
         const long long units = s.units();
@@ -78,6 +81,9 @@ int launch_mma_tc(const GemvMmaArgs& a, cudaStream_t st) {
     switch (a.sch.tc) {
         case 128: return launch_mma<PASSES, 128>(a, st);
         case 256: return launch_mma<PASSES, 256>(a, st);
+        case 1024:
+            if constexpr (PASSES == 1) return launch_mma<1, 1024>(a, st);
+            return fail(MSAQ_ERR_ARG, "1024-column tiles are planned for single-pass launches only");
         default: return launch_mma<PASSES, 512>(a, st);
     }
 }

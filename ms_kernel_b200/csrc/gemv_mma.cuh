@@ -32,7 +32,7 @@ namespace msaq {
 constexpr int GM_WARPS = 8;          // consumer warps; each owns 16 columns of every 128-column group
 constexpr int GM_THREADS = (GM_WARPS + 1) * 32;
 constexpr int GM_GROUP = 128;        // columns per group (8 warps x 16)
-constexpr int GM_MAX_TC = 512;       // columns per tile (1, 2 or 4 groups)
+constexpr int GM_MAX_TC = 1024;      // columns per tile (1, 2, 4 or 8 groups; 8 only for single-row launches)
 constexpr int GM_MAX_STAGES = 12;
 constexpr int GM_MP = 4;             // activation rows per MMA pass
 constexpr int GM_MAX_PASSES = 4;     // -> at most 16 rows per launch
@@ -271,6 +271,18 @@ __device__ __forceinline__ void gemv_group_step(uint32_t wbase, uint32_t sbase, 
     }
 }
 
+// The column groups Q, Q+1, ... of a tile, each with compile-time shared-memory offsets; ALL skips
+// the per-group test when the warp has columns in every group.
+template <int PASSES, int Q, int GROUPS, bool ALL>
+__device__ __forceinline__ void gemv_groups(int nq, uint32_t wb, uint32_t sbs, uint32_t eb, uint32_t sel, uint32_t nshift,
+                                            const uint2 (&bq)[PASSES], const int (&corr)[PASSES], const float (&cx)[PASSES],
+                                            float (&acc)[GROUPS][PASSES][2]) {
+    if constexpr (Q < GROUPS) {
+        if (ALL || Q < nq) gemv_group_step<PASSES, Q>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[Q]);
+        gemv_groups<PASSES, Q + 1, GROUPS, ALL>(nq, wb, sbs, eb, sel, nshift, bq, corr, cx, acc);
+    }
+}
+
 template <int PASSES, int TC>
 __global__ void __launch_bounds__(GM_THREADS, GM_CTAS_PER_SM)
 gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
@@ -368,16 +380,8 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
             }
             const uint32_t wb = aW + so, sbs = aS + so, eb = aE + so;
             const int nq = (cv - warp * 16 + GM_GROUP - 1) / GM_GROUP;      // column groups this warp has in the tile
-            if (nq >= GROUPS) {
-                gemv_group_step<PASSES, 0>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[0]);
-                if (GROUPS > 1) gemv_group_step<PASSES, (GROUPS > 1 ? 1 : 0)>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[GROUPS > 1 ? 1 : 0]);
-                if (GROUPS > 2) gemv_group_step<PASSES, (GROUPS > 2 ? 2 : 0)>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[GROUPS > 2 ? 2 : 0]);
-                if (GROUPS > 3) gemv_group_step<PASSES, (GROUPS > 3 ? 3 : 0)>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[GROUPS > 3 ? 3 : 0]);
-            } else {
-                if (nq > 0) gemv_group_step<PASSES, 0>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[0]);
-                if (GROUPS > 1 && nq > 1) gemv_group_step<PASSES, (GROUPS > 1 ? 1 : 0)>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[GROUPS > 1 ? 1 : 0]);
-                if (GROUPS > 2 && nq > 2) gemv_group_step<PASSES, (GROUPS > 2 ? 2 : 0)>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[GROUPS > 2 ? 2 : 0]);
-            }
+            if (nq >= GROUPS) gemv_groups<PASSES, 0, GROUPS, true>(nq, wb, sbs, eb, sel, nshift, bq, corr, cx, acc);
+            else gemv_groups<PASSES, 0, GROUPS, false>(nq, wb, sbs, eb, sel, nshift, bq, corr, cx, acc);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_empty[s]));
