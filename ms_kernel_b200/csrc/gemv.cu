@@ -17,7 +17,8 @@ namespace {
 
 // ---- tuned path (u4/gs2, column-major planes, OUT % 16 == 0) --------------------
 struct MmaPlan {
-    GemvSchedule sch;
+    GemvSchedule sch;        // sch.nb counts units of `kb` K blocks
+    int kb;
     size_t xprep_bytes, ctl_off, partial_off, total;
 };
 
@@ -31,6 +32,7 @@ MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB) {
     const int64_t rows = M < GM_MP * GM_MAX_PASSES ? M : GM_MP * GM_MAX_PASSES;
     const int passes = (int)((rows + GM_MP - 1) / GM_MP);
     s.nb = (int)NB;
+    p.kb = 1;
     const long long slots = (long long)GM_CTAS_PER_SM * sm_count();
     // Widest tile (fewest, largest TMA copies) that keeps the number of CTAs sharing one tile --
     // and with it the partial sums the finishing warp has to add up -- at or below 32.
@@ -44,10 +46,18 @@ MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB) {
         s.grid = (int)(units < slots ? units : slots);
         if (tc == GM_GROUP || (s.grid + s.col_tiles - 1) / s.col_tiles <= 32) break;
     }
+    // A single row on 512-column tiles (the tile could not get wider: too few column tiles): two K blocks per
+    // ring stage instead, for the same halving of the hand-offs per byte.
+    if (M == 1 && s.tc == GM_MAX_TC / 2 && NB >= 2) {
+        p.kb = 2;
+        s.nb = (int)((NB + 1) / 2);
+        const long long u2 = s.units();
+        s.grid = (int)(u2 < slots ? u2 : slots);
+    }
     const long long units = s.units();
     s.max_slots = (int)(((long long)s.nb * s.grid + units - 1) / units) + 1;
     const int per_sm = (s.grid + sm_count() - 1) / sm_count();
-    const int stage = gm_stage_bytes(s.tc, passes);
+    const int stage = p.kb * gm_stage_bytes(s.tc, passes);
     int stages = (200 * 1024 / per_sm) / stage;
     if (stages > GM_MAX_STAGES) stages = GM_MAX_STAGES;
     if (stages < 2) stages = 2;
@@ -59,25 +69,29 @@ MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB) {
     return p;
 }
 
-template <int PASSES, int TC>
+template <int PASSES, int TC, int KB = 1>
 int launch_mma(const GemvMmaArgs& a, cudaStream_t st) {
     static int configured[64] = {};                      // largest dynamic smem size set per device
-    const int smem = a.sch.stages * gm_stage_bytes(TC, PASSES);
+    const int smem = a.sch.stages * KB * gm_stage_bytes(TC, PASSES);
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && configured[dev] < smem) {
-        if (cudaFuncSetAttribute(gemv_u4gs2_mma_kernel<PASSES, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(gemv_u4gs2_mma_kernel<PASSES, TC, KB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  smem) != cudaSuccess)
             return fail(MSAQ_ERR_CUDA, "cannot reserve %d bytes of shared memory", smem);
         configured[dev] = smem;
     }
-    launch_chained(gemv_u4gs2_mma_kernel<PASSES, TC>, dim3(a.sch.grid), dim3(GM_THREADS), smem, st, a);
+    launch_chained(gemv_u4gs2_mma_kernel<PASSES, TC, KB>, dim3(a.sch.grid), dim3(GM_THREADS), smem, st, a);
     count_launch();
     return check_launch("gemv_u4gs2_mma");
 }
 
 template <int PASSES>
-int launch_mma_tc(const GemvMmaArgs& a, cudaStream_t st) {
+int launch_mma_tc(const GemvMmaArgs& a, int kb, cudaStream_t st) {
+    if (kb == 2) {
+        if constexpr (PASSES == 1) return launch_mma<1, GM_MAX_TC / 2, 2>(a, st);
+        return fail(MSAQ_ERR_ARG, "two K blocks per stage are planned for single-row launches only");
+    }
     switch (a.sch.tc) {
         case 128: return launch_mma<PASSES, 128>(a, st);
         case 256: return launch_mma<PASSES, 256>(a, st);
@@ -212,14 +226,14 @@ int run_mma(const __nv_bfloat16* X, const Prologue& pro, const int8_t* se, const
         xa.eps = pro.eps;
         if (int rc = launch_xprep(xa, pro.mode, (unsigned)((warps * 32 + 127) / 128), st)) return rc;
         GemvMmaArgs a{se, up, sh, base, partial, counters, status, static_cast<__nv_bfloat16*>(Y), Yf,
-                      (int)m0, rows, (int)OUT, p.sch};
+                      (int)m0, rows, (int)OUT, (int)NB, p.sch};
         // the ring depth was planned for the first tile's pass count; a last, smaller tile may go deeper but need not
         int rc;
         switch (passes) {
-            case 1: rc = launch_mma_tc<1>(a, st); break;
-            case 2: rc = launch_mma_tc<2>(a, st); break;
-            case 3: rc = launch_mma_tc<3>(a, st); break;
-            default: rc = launch_mma_tc<4>(a, st); break;
+            case 1: rc = launch_mma_tc<1>(a, p.kb, st); break;
+            case 2: rc = launch_mma_tc<2>(a, p.kb, st); break;
+            case 3: rc = launch_mma_tc<3>(a, p.kb, st); break;
+            default: rc = launch_mma_tc<4>(a, p.kb, st); break;
         }
         if (rc) return rc;
     }

@@ -231,6 +231,7 @@ struct GemvMmaArgs {
     float* y_f32;            // optional
     int m0, rows;            // this launch covers rows [m0, m0 + rows), rows <= 16
     int OUT;
+    int NB;                  // K blocks of the weight (sch.nb counts units: groups of KB blocks)
     GemvSchedule sch;
 };
 
@@ -283,7 +284,9 @@ __device__ __forceinline__ void gemv_groups(int nq, uint32_t wb, uint32_t sbs, u
     }
 }
 
-template <int PASSES, int TC>
+// KB = K blocks per ring stage (per unit).  Two halve the barrier hand-offs per byte where the tile
+// cannot get wider (few column tiles, many K blocks).
+template <int PASSES, int TC, int KB>
 __global__ void __launch_bounds__(GM_THREADS, GM_CTAS_PER_SM)
 gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -292,7 +295,8 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
 
     constexpr int GROUPS = TC / GM_GROUP;
     constexpr int OFF_SH = TC * 16, OFF_SC = TC * 24, OFF_X = TC * 25;
-    constexpr int STAGE_BYTES = TC * 25 + PASSES * GM_XREC;
+    constexpr int SUB_BYTES = TC * 25 + PASSES * GM_XREC;      // one K block of the tile with its activation record
+    constexpr int STAGE_BYTES = KB * SUB_BYTES;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const GemvSchedule sch = a.sch;
@@ -323,13 +327,19 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
                 }
                 const int o0 = c * TC, cv = min(TC, a.OUT - o0);
                 const uint32_t bar = smem_u32(&bar_full[s]);
-                const uint32_t base = smem_u32(smem) + s * STAGE_BYTES;
-                const int64_t col = (int64_t)blk * a.OUT + o0;
-                mbar_expect_tx(bar, (uint32_t)(cv * 25 + PASSES * GM_XREC));
-                bulk_g2s(base, a.upper_cm + col * 16, (uint32_t)cv * 16, bar);
-                bulk_g2s(base + OFF_SH, a.shared_cm + col * 8, (uint32_t)cv * 8, bar);
-                bulk_g2s(base + OFF_SC, a.scale_exp + col, (uint32_t)cv, bar);
-                bulk_g2s(base + OFF_X, a.xprep + (int64_t)blk * PASSES * GM_XREC, (uint32_t)(PASSES * GM_XREC), bar);
+                const int b0 = blk * KB, nblk = min(KB, a.NB - b0);         // `blk` counts units within the tile
+                mbar_expect_tx(bar, (uint32_t)(nblk * (cv * 25 + PASSES * GM_XREC)));
+#pragma unroll
+                for (int j = 0; j < KB; ++j) {
+                    if (j < nblk) {
+                        const uint32_t base = smem_u32(smem) + s * STAGE_BYTES + j * SUB_BYTES;
+                        const int64_t col = (int64_t)(b0 + j) * a.OUT + o0;
+                        bulk_g2s(base, a.upper_cm + col * 16, (uint32_t)cv * 16, bar);
+                        bulk_g2s(base + OFF_SH, a.shared_cm + col * 8, (uint32_t)cv * 8, bar);
+                        bulk_g2s(base + OFF_SC, a.scale_exp + col, (uint32_t)cv, bar);
+                        bulk_g2s(base + OFF_X, a.xprep + (int64_t)(b0 + j) * PASSES * GM_XREC, (uint32_t)(PASSES * GM_XREC), bar);
+                    }
+                }
                 if (++blk == sch.nb) { blk = 0; ++c; }
                 if (++s == sch.stages) { s = 0; ph ^= 1u; }
             }
@@ -365,23 +375,29 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
             atomicExch(a.status, 1);
             aborted = true;
         }
-        const uint32_t so = s * STAGE_BYTES;
         const int cv = min(TC, a.OUT - c * TC);
         if (!aborted) {
-            uint2 bq[PASSES];
-            int corr[PASSES];
-            float cx[PASSES];
-#pragma unroll
-            for (int p = 0; p < PASSES; ++p) {
-                const uint32_t rb = aB + so + p * GM_XREC;
-                bq[p] = lds64<0>(rb);
-                corr[p] = (int)lds32<0>(aC + so + p * GM_XREC);
-                cx[p] = __uint_as_float(lds32<4>(aC + so + p * GM_XREC));
-            }
-            const uint32_t wb = aW + so, sbs = aS + so, eb = aE + so;
+            const int nblk = min(KB, a.NB - blk * KB);                      // `blk` counts units within the tile
             const int nq = (cv - warp * 16 + GM_GROUP - 1) / GM_GROUP;      // column groups this warp has in the tile
-            if (nq >= GROUPS) gemv_groups<PASSES, 0, GROUPS, true>(nq, wb, sbs, eb, sel, nshift, bq, corr, cx, acc);
-            else gemv_groups<PASSES, 0, GROUPS, false>(nq, wb, sbs, eb, sel, nshift, bq, corr, cx, acc);
+#pragma unroll
+            for (int j = 0; j < KB; ++j) {
+                if (j < nblk) {
+                    const uint32_t so = s * STAGE_BYTES + j * SUB_BYTES;
+                    uint2 bq[PASSES];
+                    int corr[PASSES];
+                    float cx[PASSES];
+#pragma unroll
+                    for (int p = 0; p < PASSES; ++p) {
+                        const uint32_t rb = aB + so + p * GM_XREC;
+                        bq[p] = lds64<0>(rb);
+                        corr[p] = (int)lds32<0>(aC + so + p * GM_XREC);
+                        cx[p] = __uint_as_float(lds32<4>(aC + so + p * GM_XREC));
+                    }
+                    const uint32_t wb = aW + so, sbs = aS + so, eb = aE + so;
+                    if (nq >= GROUPS) gemv_groups<PASSES, 0, GROUPS, true>(nq, wb, sbs, eb, sel, nshift, bq, corr, cx, acc);
+                    else gemv_groups<PASSES, 0, GROUPS, false>(nq, wb, sbs, eb, sel, nshift, bq, corr, cx, acc);
+                }
+            }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_empty[s]));
