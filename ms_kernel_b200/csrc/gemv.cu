@@ -48,9 +48,9 @@ MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB) {
     }
     // A single row on 512-column tiles (the tile could not get wider: too few column tiles): two K blocks per
     // ring stage instead, for the same halving of the hand-offs per byte.
-    if (M == 1 && s.tc == GM_MAX_TC / 2 && NB >= 2) {
-        p.kb = 2;
-        s.nb = (int)((NB + 1) / 2);
+    if (M == 1 && (s.tc == 512 || s.tc == 256) && NB >= 4) {
+        p.kb = s.tc == 512 ? 2 : 4;                    // 25.6 KB of packed bytes per stage either way
+        s.nb = (int)((NB + p.kb - 1) / p.kb);
         const long long u2 = s.units();
         s.grid = (int)(u2 < slots ? u2 : slots);
     }
@@ -88,9 +88,9 @@ int launch_mma(const GemvMmaArgs& a, cudaStream_t st) {
 
 template <int PASSES>
 int launch_mma_tc(const GemvMmaArgs& a, int kb, cudaStream_t st) {
-    if (kb == 2) {
-        if constexpr (PASSES == 1) return launch_mma<1, GM_MAX_TC / 2, 2>(a, st);
-        return fail(MSAQ_ERR_ARG, "two K blocks per stage are planned for single-row launches only");
+    if (kb > 1) {
+        if constexpr (PASSES == 1) return kb == 2 ? launch_mma<1, 512, 2>(a, st) : launch_mma<1, 256, 4>(a, st);
+        return fail(MSAQ_ERR_ARG, "several K blocks per stage are planned for single-row launches only");
     }
     switch (a.sch.tc) {
         case 128: return launch_mma<PASSES, 128>(a, st);
