@@ -46,10 +46,10 @@ MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB) {
         s.grid = (int)(units < slots ? units : slots);
         if (tc == GM_GROUP || (s.grid + s.col_tiles - 1) / s.col_tiles <= 32) break;
     }
-    // Single-pass launches (up to four rows) on 512- or 256-column tiles: two or four K blocks per ring stage,
+    // Launches of one or two passes (up to eight rows) on 512- or 256-column tiles: two or four K blocks per ring stage,
     // for the same cut in hand-offs per byte the wider tile gives (8192x28672: 44.5 -> 41.3 us at one row,
     // 54.9 -> 50.8 us at four).
-    if (passes == 1 && (s.tc == 512 || s.tc == 256) && NB >= 4) {
+    if (passes <= 2 && (s.tc == 512 || s.tc == 256) && NB >= 4) {
         p.kb = s.tc == 512 ? 2 : 4;                    // 25.6 KB of packed bytes per stage either way
         s.nb = (int)((NB + p.kb - 1) / p.kb);
         const long long u2 = s.units();
@@ -90,8 +90,8 @@ int launch_mma(const GemvMmaArgs& a, cudaStream_t st) {
 template <int PASSES>
 int launch_mma_tc(const GemvMmaArgs& a, int kb, cudaStream_t st) {
     if (kb > 1) {
-        if constexpr (PASSES == 1) return kb == 2 ? launch_mma<1, 512, 2>(a, st) : launch_mma<1, 256, 4>(a, st);
-        return fail(MSAQ_ERR_ARG, "several K blocks per stage are planned for single-pass launches only");
+        if constexpr (PASSES <= 2) return kb == 2 ? launch_mma<PASSES, 512, 2>(a, st) : launch_mma<PASSES, 256, 4>(a, st);
+        return fail(MSAQ_ERR_ARG, "several K blocks per stage are planned for launches of up to two passes only");
     }
     switch (a.sch.tc) {
         case 128: return launch_mma<PASSES, 128>(a, st);
