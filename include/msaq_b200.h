@@ -55,11 +55,30 @@ unsigned long long msaq_launch_count(void);
  *   reads or writes anything another kernel produces or consumes.
  * MSAQ_OPT_TENSOR_MEMORY (default 1): batched GEMVs (u=4, gs=2, 9 rows and more) run on the tcgen05 tensor
  *   cores with accumulators in tensor memory; 0 keeps them on the warp-level integer MMA path (the two paths
- *   agree to the output tolerance, not bit for bit). */
+ *   agree to the output tolerance, not bit for bit).
+ * MSAQ_OPT_WAIT_POLLS (default 2^20): poll limit of every wait on a shared-memory barrier inside the pipelined
+ *   kernels.  A wait that reaches it gives up: the kernel finishes by itself, the outputs the wait fed become
+ *   NaN, and a bit is set in the status word msaq_wait_status() reads.
+ * MSAQ_OPT_TEST_SKIP_STAGE (default -1 = off; a test hook, not for production): the copy-issuing thread of
+ *   the first thread block of the pipelined GEMV / flash-decode kernels stops before this pipeline stage, so
+ *   that the wait for it runs out.  Used to check the give-up path without faulting or hanging anything. */
 #define MSAQ_OPT_CHAINED_LAUNCH 1
 #define MSAQ_OPT_TENSOR_MEMORY 2
+#define MSAQ_OPT_WAIT_POLLS 3
+#define MSAQ_OPT_TEST_SKIP_STAGE 4
 int msaq_set_option(int option, int value);
 int msaq_get_option(int option);
+
+/* Status word of the current device (no reference counterpart; the reference's kernels have no waits that can
+ * give up).  Bits: 1 = a wait gave up in the integer-MMA GEMV, 2 = in the tensor-memory GEMV, 4 = in the
+ * flash-decode kernel, 8 = an append position read from device memory was outside [0, Lcap) and the row was
+ * skipped.  The call synchronises `stream`, stores the word in *status_out and, when clear != 0, resets it.
+ * Do not call it while `stream` is being captured. */
+#define MSAQ_STATUS_WAIT_GEMV 1
+#define MSAQ_STATUS_WAIT_GEMV_TM 2
+#define MSAQ_STATUS_WAIT_KV_DECODE 4
+#define MSAQ_STATUS_BAD_APPEND_POS 8
+int msaq_wait_status(int clear, void* stream, int* status_out);
 
 /* ------------------------------------------------------------------ GEMV -- */
 
@@ -108,6 +127,8 @@ int msaq_wonly_gemv_batched(const void* X, const int8_t* scale_exp, const uint8_
  * rmsnorm(v) = v * rsqrt(mean(v^2) + eps), no gain vector.  Each intermediate is rounded to bf16 exactly as the
  * separate entry points msaq_rmsnorm / msaq_silu_mul / msaq_add_residual round it.  Column-major planes, any
  * (u, gs); formats outside the tuned path run the glue as separate kernels into the workspace tail.
+ * h_out must not overlap x or addend (MSAQ_ERR_ARG): there is no in-place residual update.
+ * A non-finite activation (Inf or NaN) turns its whole output row into NaN.
  */
 #define MSAQ_PRO_NONE 0
 #define MSAQ_PRO_RMSNORM 1

@@ -19,6 +19,7 @@ SIGNATURES = {
     "msaq_launch_count": (C.c_ulonglong, []),
     "msaq_set_option": (_int, [_int, _int]),
     "msaq_get_option": (_int, [_int]),
+    "msaq_wait_status": (_int, [_int, _p, C.POINTER(C.c_int)]),
     "msaq_wonly_gemv_workspace": (_sz, [_i64, _i64, _i64, _int, _int]),
     "msaq_wonly_gemv": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _int, _int, _p, _sz, _p]),
     "msaq_wonly_gemv_wide": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _int, _int, _p, _sz, _p]),

@@ -33,7 +33,33 @@ int check_launch(const char* what) {
 namespace {
 std::atomic<int> g_opt_chained{-1};
 std::atomic<int> g_opt_tmem{1};
+std::atomic<int> g_opt_polls{1 << 20};
+std::atomic<int> g_opt_skip{-1};
+
+// One status word per GPU that loads the library: kernels OR a bit into it when a bounded wait
+// gives up or an append position is out of range; msaq_wait_status() reads and clears it.
+__device__ int g_sticky_status;
+std::atomic<int*> g_sticky_ptr[64];
 }  // namespace
+
+unsigned option_wait_polls() { return (unsigned)g_opt_polls.load(std::memory_order_relaxed); }
+int option_test_skip_stage() { return g_opt_skip.load(std::memory_order_relaxed); }
+
+int* sticky_status() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    int* p = g_sticky_ptr[dev].load(std::memory_order_acquire);
+    if (!p) {
+        void* q = nullptr;
+        if (cudaGetSymbolAddress(&q, g_sticky_status) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        p = static_cast<int*>(q);
+        g_sticky_ptr[dev].store(p, std::memory_order_release);
+    }
+    return p;
+}
 
 bool option_chained_launch() {
     int v = g_opt_chained.load(std::memory_order_relaxed);
@@ -87,6 +113,11 @@ extern "C" int msaq_set_option(int option, int value) {
     switch (option) {
         case MSAQ_OPT_CHAINED_LAUNCH: msaq::g_opt_chained.store(value ? 1 : 0, std::memory_order_relaxed); return MSAQ_OK;
         case MSAQ_OPT_TENSOR_MEMORY: msaq::g_opt_tmem.store(value ? 1 : 0, std::memory_order_relaxed); return MSAQ_OK;
+        case MSAQ_OPT_WAIT_POLLS:
+            if (value < 1) return msaq::fail(MSAQ_ERR_ARG, "the poll limit must be positive");
+            msaq::g_opt_polls.store(value, std::memory_order_relaxed);
+            return MSAQ_OK;
+        case MSAQ_OPT_TEST_SKIP_STAGE: msaq::g_opt_skip.store(value < 0 ? -1 : value, std::memory_order_relaxed); return MSAQ_OK;
         default: return msaq::fail(MSAQ_ERR_ARG, "unknown option %d", option);
     }
 }
@@ -94,7 +125,23 @@ extern "C" int msaq_get_option(int option) {
     switch (option) {
         case MSAQ_OPT_CHAINED_LAUNCH: return msaq::option_chained_launch() ? 1 : 0;
         case MSAQ_OPT_TENSOR_MEMORY: return msaq::option_tensor_memory() ? 1 : 0;
+        case MSAQ_OPT_WAIT_POLLS: return (int)msaq::option_wait_polls();
+        case MSAQ_OPT_TEST_SKIP_STAGE: return msaq::option_test_skip_stage();
         default: return msaq::fail(MSAQ_ERR_ARG, "unknown option %d", option);
     }
 }
 extern "C" unsigned long long msaq_launch_count(void) { return msaq::g_launches.load(std::memory_order_relaxed); }
+
+extern "C" int msaq_wait_status(int clear, void* stream, int* status_out) {
+    if (!status_out) return msaq::fail(MSAQ_ERR_ARG, "null pointer");
+    int* p = msaq::sticky_status();
+    if (!p) return msaq::fail(MSAQ_ERR_CUDA, "the status word of the current device cannot be located");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int v = 0;
+    cudaError_t e = cudaMemcpyAsync(&v, p, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess && clear) e = cudaMemsetAsync(p, 0, sizeof(int), st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return msaq::fail(MSAQ_ERR_CUDA, "reading the status word: %s", cudaGetErrorString(e));
+    *status_out = v;
+    return MSAQ_OK;
+}

@@ -161,7 +161,7 @@ int run_umma(const __nv_bfloat16* X, const int8_t* se, const uint8_t* up, const 
         if (int rc = check_launch("gemv_umma_xprep")) return rc;
         const GemvSchedule sch = p.sch;
         const int smem = sch.stages * gu_stage(u) + GU_ABUFS * GU_ABUF_BYTES;
-        GemvUmmaArgs a{se, up, sh, base, partial, status, static_cast<__nv_bfloat16*>(Y), Yf, (int)m0, rows, (int)OUT, sch};
+        GemvUmmaArgs a{se, up, sh, base, partial, status, sticky_status(), static_cast<__nv_bfloat16*>(Y), Yf, (int)m0, rows, (int)OUT, sch};
         const int rc = u == 4 ? launch_umma<4>(a, smem, st) : u == 3 ? launch_umma<3>(a, smem, st) : launch_umma<2>(a, smem, st);
         if (rc) return rc;
         // every CTA boundary on a tile boundary: all tiles were written directly; otherwise some tile has partials
@@ -226,8 +226,8 @@ int run_mma(const __nv_bfloat16* X, const Prologue& pro, const int8_t* se, const
         xa.r_is_f32 = pro.r_is_f32;
         xa.eps = pro.eps;
         if (int rc = launch_xprep(xa, pro.mode, (unsigned)((warps * 32 + 127) / 128), st)) return rc;
-        GemvMmaArgs a{se, up, sh, base, partial, counters, status, static_cast<__nv_bfloat16*>(Y), Yf,
-                      (int)m0, rows, (int)OUT, (int)NB, p.sch};
+        GemvMmaArgs a{se, up, sh, base, partial, counters, status, sticky_status(), static_cast<__nv_bfloat16*>(Y), Yf,
+                      (int)m0, rows, (int)OUT, (int)NB, p.sch, option_wait_polls(), option_test_skip_stage()};
         // the ring depth was planned for the first tile's pass count; a last, smaller tile may go deeper but need not
         int rc;
         switch (passes) {
@@ -341,6 +341,15 @@ extern "C" int msaq_wonly_gemv_fused(const void* x, int prologue, const void* ad
     if (prologue == MSAQ_PRO_ADD_RMSNORM && (!addend || !h_out))
         return fail(MSAQ_ERR_ARG, "the add+rmsnorm prologue needs an addend and h_out");
     if (M <= 0 || OUT <= 0 || NB <= 0) return fail(MSAQ_ERR_ARG, "M, OUT and NB must be positive");
+    if (prologue == MSAQ_PRO_ADD_RMSNORM) {
+        // Every thread block re-reads whole rows of x and addend for the row norm while others write h_out:
+        // an in-place update would let some of them see the sum already applied.
+        const uintptr_t h0 = reinterpret_cast<uintptr_t>(h_out), h1 = h0 + (size_t)M * NB * BLOCK * 2;
+        const uintptr_t x0 = reinterpret_cast<uintptr_t>(x), x1 = x0 + (size_t)M * NB * BLOCK * 2;
+        const uintptr_t a0 = reinterpret_cast<uintptr_t>(addend), a1 = a0 + (size_t)M * NB * BLOCK * (addend_is_f32 ? 4 : 2);
+        if ((h0 < x1 && x0 < h1) || (h0 < a1 && a0 < h1))
+            return fail(MSAQ_ERR_ARG, "h_out must not overlap x or addend (no in-place residual update)");
+    }
     if (M > INT32_MAX || OUT > INT32_MAX || NB * BLOCK > INT32_MAX / 2) return fail(MSAQ_ERR_ARG, "size exceeds 2^31");
     if (int rc = require_sm100()) return rc;
     const size_t need = msaq_wonly_gemv_fused_workspace(M, OUT, NB, u, gs);

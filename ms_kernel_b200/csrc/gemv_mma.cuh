@@ -212,7 +212,8 @@ gemv_xprep_kernel(const XprepArgs a) {
     if (lane == 0) {
         int* tc = reinterpret_cast<int*>(rec + 256 + mm * 16);
         tc[0] = -8 * (sh * 256 + sl);                         // correction for the offset-binary shared codes
-        tc[1] = (int)((uint32_t)(E - 14 + 127) << 23);        // 2^(E-14) as float bits
+        // 2^(E-14) as float bits; an Inf or NaN in the block makes the multiplier NaN, and with it the output row
+        tc[1] = ax >= 0x7F800000u ? 0x7FC00000 : (int)((uint32_t)(E - 14 + 127) << 23);
         tc[2] = 0;
         tc[3] = 0;
     }
@@ -227,12 +228,15 @@ struct GemvMmaArgs {
     float* partial;          // [max_slots][rows][OUT]
     int* tile_counters;      // [col_tiles], zeroed by the staging kernel
     int* status;             // set to 1 when a bounded wait gave up
+    int* sticky;             // the library's per-device status word (may be null)
     __nv_bfloat16* y;        // [M][OUT]
     float* y_f32;            // optional
     int m0, rows;            // this launch covers rows [m0, m0 + rows), rows <= 16
     int OUT;
     int NB;                  // K blocks of the weight (sch.nb counts units: groups of KB blocks)
     GemvSchedule sch;
+    uint32_t max_polls;      // limit of every mbarrier wait (see mbar_wait_bounded)
+    int skip_stage;          // test hook: the producer of CTA 0 stops before this stage (-1: never)
 };
 
 // One 16-column x 32-element step of a warp: decode both columns' codes into the
@@ -318,13 +322,16 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
         // ------------------------------ producer ------------------------------
         if (lane == 0) {
             chain_wait();                          // the staged activations come from the kernel before this one
-            int s = 0;
+            int s = 0, issued = 0;
             uint32_t ph = 1;                       // parity of the "previous" empty phase: passes at once on a fresh barrier
+            const bool inject = a.skip_stage >= 0 && blockIdx.x == 0;
             for (int it = 0; it < n_iter; ++it) {
-                if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ph)) {
-                    atomicExch(a.status, 1);
+                if (inject && it == a.skip_stage) break;          // the consumers' wait for this stage runs out
+                if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ph, a.max_polls)) {
+                    report_wait_failure(a.status, a.sticky, WAIT_FAIL_GEMV_MMA);
                     break;
                 }
+                ++issued;
                 const int o0 = c * TC, cv = min(TC, a.OUT - o0);
                 const uint32_t bar = smem_u32(&bar_full[s]);
                 const int b0 = blk * KB, nblk = min(KB, a.NB - b0);         // `blk` counts units within the tile
@@ -343,6 +350,10 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
                 if (++blk == sch.nb) { blk = 0; ++c; }
                 if (++s == sch.stages) { s = 0; ph ^= 1u; }
             }
+            // Leave only when every copy this thread issued has landed: shared memory must not be
+            // handed to the next CTA with a copy still in flight (consumers that gave up do not wait).
+            for (int i = max(0, issued - sch.stages); i < issued; ++i)
+                mbar_wait_bounded(smem_u32(&bar_full[i % sch.stages]), (uint32_t)(i / sch.stages) & 1u, a.max_polls);
         }
         return;
     }
@@ -363,16 +374,17 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
     for (int q = 0; q < GROUPS; ++q)
 #pragma unroll
         for (int p = 0; p < PASSES; ++p) acc[q][p][0] = acc[q][p][1] = 0.0f;
-    // A wait that gives up marks the warp aborted: it stops waiting and computing,
-    // still releases its stages, and publishes nothing (the status word is set).
+    // A wait that gives up marks the warp aborted: it sets the status word, stops waiting and
+    // computing, still releases its stages and still takes part in the tile hand-off, where its
+    // outputs become NaN (directly, or through the status word the finishing warp reads).
     bool aborted = false;
     chain_wait();
 
     int s = 0;
     uint32_t ph = 0;
     for (int it = 0; it < n_iter; ++it) {
-        if (!aborted && !mbar_wait_bounded(smem_u32(&bar_full[s]), ph)) {
-            atomicExch(a.status, 1);
+        if (!aborted && !mbar_wait_bounded(smem_u32(&bar_full[s]), ph, a.max_polls)) {
+            report_wait_failure(a.status, a.sticky, WAIT_FAIL_GEMV_MMA);
             aborted = true;
         }
         const int cv = min(TC, a.OUT - c * TC);
@@ -412,7 +424,14 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
             const int first = sch.first_cta(c), nslots = sch.last_cta(c) - first + 1;
             const int slot = blockIdx.x - first, o0 = c * TC;
             const int nq = (cv - warp * 16 + GM_GROUP - 1) / GM_GROUP;     // groups in which this warp has columns
-            if (nq > 0 && !aborted) {
+            if (aborted) {
+                const float nan = __int_as_float(0x7FC00000);
+#pragma unroll
+                for (int q = 0; q < GROUPS; ++q)
+#pragma unroll
+                    for (int p = 0; p < PASSES; ++p) acc[q][p][0] = acc[q][p][1] = nan;
+            }
+            if (nq > 0) {
                 if (nslots == 1) {
 #pragma unroll
                     for (int q = 0; q < GROUPS; ++q) {

@@ -271,6 +271,7 @@ struct GemvUmmaArgs {
     const uint8_t* xs;       // staged activation tiles [NB][gu_xtile_bytes(rows)]
     float* partial;          // [max_slots][rows][OUT]
     int* status;
+    int* sticky;             // the library's per-device status word (may be null)
     __nv_bfloat16* y;        // [M][OUT]
     float* y_f32;            // optional
     int m0, rows;            // this launch covers activation rows [m0, m0 + rows), rows <= 128
@@ -352,7 +353,7 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
         for (int it = 0; it < n_iter; ++it) {
             bool stop = abort_flag != 0;
             if (!stop && !mbar_wait_bounded(smem_u32(&bar_empty[s]), ph)) {
-                atomicExch(a.status, 1);
+                report_wait_failure(a.status, a.sticky, WAIT_FAIL_GEMV_UMMA);
                 abort_flag = 1;
                 stop = true;
             }
@@ -385,7 +386,7 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
                 bool ok = mbar_wait_bounded(smem_u32(&bar_afull[buf]), (aph >> buf) & 1u);
                 if (ok && fresh) ok = mbar_wait_bounded(smem_u32(&bar_accempty), accph);
                 if (!ok) {
-                    atomicExch(a.status, 1);
+                    report_wait_failure(a.status, a.sticky, WAIT_FAIL_GEMV_UMMA);
                     abort_flag = 1;
                     break;
                 }
@@ -431,7 +432,7 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
             const int cv = min(GU_TR, a.OUT - o0);
             if (!aborted && abort_flag) aborted = true;
             if (!aborted && !mbar_wait_bounded(smem_u32(&bar_accfull), accfph)) {
-                atomicExch(a.status, 1);
+                report_wait_failure(a.status, a.sticky, WAIT_FAIL_GEMV_UMMA);
                 abort_flag = 1;
                 aborted = true;
             }
@@ -498,7 +499,7 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
                 bool ok = mbar_wait_bounded(smem_u32(&bar_full[s]), ph);
                 ok = ok && mbar_wait_bounded(smem_u32(&bar_aempty[buf]), (aeph >> bsel) & 1u);
                 if (!ok) {
-                    atomicExch(a.status, 1);
+                    report_wait_failure(a.status, a.sticky, WAIT_FAIL_GEMV_UMMA);
                     abort_flag = 1;
                     aborted = true;
                 }
@@ -530,7 +531,7 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
     __syncthreads();
     if (warp >= GU_WARP_MMA && lane == 0) tc_commit(smem_u32(&bar_done));   // arrives once this issuer's MMAs have completed
     if (warp == GU_WARP_MMA) {
-        if (lane == 0 && !mbar_wait_bounded(smem_u32(&bar_done), 0)) atomicExch(a.status, 1);
+        if (lane == 0 && !mbar_wait_bounded(smem_u32(&bar_done), 0)) report_wait_failure(a.status, a.sticky, WAIT_FAIL_GEMV_UMMA);
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, tmem_cols);

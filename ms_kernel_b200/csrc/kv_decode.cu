@@ -83,8 +83,9 @@ int run_mma(const __nv_bfloat16* q, KvPlanes kp, KvPlanes vp, void* out, float* 
     const KvMmaPlan p = plan_mma(B, H, Hkv, Lk);
     uint8_t* base = static_cast<uint8_t*>(ws);
     int* status = reinterpret_cast<int*>(base + p.status_off);
-    KvMmaArgs a{q, kp, vp, reinterpret_cast<float*>(base), seq_lens, status, (int)H, (int)Hkv, (int)Lk, (int)Lcap,
-                p.key_tile, p.S, qrot, (float)(1.4426950408889634 / sqrt(128.0))};
+    KvMmaArgs a{q, kp, vp, reinterpret_cast<float*>(base), seq_lens, status, sticky_status(), (int)H, (int)Hkv, (int)Lk,
+                (int)Lcap, p.key_tile, p.S, qrot, (float)(1.4426950408889634 / sqrt(128.0)), option_wait_polls(),
+                option_test_skip_stage()};
     int rc;
     switch (H / Hkv) {
         case 1: rc = launch_kv_mma<1>(a, p.S, (int)Hkv, (int)B, st); break;

@@ -37,6 +37,7 @@ constexpr int KVM_K_UP = 0, KVM_K_SH = 4 * KVM_UP, KVM_K_SC = KVM_K_SH + 4 * KVM
 constexpr int KVM_V_UP = KVM_K_SC + 4 * KVM_SC, KVM_V_SH = KVM_V_UP + 4 * KVM_UP, KVM_V_SC = KVM_V_SH + 4 * KVM_SH;
 constexpr int KVM_STAGE_BYTES = KVM_V_SC + 4 * KVM_SC;            // 25600
 constexpr int KVM_QREC = 320;               // staged query record per (block, pass); layout as in gemv_mma.cuh
+constexpr float KVM_SPLIT_TAU = 0.015625f;  // 2^-6: boundary between the big and the small keys of a split chunk
 constexpr int KVM_PSTRIDE = 40;             // floats per head row of the probability exchange buffer
 constexpr int KVM_OFF_Q = KVM_STAGES * KVM_STAGE_BYTES;
 constexpr int KVM_OFF_P = KVM_OFF_Q + 4 * 2 * KVM_QREC;
@@ -49,8 +50,11 @@ struct KvMmaArgs {
     float* partial;             // [B][Hq][S][130]
     const int32_t* seq_lens;    // optional
     int* status;
+    int* sticky;                // the library's per-device status word (may be null)
     int Hq, Hkv, Lk, Lcap, key_tile, S, qrot;
     float sm_scale_log2;        // log2(e) / sqrt(D)
+    uint32_t max_polls;         // limit of every mbarrier wait (see mbar_wait_bounded)
+    int skip_stage;             // test hook: the producer of CTA (0,0,0) stops before this stage (-1: never)
 };
 
 template <int G>
@@ -86,11 +90,15 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
             int s = 0;
             uint32_t ph = 1;
             const int64_t head_row = ((int64_t)b * a.Hkv + hk) * 4;
+            const bool inject = a.skip_stage >= 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0;
+            int issued = 0;
             for (int it = 0; it < n_stage; ++it) {
-                if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ph)) {
-                    atomicExch(a.status, 1);
+                if (inject && it == a.skip_stage) break;               // the consumers' wait for this stage runs out
+                if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ph, a.max_polls)) {
+                    report_wait_failure(a.status, a.sticky, WAIT_FAIL_KV_DECODE);
                     break;
                 }
+                ++issued;
                 const int j = j0 + it * KVM_TK;
                 const int nk = min(KVM_TK, (j1 - j + 15) & ~15);       // whole 16-key groups (capacity is a multiple of 16)
                 const uint32_t bar = smem_u32(&bar_full[s]);
@@ -108,6 +116,10 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
                 }
                 if (++s == KVM_STAGES) { s = 0; ph ^= 1u; }
             }
+            // Leave only when every copy this thread issued has landed: shared memory must not be
+            // handed to the next CTA with a copy still in flight (consumers that gave up do not wait).
+            for (int i = max(0, issued - KVM_STAGES); i < issued; ++i)
+                mbar_wait_bounded(smem_u32(&bar_full[i % KVM_STAGES]), (uint32_t)(i / KVM_STAGES) & 1u, a.max_polls);
         }
         return;
     }
@@ -151,7 +163,8 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
         if ((lane & 7) == 0) {
             int* tc = reinterpret_cast<int*>(rec + 256 + mm * 16);
             tc[0] = -8 * sum;
-            tc[1] = __float_as_int(ldexpf(a.sm_scale_log2, E - 14));     // scores come out in the exp2 domain
+            // scores come out in the exp2 domain; an Inf or NaN in the query block makes the head's output NaN
+            tc[1] = ax >= 0x7F800000u ? 0x7FC00000 : __float_as_int(ldexpf(a.sm_scale_log2, E - 14));
         }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(KVM_WARPS * 32) : "memory");
@@ -175,8 +188,8 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
     int s = 0;
     uint32_t ph = 0;
     for (int it = 0; it < n_stage; ++it) {
-        if (!aborted && !mbar_wait_bounded(smem_u32(&bar_full[s]), ph)) {
-            atomicExch(a.status, 1);
+        if (!aborted && !mbar_wait_bounded(smem_u32(&bar_full[s]), ph, a.max_polls)) {
+            report_wait_failure(a.status, a.sticky, WAIT_FAIL_KV_DECODE);
             aborted = true;
         }
         const uint32_t so = sb + s * KVM_STAGE_BYTES;
@@ -230,7 +243,15 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
                 }
             }
             // ---- online softmax (exp2 domain); thread (g,t): head 4p+t, keys ck + {g, g+8, 16+g, 24+g} ----
-            float alpha[PASSES];
+            // Probabilities are taken relative to the CHUNK's own maximum (so the 16-bit fixed point of
+            // the P.V operand always spans the chunk's largest key) and the factor 2^(chunk max -
+            // running max) is applied in fp32 to the chunk's integer result: a chunk far below an
+            // earlier dominant key keeps its full relative precision.
+            // A chunk whose probabilities fall into a "big" set (within 2^-6 of the chunk maximum, e.g. an
+            // attention sink) and a "small" set whose sum is itself below 2^-6 would leave the small keys
+            // under the resolution of the 16-bit operand.  Such a chunk (split[p] > 0, rare) takes two P.V
+            // passes: the small keys relative to their own sum, then the big keys relative to the maximum.
+            float alpha[PASSES], beta[PASSES], split[PASSES];
 #pragma unroll
             for (int p = 0; p < PASSES; ++p) {
                 float mx = -INFINITY;
@@ -246,18 +267,25 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
                 const float m_new = fmaxf(m_run[p], mx);
                 const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
                 alpha[p] = exp2f(m_run[p] - m_use);                                          // 0 when nothing was seen before
-                float ps = 0.0f;
+                const float mc = (mx == -INFINITY) ? 0.0f : mx;                              // the chunk's own maximum
+                beta[p] = (mx == -INFINITY) ? 0.0f : exp2f(mx - m_use);
+                float ps = 0.0f, psm = 0.0f;
 #pragma unroll
                 for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
                     for (int r = 0; r < 2; ++r) {
-                        const float pv = exp2f(S[p][mt][r] - m_use);
+                        const float pv = exp2f(S[p][mt][r] - mc);
                         ps += pv;
+                        psm += (pv < KVM_SPLIT_TAU) ? pv : 0.0f;
                         Pw[(4 * p + t) * KVM_PSTRIDE + mt * 16 + r * 8 + g] = pv;
                     }
 #pragma unroll
-                for (int o = 4; o <= 16; o <<= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
-                l_run[p] = l_run[p] * alpha[p] + ps;
+                for (int o = 4; o <= 16; o <<= 1) {
+                    ps += __shfl_xor_sync(0xffffffffu, ps, o);
+                    psm += __shfl_xor_sync(0xffffffffu, psm, o);
+                }
+                split[p] = (psm > 0.0f && psm < KVM_SPLIT_TAU) ? psm : 0.0f;
+                l_run[p] = fmaf(l_run[p], alpha[p], ps * beta[p]);
                 m_run[p] = m_new;
             }
             // ---- value scales of the chunk: E_max per block, and 2^-(E_max - e) per key ----
@@ -273,9 +301,17 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
             __syncwarp();
             // rescale of the running output of head g (PV layout) by that head's alpha
             float al = __shfl_sync(0xffffffffu, alpha[0], g & 3);
+            float be = __shfl_sync(0xffffffffu, beta[0], g & 3);      // head g's chunk factor, PV layout
             if (PASSES > 1) {
                 const float al1 = __shfl_sync(0xffffffffu, alpha[PASSES - 1], g & 3);
+                const float be1 = __shfl_sync(0xffffffffu, beta[PASSES - 1], g & 3);
                 al = (g < 4) ? al : al1;
+                be = (g < 4) ? be : be1;
+            }
+            float sa = __shfl_sync(0xffffffffu, split[0], g & 3);     // head g's small-set sum when its chunk is split
+            if (PASSES > 1) {
+                const float sa1 = __shfl_sync(0xffffffffu, split[PASSES - 1], g & 3);
+                sa = (g < 4) ? sa : sa1;
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i)
@@ -293,9 +329,26 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) pf[i] = 0.0f;
             }
+            if (G < 8 && g >= G) sa = 0.0f;
+            const bool is_split = sa > 0.0f;
+            const int n_pv = __any_sync(0xffffffffu, is_split) ? 2 : 1;
+            const float sa_inv = is_split ? __frcp_rn(sa) : 1.0f;
             // ---- P.V: per block 4 n-tiles of 8 channels (+ one all-ones MMA for the code offset) ----
             const int lrow = lane & 15;
             const int vkey = 8 * (lrow >> 2) + 2 * (lrow & 3) + (lane >> 4);      // even keys -> matrix 0, odd -> matrix 1
+#pragma unroll 1
+            for (int pvp = 0; pvp < n_pv; ++pvp) {
+            float pq[8];                         // this pass's probabilities and their common factor
+            float bsc;
+            if (pvp == 0) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) pq[i] = is_split ? (pf[i] < KVM_SPLIT_TAU ? pf[i] * sa_inv : 0.0f) : pf[i];
+                bsc = is_split ? be * sa : be;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) pq[i] = (is_split && pf[i] >= KVM_SPLIT_TAU) ? pf[i] : 0.0f;
+                bsc = be;
+            }
 #pragma unroll
             for (int blk = 0; blk < 4; ++blk) {
                 // P' = p * 2^(e - E_max) as u16, bytes split into the hi (row g) and lo (row g+8) operand planes
@@ -305,7 +358,7 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
                     const float4 r1 = *reinterpret_cast<const float4*>(Rw + blk * 32 + 8 * t + 4);
                     const float rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) pv16[i] = __float2uint_rn(pf[i] * rr[i] * 65535.0f);
+                    for (int i = 0; i < 8; ++i) pv16[i] = __float2uint_rn(fminf(pq[i] * rr[i], 1.0f) * 65535.0f);
                 }
                 uint32_t PA[4];
                 {
@@ -332,7 +385,7 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
                     mma_u8s8_16832_z(Dc, PA, ones);
                 }
                 const int corr = -8 * (Dc[0] * 256 + Dc[2]);                   // every shared code carries +8
-                const float osc = __int_as_float((emax[blk] + 127) << 23) * (1.0f / 65535.0f);
+                const float osc = __int_as_float((emax[blk] + 127) << 23) * (1.0f / 65535.0f) * bsc;
                 // n-tile 0: channel 2n+1 (high nibbles of byte column g), 1: channel 2n, 2: 17+2n, 3: 16+2n
 #pragma unroll
                 for (int n = 0; n < 4; ++n) {
@@ -346,6 +399,7 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
                     acc[blk][n][0] = fmaf((float)(Dv[0] * 256 + Dv[2] + corr), osc, acc[blk][n][0]);
                     acc[blk][n][1] = fmaf((float)(Dv[1] * 256 + Dv[3] + corr), osc, acc[blk][n][1]);
                 }
+            }
             }
         }
         __syncwarp();
@@ -362,7 +416,7 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
         for (int p = 0; p < PASSES; ++p) {
             const int hh = 4 * p + t;
             if (hh < G) {
-                mb[(warp * G + hh) * 130 + 128] = m_run[p];
+                mb[(warp * G + hh) * 130 + 128] = aborted ? __int_as_float(0x7FC00000) : m_run[p];   // NaN marks a warp that gave up
                 mb[(warp * G + hh) * 130 + 129] = l_run[p];
             }
         }
@@ -384,16 +438,21 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
     for (int idx = tid; idx < G * 130; idx += KVM_WARPS * 32) {
         const int hh = idx / 130, d = idx % 130;
         float mg = -INFINITY;
+        bool bad = false;
 #pragma unroll
-        for (int w = 0; w < KVM_WARPS; ++w) mg = fmaxf(mg, mb[(w * G + hh) * 130 + 128]);
+        for (int w = 0; w < KVM_WARPS; ++w) {
+            const float mw = mb[(w * G + hh) * 130 + 128];
+            bad = bad || (mw != mw);
+            mg = fmaxf(mg, mw);                                                // fmaxf ignores the NaN
+        }
         float r;
-        if (d == 128) r = aborted ? __int_as_float(0x7FC00000) : mg;
+        if (d == 128) r = bad ? __int_as_float(0x7FC00000) : mg;
         else {
             r = 0.0f;
 #pragma unroll
             for (int w = 0; w < KVM_WARPS; ++w) {
                 const float mw = mb[(w * G + hh) * 130 + 128];
-                const float wgt = (mw == -INFINITY) ? 0.0f : exp2f(mw - mg);
+                const float wgt = (mw == -INFINITY || mw != mw) ? 0.0f : exp2f(mw - mg);
                 r = fmaf(mb[(w * G + hh) * 130 + (d == 129 ? 129 : d)], wgt, r);
             }
         }

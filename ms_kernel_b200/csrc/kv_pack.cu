@@ -21,6 +21,7 @@ struct RowMap {
     int64_t Lcap;            // key stride of the planes
     const int32_t* pos;      // optional per-sequence slot (varlen append)
     int64_t heads_per_seq;   // Hkv, used with pos
+    int* sticky;             // the library's per-device status word: bit BAD_APPEND_POS when a pos[] entry is out of range
 };
 
 // 2^k as a double, k in [-1022, 1023].
@@ -73,7 +74,15 @@ quantize_rows_kernel(const QuantJobs jobs, RowMap map, Fmt f) {
 
     const int64_t head = row / map.rows_per_head;
     int64_t key = map.key0 + row % map.rows_per_head;
-    if (map.pos) key = map.pos[head / map.heads_per_seq];
+    if (map.pos) {
+        // A position that comes from device memory cannot be checked by the host: a stale or negative
+        // entry must not write outside the planes.  The row is skipped and the status word says so.
+        key = map.pos[head / map.heads_per_seq];
+        if (key < 0 || key >= map.Lcap) {
+            if (lane == 0 && map.sticky) atomicOr(map.sticky, BAD_APPEND_POS);
+            return;
+        }
+    }
     const int lim = (1 << (7 - f.u)) - 1, slo = -(1 << (f.u - 1)), shi = (1 << (f.u - 1)) - 1;
     const int g0 = lane & ~(f.gs - 1);                        // first lane of this lane's group
 
@@ -230,13 +239,13 @@ using namespace msaq;
 
 extern "C" int msaq_kv_append(const void* X, int8_t* scale_exp, uint8_t* upper, uint8_t* shared, int64_t H,
                               int64_t D, int64_t NB, int64_t pos, int64_t Lcap, int u, int gs, void* stream) {
-    RowMap m{H, 1, pos, Lcap, nullptr, 1};
+    RowMap m{H, 1, pos, Lcap, nullptr, 1, nullptr};
     return quantize_rows(X, scale_exp, upper, shared, m, D, NB, u, gs, false, stream);
 }
 
 extern "C" int msaq_kv_append_rot(const void* X, int8_t* scale_exp, uint8_t* upper, uint8_t* shared, int64_t H,
                                   int64_t D, int64_t NB, int64_t pos, int64_t Lcap, int u, int gs, void* stream) {
-    RowMap m{H, 1, pos, Lcap, nullptr, 1};
+    RowMap m{H, 1, pos, Lcap, nullptr, 1, nullptr};
     return quantize_rows(X, scale_exp, upper, shared, m, D, NB, u, gs, true, stream);
 }
 
@@ -245,7 +254,7 @@ extern "C" int msaq_kv_append_varlen(const void* X, int8_t* scale_exp, uint8_t* 
                                      int gs, int rotate, void* stream) {
     if (!pos) return fail(MSAQ_ERR_ARG, "pos is null");
     if (Hkv <= 0) return fail(MSAQ_ERR_ARG, "Hkv must be positive");
-    RowMap m{B * Hkv, 1, 0, Lcap, pos, Hkv};
+    RowMap m{B * Hkv, 1, 0, Lcap, pos, Hkv, sticky_status()};
     return quantize_rows(X, scale_exp, upper, shared, m, D, NB, u, gs, rotate != 0, stream);
 }
 
@@ -256,7 +265,7 @@ extern "C" int msaq_kv_append_pair(const void* Xk, const void* Xv, int8_t* k_sca
     if (!Xk || !Xv || !k_scale_exp || !k_upper || !k_shared || !v_scale_exp || !v_upper || !v_shared)
         return fail(MSAQ_ERR_ARG, "null pointer");
     if (B <= 0 || Hkv <= 0) return fail(MSAQ_ERR_ARG, "B and Hkv must be positive");
-    RowMap m{B * Hkv, 1, pos_per_seq ? 0 : pos, Lcap, pos_per_seq, Hkv};
+    RowMap m{B * Hkv, 1, pos_per_seq ? 0 : pos, Lcap, pos_per_seq, Hkv, pos_per_seq ? sticky_status() : nullptr};
     Fmt f;
     if (int rc = check_rows(m, D, NB, u, gs, &f)) return rc;
     QuantJobs jobs{};

@@ -42,6 +42,9 @@ int sm_count();               // SM count of the current device (cached per devi
 int require_sm100();          // MSAQ_OK or MSAQ_ERR_DEVICE
 bool option_chained_launch(); // kernels are launched with programmatic stream serialisation
 bool option_tensor_memory();  // batched GEMVs of 9 rows and more run on tcgen05 with tensor-memory accumulators
+unsigned option_wait_polls(); // poll limit of the bounded mbarrier waits
+int option_test_skip_stage(); // test hook: pipeline stage whose copy the first CTA's producer leaves out (-1: none)
+int* sticky_status();         // device address of the per-device status word on the current device (null on failure)
 
 // Launch `kernel` so that it may begin while the previous kernel in the stream drains (see
 // chain_wait / chain_release): every kernel of this library executes chain_wait() before it

@@ -56,13 +56,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait: gives up after a fixed number of polls and reports failure, so
 // that a lost copy can never hang the GPU.  Returns true when the phase completed.
 constexpr uint32_t MBAR_FAST_POLLS = 2048;
-constexpr uint32_t MBAR_MAX_POLLS = 1u << 20;
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < MBAR_MAX_POLLS; ++i) {
+constexpr uint32_t MBAR_MAX_POLLS = 1u << 20;          // default limit; the host passes option_wait_polls()
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t max_polls = MBAR_MAX_POLLS) {
+    for (uint32_t i = 0; i < max_polls; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (i >= MBAR_FAST_POLLS) __nanosleep(128);
     }
     return false;
+}
+
+// A wait gave up: mark this call's status word (the finishing code turns the outputs into NaN) and
+// OR `bit` into the library's sticky per-device word that msaq_wait_status() reports to the host.
+constexpr int WAIT_FAIL_GEMV_MMA = 1, WAIT_FAIL_GEMV_UMMA = 2, WAIT_FAIL_KV_DECODE = 4, BAD_APPEND_POS = 8;
+__device__ __forceinline__ void report_wait_failure(int* status, int* sticky, int bit) {
+    atomicExch(status, 1);
+    if (sticky) atomicOr(sticky, bit);
 }
 
 // TMA bulk copy global -> shared of `bytes` (multiple of 16, both addresses

@@ -391,6 +391,11 @@ Tensor add_residual(const Tensor& h, const Tensor& delta) {
 
 int64_t launch_count() { return (int64_t)msaq_launch_count(); }
 void set_option(int64_t option, int64_t value) { check_rc(msaq_set_option((int)option, (int)value), "set_option"); }
+int64_t wait_status(bool clear) {
+    int v = 0;
+    check_rc(msaq_wait_status(clear ? 1 : 0, at::cuda::getCurrentCUDAStream().stream(), &v), "wait_status");
+    return v;
+}
 int64_t get_option(int64_t option) { return (int64_t)msaq_get_option((int)option); }
 
 }  // namespace
@@ -440,6 +445,7 @@ TORCH_LIBRARY(msaq, m) {
     m.def("launch_count() -> int", &launch_count);
     m.def("set_option(int option, int value) -> ()", &set_option);
     m.def("get_option(int option) -> int", &get_option);
+    m.def("wait_status(bool clear) -> int", &wait_status);
 }
 
 // An importable, otherwise empty Python module: `import ms_cuda` loads this
