@@ -44,14 +44,19 @@ NCU_TRAFFIC = {"kernel": "gemv_u4gs2_mma_kernel", "shape": [28672, 4096], "bytes
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=None, help="default 200 (reference arm: 10)")
+    ap.add_argument("--warmup", type=int, default=None, help="default 20 (reference arm: 2)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-detail", action="store_true")
     ap.add_argument("--case", default=None, choices=["gemv", "kv"],
                     help="run a few launches of one op only (small driver for ncu captures)")
-    return ap.parse_args()
+    a = ap.parse_args()
+    if a.steps is None:
+        a.steps = 200 if a.impl == "ours" else 10
+    if a.warmup is None:
+        a.warmup = 20 if a.impl == "ours" else 2
+    return a
 
 
 def measured_peak():
@@ -102,7 +107,7 @@ class ClockSampler:
                         self._once()
                     except Exception:
                         pass
-                    self._stop.wait(0.002)
+                    self._stop.wait(0.005)
             self._thread = threading.Thread(target=loop, daemon=True)
             self._thread.start()
         return self
@@ -129,26 +134,25 @@ def gemv_bytes(OUT, K, M, u, gs):
     return OUT * (K // 32) * plane_bytes(u, gs) + 2 * K * M + 2 * OUT * M
 
 
-def make_linear(OUT, K, u, gs, seed, dev):
-    """Random bf16 ~N(0, 0.02) weight packed on the device -> resident PackedLinear."""
+def make_pack(OUT, K, u, gs, seed, dev):
+    """Random bf16 ~N(0, 0.02) weight packed on the device -> pack dict holding the column-major planes."""
     import torch
-    from ms_kernel_b200 import ops, pack
+    from ms_kernel_b200 import pack, tp
     g = torch.Generator(device=dev).manual_seed(seed)
-    lin = None
     # pack in row chunks so that the bf16 source never needs more than ~1 GB
     rows = max(1, min(OUT, (512 << 20) // (2 * K)))
     parts = []
     for r0 in range(0, OUT, rows):
         W = (torch.randn((min(rows, OUT - r0), K), generator=g, device=dev) * 0.02).to(torch.bfloat16)
-        parts.append(pack.pack_weight(W, u, gs, device=dev))
-        del W
-    if len(parts) == 1:
-        p = parts[0]
-    else:
-        from ms_kernel_b200 import tp
-        p = tp.concat_rows(parts)
-    lin = ops.PackedLinear(p, dev)
-    return lin
+        p = pack.pack_weight(W, u, gs, device=dev)
+        del p["upper"], p["shared"], W                 # the kernels read the column-major planes only
+        parts.append(p)
+    return parts[0] if len(parts) == 1 else tp.concat_rows(parts)
+
+
+def make_linear(OUT, K, u, gs, seed, dev):
+    from ms_kernel_b200 import ops
+    return ops.PackedLinear(make_pack(OUT, K, u, gs, seed, dev), dev)
 
 
 def graph_time(fns, iters, dev):
@@ -182,33 +186,61 @@ def graph_time(fns, iters, dev):
 # --------------------------------------------------------------------------
 # the layer step
 # --------------------------------------------------------------------------
-class LayerSet:
-    """One rank's share of one decoder layer (weights + KV cache) and its graph."""
+def layer_packs(shape, dev, seed):
+    """One whole decoder layer, packed: the same bytes on every rank that uses the same seed."""
+    d = shape.head_dim
+    dims = {"q": (shape.n_q * d, shape.hidden), "k": (shape.n_kv * d, shape.hidden), "v": (shape.n_kv * d, shape.hidden),
+            "o": (shape.hidden, shape.n_q * d), "gate": (shape.ffn, shape.hidden), "up": (shape.ffn, shape.hidden),
+            "down": (shape.hidden, shape.ffn)}
+    return {name: make_pack(OUT, K, U, GS, seed * 16 + i, dev) for i, (name, (OUT, K)) in enumerate(dims.items())}
 
-    def __init__(self, shape, world, rank, B, dev, seed, all_reduce):
+
+def rope_tables_pos(pos, head_dim, dev):
+    """cos, sin [1, head_dim/2] of one position, as the reference's harness builds them
+    (tests/harness_batchsweep.py:124-129, theta = 500000)."""
+    import torch
+    inv = 1.0 / (500000.0 ** (torch.arange(0, head_dim, 2, device=dev).float() / head_dim))
+    f = torch.outer(torch.tensor([float(pos)], device=dev), inv)
+    return torch.cos(f).contiguous(), torch.sin(f).contiguous()
+
+
+class LayerSet:
+    """One rank's share of one decoder layer (weights + KV cache) and its graph.  The layer and the
+    cache contents are generated whole from `seed` (identically on every rank) and then sharded, so
+    that the tensor-parallel step can be compared with the single-GPU step on the same layer."""
+
+    def __init__(self, shape, world, rank, B, dev, seed, all_reduce, packs=None, linears=None):
         import torch
         from ms_kernel_b200 import ops, tp
-        self.B = B
-        lin = {}
-        for i, (name, (OUT, K)) in enumerate(shape.weight_shapes_local(world).items()):
-            lin[name] = make_linear(OUT, K, U, GS, seed * 16 + i + 1000 * rank, dev)
+        self.B, self.shape, self.world, self.rank, self.seed, self.dev = B, shape, world, rank, seed, dev
+        if linears is None:
+            packs = packs if packs is not None else layer_packs(shape, dev, seed)
+            local = tp.shard_layer(packs, shape, world, rank)
+            linears = {name: ops.PackedLinear(p, dev) for name, p in local.items()}
         q, kv, f = shape.local(world)
         self.Lcap = LK + 16                    # capacity a multiple of 16: the tuned decode path
         self.cache = ops.KVCache(B, kv, shape.head_dim, self.Lcap, U, GS, dev, rotate=True)
         g = torch.Generator(device=dev).manual_seed(seed + 77)
         chunk = 2048
         for k0 in range(0, LK, chunk):
-            Kt = torch.randn((B, kv, chunk, shape.head_dim), generator=g, device=dev).to(torch.bfloat16)
-            Vt = torch.randn((B, kv, chunk, shape.head_dim), generator=g, device=dev).to(torch.bfloat16)
-            self.cache.fill(Kt, Vt, key0=k0)
-        self.layer = tp.DecoderLayerTP(shape, world, lin, self.cache, all_reduce)
-        self.h_in = torch.zeros((B, shape.hidden), dtype=torch.bfloat16, device=dev)
+            # the whole batch x all kv heads, then this rank's heads: every rank draws the same numbers
+            Kt = torch.randn((B, shape.n_kv, chunk, shape.head_dim), generator=g, device=dev).to(torch.bfloat16)
+            Vt = torch.randn((B, shape.n_kv, chunk, shape.head_dim), generator=g, device=dev).to(torch.bfloat16)
+            sl = slice(rank * kv, (rank + 1) * kv)
+            self.cache.fill(Kt[:, sl].contiguous(), Vt[:, sl].contiguous(), key0=k0)
+            del Kt, Vt
+        self.layer = tp.DecoderLayerTP(shape, world, linears, self.cache, all_reduce)
+        gh = torch.Generator(device=dev).manual_seed(seed + 99)
+        self.h_in = torch.randn((B, shape.hidden), generator=gh, device=dev).to(torch.bfloat16)
+        self.rope = rope_tables_pos(LK - 1, shape.head_dim, dev)
         self.h_out = None
         self.graph = None
-        self.weight_bytes = sum(l.nbytes() for l in lin.values())
+        self.weight_bytes = sum(l.nbytes() for l in linears.values())
 
     def eager(self):
-        return self.layer.step(self.h_in, LK - 1, LK)
+        # the step of the reference's decode_step (tests/harness_batchsweep.py:230-243): RoPE on q and k at the
+        # new token's position, append to slot LK-1, attend LK keys
+        return self.layer.step(self.h_in, LK - 1, LK, rope=self.rope)
 
     def capture(self):
         import torch
@@ -220,6 +252,31 @@ class LayerSet:
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self.h_out = self.eager()
+
+
+def timed_windows(replay, steps, barrier, reduce_max, min_total_ms=60.0, max_windows=40):
+    """Device time of `steps` replays, as the best of several windows.
+
+    A window: host barrier + device synchronise, one UNTIMED replay (its exchanges make every rank's
+    stream wait for the slowest rank, so the timed region starts aligned on the device, whatever the
+    host-side skew after the barrier), start event, exactly `steps` replays, stop event, synchronise.
+    A window's time is the maximum over the ranks; windows repeat (at least three) until they add up to
+    `min_total_ms`, so the result does not depend on how short `steps` makes one window."""
+    import torch
+    e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+    times, total = [], 0.0
+    while len(times) < 3 or (total < min_total_ms and len(times) < max_windows):
+        barrier()
+        replay(-1)
+        e0.record()
+        for i in range(steps):
+            replay(i)
+        e1.record()
+        torch.cuda.synchronize()
+        t = reduce_max(e0.elapsed_time(e1))
+        times.append(t)
+        total += t
+    return min(times), times
 
 
 def run_ours(args):
@@ -238,23 +295,45 @@ def run_ours(args):
     if world > 1:
         import datetime
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+    clocks = ClockSampler(local)               # NVML is opened here, well before any timed region
 
-    def all_reduce(t):
+    def nccl_all_reduce(t):
         dist.all_reduce(t)
         return t
 
     shape = tp.LayerShape.llama31_70b()
-    B = args.batch
-    exchange = "none"
-    if world > 1:
-        exchange = "nccl all-reduce"
+    state = {"exchange": "none"}
+
+    def make_all_reduce(B):
+        if world == 1:
+            return None
         if os.environ.get("MSAQ_BENCH_EXCHANGE", "peer") == "peer":
             try:
-                all_reduce = tp.peer_all_reduce(dist.group.WORLD, B * shape.hidden, torch.float32, dev)
-                exchange = "one-shot all-reduce over NVLink peer memory (torch symmetric memory)"
+                ar = tp.peer_all_reduce(dist.group.WORLD, B * shape.hidden, torch.float32, dev)
+                state["exchange"] = "one-shot all-reduce over NVLink peer memory (torch symmetric memory)"
+                return ar
             except Exception as e:                              # keep NCCL, say why
-                exchange = "nccl all-reduce (symmetric memory unavailable: %s)" % str(e).splitlines()[0][:80]
-    probe = LayerSet(shape, world, rank, B, dev, 1, all_reduce)
+                state["exchange"] = "nccl all-reduce (symmetric memory unavailable: %s)" % str(e).splitlines()[0][:80]
+                return nccl_all_reduce
+        state["exchange"] = "nccl all-reduce"
+        return nccl_all_reduce
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def reduce_max(x):
+        if world == 1:
+            return float(x)
+        t = torch.tensor([float(x)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    B = args.batch
+    all_reduce = make_all_reduce(B)
+    packs0 = layer_packs(shape, dev, 1)
+    probe = LayerSet(shape, world, rank, B, dev, 1, all_reduce, packs=packs0)
     per_rank_bytes = probe.layer.algorithmic_bytes(B, B * LK, U, GS)
     # rotate over enough distinct weight + cache sets that a step never finds its bytes in L2
     n_sets = max(1, -(-3 * L2_BYTES // max(1, per_rank_bytes)))
@@ -268,32 +347,43 @@ def run_ours(args):
         s.capture()
     torch.cuda.synchronize()
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
+    # ---- tensor-parallel parity: the sharded step against the single-GPU step on the same layer ----
+    tp_parity = None
+    if world > 1:
+        for _ in range(4):                       # back-to-back replays: the exchange buffers rotate and are reused
+            sets[0].graph.replay()
         torch.cuda.synchronize()
+        if rank == 0:
+            ref = LayerSet(shape, 1, 0, B, dev, 1, None, packs=packs0)
+            h_ref = ref.eager().float()
+            h_tp = sets[0].h_out.float()
+            h0 = sets[0].h_in.float()
+            tp_parity = float(((h_tp - h_ref).norm() / (h_ref - h0).norm()).item())
+            finite = bool(torch.isfinite(h_tp).all().item())
+            del ref, h_ref
+            torch.cuda.empty_cache()
+            if not finite or not tp_parity <= 2e-2:
+                print(json.dumps({"error": "tensor-parallel step differs from the single-GPU step",
+                                  "tp_parity_rel_fro": tp_parity, "finite": finite}), flush=True)
+                os._exit(3)
+        barrier()                                # nobody replays (and waits in an exchange) while rank 0 still checks
+    del packs0
 
     for i in range(max(3, args.warmup)):
         sets[i % n_sets].graph.replay()
-    barrier()
-    e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
-    with ClockSampler(local) as clocks:
-        e0.record()
-        for i in range(args.steps):
-            sets[i % n_sets].graph.replay()
-        e1.record()
-        barrier()
-    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_per_step = float(ms.item()) / args.steps
+
+    def replay(i):
+        sets[i % n_sets].graph.replay()
+
+    with clocks:
+        best_ms, windows = timed_windows(replay, args.steps, barrier, reduce_max)
+    ms_per_step = best_ms / args.steps
     total_bytes = per_rank_bytes * world
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
 
-    # ---- end to end: eager public API, host buffers in and out every step -------------------
+    # ---- end to end: the public API with host buffers in and out every step -------------------
     h_host = torch.randn((B, shape.hidden)).to(torch.bfloat16).pin_memory()
     out_host = torch.empty((B, shape.hidden), dtype=torch.bfloat16).pin_memory()
-    e2e_steps = min(args.steps, 50)
 
     def e2e_step(i, eager):
         s = sets[i % n_sets]
@@ -306,25 +396,25 @@ def run_ours(args):
         out_host.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    def e2e_time(eager):
+    def e2e_time(eager, n):
         for i in range(3):
             e2e_step(i, eager)
-        barrier()
-        t0 = time.perf_counter()
-        for i in range(e2e_steps):
-            e2e_step(i, eager)
-        barrier()
-        t = torch.tensor([(time.perf_counter() - t0) * 1e3 / e2e_steps], device=dev)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        best = float("inf")
+        for _ in range(3):
+            barrier()
+            t0 = time.perf_counter()
+            for i in range(n):
+                e2e_step(i, eager)
+            best = min(best, reduce_max((time.perf_counter() - t0) * 1e3 / n))
+        return best
 
-    e2e_ms_val = e2e_time(False)
-    e2e_eager_ms = e2e_time(True)
+    e2e_steps = max(args.steps, 200)
+    e2e_ms_val = e2e_time(False, e2e_steps)
+    e2e_eager_ms = e2e_time(True, e2e_steps)
     e2e_value = total_bytes / (e2e_ms_val * 1e-3) / 1e9
 
     peak, peak_kind = measured_peak()
-    # ---- the dominant launch of the step, alone: this rank's gate+up GEMV (with its staging kernel) ----
+    # ---- the dominant launch of the step, alone: this rank's gate+up GEMV (with its activation staging) ----
     gu = [st.layer.lin["gate_up"] for st in sets]
     gu_us = graph_time([(lambda l=l, st=st: l.fwd_fused(st.h_in, ops.PRO_RMSNORM)) for l, st in zip(gu, sets)], 20, dev)
     gu_bytes = gemv_bytes(gu[0].OUT, gu[0].K, B, U, GS)
@@ -334,9 +424,34 @@ def run_ours(args):
                 "traffic": round(gu_bytes * NCU_TRAFFIC["bytes_per_launch"] / NCU_TRAFFIC["algorithmic_bytes"]),
                 "traffic_source": "ncu dram bytes of the 28672x4096 launch, scaled by algorithmic bytes",
                 "algorithmic_bytes": gu_bytes,
-                "kernel": "gemv_u4gs2_mma_kernel + its staging kernel: the layer's gate+up GEMV, %d x %d u4/gs2 M=%d"
+                "kernel": "gemv_u4gs2_mma_kernel with its activation staging: the layer's gate+up GEMV, %d x %d u4/gs2 M=%d"
                           % (gu[0].OUT, gu[0].K, B),
                 "us_per_launch": round(gu_us, 2), "share_of_step": round(gu_us / (ms_per_step * 1e3), 3)}
+
+    # ---- the same layer step at the other configured batch sizes (weights shared with the sets above) ----
+    layer_detail = []
+    for Bx in (8, 32):
+        if Bx == B or args.no_detail:
+            continue
+        arx = make_all_reduce(Bx)
+        bytes_x = tp.DecoderLayerTP(shape, world, sets[0].layer.lin, None, glue=sets[0].layer.glue).algorithmic_bytes(
+            Bx, Bx * LK, U, GS)
+        nx = int(max(1, min(n_sets, -(-3 * L2_BYTES // bytes_x))))
+        xs = [LayerSet(shape, world, rank, Bx, dev, 1 + i, arx, linears=sets[i].layer.lin) for i in range(nx)]
+        for x in xs:
+            x.capture()
+        for i in range(3):
+            xs[i % nx].graph.replay()
+        bx_ms, bx_windows = timed_windows(lambda i: xs[i % nx].graph.replay(), args.steps, barrier, reduce_max,
+                                          min_total_ms=30.0)
+        us = bx_ms / args.steps * 1e3
+        layer_detail.append({"B": Bx, "Lk": LK, "us_per_step": round(us, 2),
+                             "GBps": round(bytes_x * world / us / 1e3, 1),
+                             "frac_of_%s_peak_per_gpu" % peak_kind: round(bytes_x / us / 1e3 / peak, 4),
+                             "windows": len(bx_windows), "sets": nx})
+        del xs
+        torch.cuda.empty_cache()
+
     line = {
         "metric": "achieved_hbm_bandwidth_on_algorithmic_bytes", "value": round(value, 1), "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
@@ -344,31 +459,40 @@ def run_ours(args):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "u4 codes -> int8 MMA (M<=8) / bf16 tcgen05 (M>=9), fp32 accumulate, bf16 in/out", "data": "synthetic",
         "config": {
-            "workload": "llama-3.1-70b-shaped decoder layer, one decode step, u4/gs2 packed weights and KV cache, "
-                        "hidden 8192, Hq 64, Hkv 8, D 128, FFN 28672, Lk %d, B %d" % (LK, B),
+            "workload": "llama-3.1-70b-shaped decoder layer, one decode step (RoPE on q and k included), u4/gs2 packed "
+                        "weights and KV cache, hidden 8192, Hq 64, Hkv 8, D 128, FFN 28672, Lk %d, B %d" % (LK, B),
             "parallelism": "tp%d (rows of QKV/gate/up, K blocks of O/down, kv heads; 2 all-reduces per layer)" % world,
-            "exchange": exchange,
+            "exchange": state["exchange"],
             "l2": "rotating over %d distinct weight+cache sets (%.0f MB per GPU per set)" % (n_sets, per_rank_bytes / 1e6),
-            "timing": "CUDA-graph replay per step, CUDA events on the launching stream, max over ranks",
+            "timing": "CUDA-graph replay per step; CUDA events on the launching stream around exactly `steps` replays, "
+                      "barrier + synchronise on both sides, one untimed replay after the barrier to align the ranks on "
+                      "the device; max over ranks per window, best of %d windows" % len(windows),
             "algorithmic_bytes_per_step": int(total_bytes),
         },
+        "windows_ms": [round(w, 4) for w in windows],
+        "tp_parity_rel_fro": tp_parity,
         "frac_of_nominal_8TBs_per_gpu": round(value / world / NOMINAL_PEAK_GBS, 4),
         "frac_of_%s_peak_per_gpu" % peak_kind: round(value / world / peak, 4),
         "clocks": clocks.summary(),
         "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "us_per_step": round(e2e_ms_val * 1e3, 1),
                 "h2d_bytes_per_step": int(h_host.numel() * 2), "d2h_bytes_per_step": int(out_host.numel() * 2),
-                "us_per_step_eager": round(e2e_eager_ms * 1e3, 1),
+                "us_per_step_eager": round(e2e_eager_ms * 1e3, 1), "steps": e2e_steps,
                 "api": "ms_kernel_b200.tp.DecoderLayerTP.step over ops.PackedLinear / ops.KVCache, captured once in a "
                        "CUDA graph and replayed per step (us_per_step_eager: the same call launched eagerly); "
-                       "activations in from / result out to pinned host buffers, wall clock with a stream sync per step"},
-        "gpu_launches": launches_per_step * args.steps,
+                       "activations in from / result out to pinned host buffers, wall clock with a stream sync per step, "
+                       "best of 3 runs"},
+        "gpu_launches": launches_per_step * args.steps * len(windows),
         "gpu_launches_per_step": launches_per_step,
         "roofline": roofline,
     }
+    if layer_detail:
+        line["detail"] = {"layer": layer_detail}
     if world == 1 and rank == 0 and not args.no_detail:
         del sets, probe
         torch.cuda.empty_cache()
-        line.update(single_gpu_detail(dev, peak, peak_kind))
+        extra = single_gpu_detail(dev, peak, peak_kind)
+        line.setdefault("detail", {}).update(extra.pop("detail"))
+        line.update(extra)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -418,11 +542,14 @@ def single_gpu_detail(dev, peak, peak_kind):
         g = torch.Generator(device=dev).manual_seed(9)
         for _ in range(copies):
             c = ops.KVCache(B, Hkv, D, Lk + 16, U, GS, dev, rotate=True)
-            for k0 in range(0, Lk, 4096):
-                n = min(4096, Lk - k0)
-                Kt = torch.randn((B, Hkv, n, D), generator=g, device=dev).to(torch.bfloat16)
+            step_keys = 4096 if B <= 16 else 1024
+            for k0 in range(0, Lk, step_keys):
+                n = min(step_keys, Lk - k0)
+                Kt = torch.randn((B, Hkv, n, D), generator=g, device=dev)
                 Kt[..., [3, 40, 77, 120]] *= 20
-                c.fill(Kt, torch.randn((B, Hkv, n, D), generator=g, device=dev).to(torch.bfloat16), key0=k0)
+                c.fill(Kt.to(torch.bfloat16), torch.randn((B, Hkv, n, D), generator=g, device=dev).to(torch.bfloat16),
+                       key0=k0)
+                del Kt
             caches.append(c)
         q = torch.randn((B, Hq, D), generator=g, device=dev).to(torch.bfloat16)
         kn = torch.randn((B, Hkv, D), generator=g, device=dev).to(torch.bfloat16)
@@ -442,10 +569,12 @@ def single_gpu_detail(dev, peak, peak_kind):
         del caches
         torch.cuda.empty_cache()
 
-    for Hq, Lk in ((8, 4096), (8, 16384), (16, 16384)):
-        kv_case("mha", 1, Hq, Hq, Lk, False)
-    for Lk, B in ((4096, 1), (16384, 1), (16384, 8), (32768, 16)):
-        kv_case("gqa32/8", B, 32, 8, Lk, True)
+    for Hq in (8, 16):
+        for Lk in (4096, 16384):
+            kv_case("mha", 1, Hq, Hq, Lk, False)
+    for Lk in (4096, 16384, 32768):
+        for B in (1, 8, 16, 64):
+            kv_case("gqa32/8", B, 32, 8, Lk, True)
     out["cpu_baseline"] = cpu_oracle_sample()
     return out
 
@@ -519,9 +648,9 @@ def run_reference(args):
         for _ in range(B):
             orc.decode_attention_planes(qh, kp, vp, U, GS, Lk)
 
-    for _ in range(max(1, min(args.warmup, 2))):
+    for _ in range(args.warmup):
         step()
-    steps = max(1, min(args.steps, 5))
+    steps = max(1, args.steps)
     t0 = time.perf_counter()
     for _ in range(steps):
         step()
@@ -531,11 +660,13 @@ def run_reference(args):
               "kv head's decode over Lk/%d keys per sequence; %d timed passes" % (frac_rows, frac_keys, steps))
     line = {
         "impl": "reference", "metric": "achieved_hbm_bandwidth_on_algorithmic_bytes", "value": round(value, 5),
-        "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": max(1, min(args.warmup, 2)),
+        "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
         "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "float64 (NumPy)", "data": "synthetic",
-        "config": {"workload": "llama-3.1-70b-shaped decoder layer, one decode step, u4/gs2, Lk %d, B %d "
-                               "(bounded sample, see cpu_baseline.sample)" % (LK, B)},
+        "config": {"workload": "llama-3.1-70b-shaped decoder layer, one decode step, u4/gs2, Lk %d, B %d -- a BOUNDED "
+                               "SAMPLE of it per step: 1/%d of the output rows of each of the four GEMVs and one kv head's "
+                               "decode over Lk/%d keys per sequence (the NumPy oracle needs about a minute for the whole "
+                               "step); GB/s on the sample's own algorithmic bytes" % (LK, B, frac_rows, frac_keys)},
         "cpu_baseline": {"value": round(value, 5), "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": round(value, 5), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

@@ -208,6 +208,33 @@ int msaq_kv_append_pair(const void* Xk, const void* Xv, int8_t* k_scale_exp, uin
                         int64_t Lcap, int u, int gs, int rotate_k, void* stream);
 
 /*
+ * Rotary position embedding fused into the cache writers and the decode prologue (no reference counterpart as an
+ * operator: the reference's harness applies RoPE to q and k in PyTorch between the QKV projection and the append,
+ * tests/harness_batchsweep.py:118-137 `rope_pos` / `rope_bthd`, :237).  Tables are the harness's: rope_cos / rope_sin
+ * fp32 [rope_rows][D/2] in device memory with cos(pos * theta^(-2j/D)); rope_rows == 1 holds the one position of this
+ * step (`rope_pos`), otherwise the row index is the token's position (`rope_tables`) and rope_rows must cover every
+ * position that can occur (the capacity, for positions read from device memory).  A pair (x[2j], x[2j+1]) becomes
+ * bf16(x1*c - x2*s), bf16(x1*s + x2*c) with every fp32 product and sum rounded separately, bit for bit what
+ * rope_bthd yields; then the Hadamard rotation (when asked) and the quantiser see those bf16 values.
+ *   msaq_rope                    out[B,heads,D] = RoPE(x[B,heads,D]) at position pos (pos_per_seq[b] when given)
+ *   msaq_kv_append_pair_rope     msaq_kv_append_pair with RoPE on the K rows at the slot each row goes to
+ *   msaq_kv_write_rope           msaq_kv_write with RoPE on every row at its slot (the prefill K path)
+ *   msaq_kv_decode_attention_rope  the batched decode with RoPE on each query row at q_pos (q_pos_per_seq[b])
+ * rope_cos == NULL turns each of the last three into the entry point it extends.
+ */
+int msaq_rope(const void* x, void* out, int64_t B, int64_t heads, int64_t D, const float* rope_cos,
+              const float* rope_sin, int64_t rope_rows, int64_t pos, const int32_t* pos_per_seq, void* stream);
+int msaq_kv_append_pair_rope(const void* Xk, const void* Xv, int8_t* k_scale_exp, uint8_t* k_upper, uint8_t* k_shared,
+                             int8_t* v_scale_exp, uint8_t* v_upper, uint8_t* v_shared,
+                             int64_t B, int64_t Hkv, int64_t D, int64_t NB, int64_t pos, const int32_t* pos_per_seq,
+                             int64_t Lcap, int u, int gs, int rotate_k,
+                             const float* rope_cos, const float* rope_sin, int64_t rope_rows, void* stream);
+int msaq_kv_write_rope(const void* X, int8_t* scale_exp, uint8_t* upper, uint8_t* shared,
+                       int64_t H, int64_t L, int64_t D, int64_t NB, int64_t key0, int64_t Lcap,
+                       int u, int gs, int rotate,
+                       const float* rope_cos, const float* rope_sin, int64_t rope_rows, void* stream);
+
+/*
  * Prefill pack: X[H,L,D] (bf16) -> slots [key0, key0+L) of planes with key
  * stride Lcap (Lcap = L, key0 = 0 gives the reference's freshly allocated
  * planes).  rotate != 0 applies the Hadamard rotation to every row first.
@@ -268,6 +295,17 @@ int msaq_kv_decode_attention_batched(const void* q,
                                      int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D,
                                      int64_t NB, int u, int gs, int64_t Lcap, int qrot,
                                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* The batched decode with the rotary embedding of the query rows in the prologue (see msaq_rope above). */
+int msaq_kv_decode_attention_rope(const void* q,
+                                  const int8_t* ks, const uint8_t* ku, const uint8_t* kh,
+                                  const int8_t* vs, const uint8_t* vu, const uint8_t* vh,
+                                  void* out, float* out_f32, const int32_t* seq_lens,
+                                  int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D,
+                                  int64_t NB, int u, int gs, int64_t Lcap, int qrot,
+                                  const float* rope_cos, const float* rope_sin, int64_t rope_rows,
+                                  int64_t q_pos, const int32_t* q_pos_per_seq,
+                                  void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------- layer-step glue -- */
 

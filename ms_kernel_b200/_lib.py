@@ -34,6 +34,12 @@ SIGNATURES = {
     "msaq_kv_append_varlen": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _p, _i64, _int, _int, _int, _p]),
     "msaq_kv_append_pair": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p, _i64, _int, _int,
                                    _int, _p]),
+    "msaq_rope": (_int, [_p, _p, _i64, _i64, _i64, _p, _p, _i64, _i64, _p, _p]),
+    "msaq_kv_append_pair_rope": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p, _i64, _int, _int,
+                                        _int, _p, _p, _i64, _p]),
+    "msaq_kv_write_rope": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _p, _p, _i64, _p]),
+    "msaq_kv_decode_attention_rope": (_int, [_p] * 7 + [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64,
+                                                          _int, _int, _i64, _int, _p, _p, _i64, _i64, _p, _p, _sz, _p]),
     "msaq_kv_write": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _p]),
     "msaq_hadamard_rotate": (_int, [_p, _p, _i64, _i64, _p]),
     "msaq_pack_weight": (_int, [_p, _int, _p, _p, _p, _p, _p, _i64, _i64, _int, _int, _p]),

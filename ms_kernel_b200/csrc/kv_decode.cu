@@ -78,14 +78,21 @@ int launch_kv_mma(const KvMmaArgs& a, int S, int Hkv, int B, cudaStream_t st) {
     return check_launch("kv_decode_u4gs2");
 }
 
+struct QRope {
+    Rope rope;
+    int64_t q_pos;
+    const int32_t* q_pos_per_seq;
+};
+
 int run_mma(const __nv_bfloat16* q, KvPlanes kp, KvPlanes vp, void* out, float* out_f32, const int32_t* seq_lens,
-            int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t Lcap, int qrot, void* ws, cudaStream_t st) {
+            int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t Lcap, int qrot, const QRope& qr, void* ws,
+            cudaStream_t st) {
     const KvMmaPlan p = plan_mma(B, H, Hkv, Lk);
     uint8_t* base = static_cast<uint8_t*>(ws);
     int* status = reinterpret_cast<int*>(base + p.status_off);
     KvMmaArgs a{q, kp, vp, reinterpret_cast<float*>(base), seq_lens, status, sticky_status(), (int)H, (int)Hkv, (int)Lk,
-                (int)Lcap, p.key_tile, p.S, qrot, (float)(1.4426950408889634 / sqrt(128.0)), option_wait_polls(),
-                option_test_skip_stage()};
+                (int)Lcap, p.key_tile, p.S, qrot, (float)(1.4426950408889634 / sqrt(128.0)), qr.rope, qr.q_pos,
+                qr.q_pos_per_seq, KVM_SPLIT_TAU, option_wait_polls(), option_test_skip_stage()};
     int rc;
     switch (H / Hkv) {
         case 1: rc = launch_kv_mma<1>(a, p.S, (int)Hkv, (int)B, st); break;
@@ -102,8 +109,14 @@ int run_mma(const __nv_bfloat16* q, KvPlanes kp, KvPlanes vp, void* out, float* 
 
 int decode_dispatch(const void* q, KvPlanes kp, KvPlanes vp, void* out, float* out_f32, const int32_t* seq_lens,
                     int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D, int64_t NB, int u, int gs,
-                    int64_t Lcap, int qrot, void* ws, size_t ws_bytes, void* stream) {
+                    int64_t Lcap, int qrot, const QRope& qr, void* ws, size_t ws_bytes, void* stream) {
     Fmt f;
+    if (qr.rope.cos) {
+        if (!qr.rope.sin || qr.rope.rows < 1) return fail(MSAQ_ERR_ARG, "bad RoPE tables");
+        if (!qr.q_pos_per_seq && qr.rope.rows != 1 && (qr.q_pos < 0 || qr.q_pos >= qr.rope.rows))
+            return fail(MSAQ_ERR_ARG, "query position %lld outside the %lld RoPE table rows", (long long)qr.q_pos,
+                        (long long)qr.rope.rows);
+    }
     if (!make_fmt(u, gs, &f)) return fail(MSAQ_ERR_UNSUPPORTED, "unsupported format u=%d gs=%d", u, gs);
     if (!q || !kp.s || !kp.u || !kp.h || !vp.s || !vp.u || !vp.h || !out) return fail(MSAQ_ERR_ARG, "null pointer");
     if (B <= 0 || H <= 0 || Hkv <= 0 || Lk <= 0) return fail(MSAQ_ERR_ARG, "B, H, Hkv and Lk must be positive");
@@ -127,7 +140,7 @@ int decode_dispatch(const void* q, KvPlanes kp, KvPlanes vp, void* out, float* o
         !((reinterpret_cast<uintptr_t>(kp.s) | reinterpret_cast<uintptr_t>(kp.u) | reinterpret_cast<uintptr_t>(kp.h) |
            reinterpret_cast<uintptr_t>(vp.s) | reinterpret_cast<uintptr_t>(vp.u) | reinterpret_cast<uintptr_t>(vp.h)) & 15))
         return run_mma(static_cast<const __nv_bfloat16*>(q), kp, vp, out, out_f32, seq_lens, B, H, Hkv, Lk, Lcap, qrot,
-                       ws, st);
+                       qr, ws, st);
     const KvPlan p = plan_generic(B, H, Lk);
     const float sm_scale = (float)(1.0 / sqrt((double)D));
     float* partial = static_cast<float*>(ws);
@@ -136,7 +149,7 @@ int decode_dispatch(const void* q, KvPlanes kp, KvPlanes vp, void* out, float* o
     const size_t smem = ((size_t)D + KVG_CHUNK) * sizeof(float);
 #define MSAQ_GO(U) launch_chained(kv_decode_generic_kernel<U>, grid, dim3(KVG_THREADS), smem, st, \
         qq, kp, vp, partial, seq_lens, (int)H, (int)Hkv, (int)Lk, (int)Lcap, (int)D, (int)NB, f, p.key_tile, p.S, \
-        sm_scale, qrot)
+        sm_scale, qrot, qr.rope, qr.q_pos, qr.q_pos_per_seq)
     if (u == 4) MSAQ_GO(4); else if (u == 3) MSAQ_GO(3); else MSAQ_GO(2);
 #undef MSAQ_GO
     count_launch();
@@ -170,7 +183,7 @@ extern "C" int msaq_kv_decode_attention(const void* q, const int8_t* ks, const u
                                         int u, int gs, int64_t Lcap, void* workspace, size_t workspace_bytes,
                                         void* stream) {
     return decode_dispatch(q, KvPlanes{ks, ku, kh}, KvPlanes{vs, vu, vh}, out, out_f32, nullptr, 1, H, Hkv, Lk, D, NB,
-                           u, gs, Lcap, 0, workspace, workspace_bytes, stream);
+                           u, gs, Lcap, 0, QRope{}, workspace, workspace_bytes, stream);
 }
 
 extern "C" int msaq_kv_decode_attention_batched(const void* q, const int8_t* ks, const uint8_t* ku, const uint8_t* kh,
@@ -180,5 +193,17 @@ extern "C" int msaq_kv_decode_attention_batched(const void* q, const int8_t* ks,
                                                 int64_t Lcap, int qrot, void* workspace, size_t workspace_bytes,
                                                 void* stream) {
     return decode_dispatch(q, KvPlanes{ks, ku, kh}, KvPlanes{vs, vu, vh}, out, out_f32, seq_lens, B, H, Hkv, Lk, D, NB,
-                           u, gs, Lcap, qrot, workspace, workspace_bytes, stream);
+                           u, gs, Lcap, qrot, QRope{}, workspace, workspace_bytes, stream);
+}
+
+extern "C" int msaq_kv_decode_attention_rope(const void* q, const int8_t* ks, const uint8_t* ku, const uint8_t* kh,
+                                             const int8_t* vs, const uint8_t* vu, const uint8_t* vh, void* out,
+                                             float* out_f32, const int32_t* seq_lens, int64_t B, int64_t H, int64_t Hkv,
+                                             int64_t Lk, int64_t D, int64_t NB, int u, int gs, int64_t Lcap, int qrot,
+                                             const float* rope_cos, const float* rope_sin, int64_t rope_rows,
+                                             int64_t q_pos, const int32_t* q_pos_per_seq, void* workspace,
+                                             size_t workspace_bytes, void* stream) {
+    return decode_dispatch(q, KvPlanes{ks, ku, kh}, KvPlanes{vs, vu, vh}, out, out_f32, seq_lens, B, H, Hkv, Lk, D, NB,
+                           u, gs, Lcap, qrot, QRope{Rope{rope_cos, rope_sin, rope_rows}, q_pos, q_pos_per_seq}, workspace,
+                           workspace_bytes, stream);
 }

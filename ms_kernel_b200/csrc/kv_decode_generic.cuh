@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(KVG_THREADS)
 kv_decode_generic_kernel(const __nv_bfloat16* __restrict__ q, KvPlanes kp, KvPlanes vp,
                          float* __restrict__ partial, const int32_t* __restrict__ seq_lens,
                          int H, int Hkv, int Lk, int Lcap, int D, int NB, Fmt f, int key_tile, int S,
-                         float sm_scale, int qrot) {
+                         float sm_scale, int qrot, Rope rope, int64_t q_pos, const int32_t* __restrict__ q_pos_per_seq) {
     chain_wait();
     extern __shared__ float smem[];
     float* q_sh = smem;                    // [D]
@@ -80,7 +80,21 @@ kv_decode_generic_kernel(const __nv_bfloat16* __restrict__ q, KvPlanes kp, KvPla
     const int len = seq_lens ? min(seq_lens[b], Lk) : Lk;
     const int64_t head_base = ((int64_t)b * Hkv + hk) * NB;       // in units of Lcap slots
 
-    for (int d = tid; d < D; d += KVG_THREADS) q_sh[d] = __bfloat162float(q[((int64_t)b * H + h) * D + d]);
+    if (rope.cos) {
+        // the query's rotary embedding at its own position (the slot the step's new token went to)
+        int64_t p = q_pos_per_seq ? q_pos_per_seq[b] : q_pos;
+        p = rope.rows == 1 ? 0 : min(max(p, (int64_t)0), rope.rows - 1);
+        const __nv_bfloat16* qr = q + ((int64_t)b * H + h) * D;
+        for (int d = tid; d < D; d += KVG_THREADS) {
+            const int j = d >> 1;
+            float o1, o2;
+            rope_pair(__bfloat162float(qr[d & ~1]), __bfloat162float(qr[d | 1]), rope.cos[p * (D / 2) + j],
+                      rope.sin[p * (D / 2) + j], &o1, &o2);
+            q_sh[d] = (d & 1) ? o2 : o1;
+        }
+    } else {
+        for (int d = tid; d < D; d += KVG_THREADS) q_sh[d] = __bfloat162float(q[((int64_t)b * H + h) * D + d]);
+    }
     __syncthreads();
     if (qrot) {
         for (int hh = 1; hh < D; hh <<= 1) {

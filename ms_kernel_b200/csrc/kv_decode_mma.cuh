@@ -37,7 +37,7 @@ constexpr int KVM_K_UP = 0, KVM_K_SH = 4 * KVM_UP, KVM_K_SC = KVM_K_SH + 4 * KVM
 constexpr int KVM_V_UP = KVM_K_SC + 4 * KVM_SC, KVM_V_SH = KVM_V_UP + 4 * KVM_UP, KVM_V_SC = KVM_V_SH + 4 * KVM_SH;
 constexpr int KVM_STAGE_BYTES = KVM_V_SC + 4 * KVM_SC;            // 25600
 constexpr int KVM_QREC = 320;               // staged query record per (block, pass); layout as in gemv_mma.cuh
-constexpr float KVM_SPLIT_TAU = 0.015625f;  // 2^-6: boundary between the big and the small keys of a split chunk
+constexpr float KVM_SPLIT_TAU = 0.001953125f;  // 2^-9: boundary between the big and the small keys of a split chunk
 constexpr int KVM_PSTRIDE = 40;             // floats per head row of the probability exchange buffer
 constexpr int KVM_OFF_Q = KVM_STAGES * KVM_STAGE_BYTES;
 constexpr int KVM_OFF_P = KVM_OFF_Q + 4 * 2 * KVM_QREC;
@@ -53,6 +53,10 @@ struct KvMmaArgs {
     int* sticky;                // the library's per-device status word (may be null)
     int Hq, Hkv, Lk, Lcap, key_tile, S, qrot;
     float sm_scale_log2;        // log2(e) / sqrt(D)
+    Rope rope;                  // rotary embedding of the query (cos == nullptr: none)
+    int64_t q_pos;              // the query's position, or per sequence:
+    const int32_t* q_pos_per_seq;
+    float split_limit;          // a chunk whose small keys sum to less than this (relative to its maximum) may split
     uint32_t max_polls;         // limit of every mbarrier wait (see mbar_wait_bounded)
     int skip_stage;             // test hook: the producer of CTA (0,0,0) stops before this stage (-1: never)
 };
@@ -131,6 +135,11 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
         float v[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) v[i] = __bfloat162float(qp[i]);
+        if (a.rope.cos) {
+            int64_t p = a.q_pos_per_seq ? a.q_pos_per_seq[b] : a.q_pos;
+            p = a.rope.rows == 1 ? 0 : min(max(p, (int64_t)0), a.rope.rows - 1);
+            rope_warp<4>(v, lane, a.rope, p);
+        }
         if (a.qrot) {
             fwht_warp<4>(v, lane);
             const float inv = 0.08838834764831845f;                       // 1/sqrt(128)
@@ -247,8 +256,8 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
             // the P.V operand always spans the chunk's largest key) and the factor 2^(chunk max -
             // running max) is applied in fp32 to the chunk's integer result: a chunk far below an
             // earlier dominant key keeps its full relative precision.
-            // A chunk whose probabilities fall into a "big" set (within 2^-6 of the chunk maximum, e.g. an
-            // attention sink) and a "small" set whose sum is itself below 2^-6 would leave the small keys
+            // A chunk whose probabilities fall into a "big" set (within 2^-9 of the chunk maximum, e.g. an
+            // attention sink) and a "small" set whose sum is itself below 2^-9 would leave the small keys
             // under the resolution of the 16-bit operand.  Such a chunk (split[p] > 0, rare) takes two P.V
             // passes: the small keys relative to their own sum, then the big keys relative to the maximum.
             float alpha[PASSES], beta[PASSES], split[PASSES];
@@ -284,7 +293,7 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
                     ps += __shfl_xor_sync(0xffffffffu, ps, o);
                     psm += __shfl_xor_sync(0xffffffffu, psm, o);
                 }
-                split[p] = (psm > 0.0f && psm < KVM_SPLIT_TAU) ? psm : 0.0f;
+                split[p] = (psm > 0.0f && psm < a.split_limit) ? psm : 0.0f;
                 l_run[p] = fmaf(l_run[p], alpha[p], ps * beta[p]);
                 m_run[p] = m_new;
             }
@@ -330,7 +339,25 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
                 for (int i = 0; i < 8; ++i) pf[i] = 0.0f;
             }
             if (G < 8 && g >= G) sa = 0.0f;
-            const bool is_split = sa > 0.0f;
+            bool is_split = sa > 0.0f;
+            if (__any_sync(0xffffffffu, is_split)) {
+                // Confirm with the value scales: the small keys only need their own pass when every big key
+                // enters the P.V operand far below full scale, i.e. its value block scales are all at
+                // least 2^4 under the chunk's (an attention sink with a small value row).  Otherwise the big
+                // keys' own contribution dwarfs what the small keys lose to rounding.
+                float big_scale = 0.0f;
+#pragma unroll
+                for (int blk = 0; blk < 4; ++blk) {
+                    const float4 r0 = *reinterpret_cast<const float4*>(Rw + blk * 32 + 8 * t);
+                    const float4 r1 = *reinterpret_cast<const float4*>(Rw + blk * 32 + 8 * t + 4);
+                    const float rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) big_scale = fmaxf(big_scale, pf[i] >= KVM_SPLIT_TAU ? rr[i] : 0.0f);
+                }
+                big_scale = fmaxf(big_scale, __shfl_xor_sync(0xffffffffu, big_scale, 1));
+                big_scale = fmaxf(big_scale, __shfl_xor_sync(0xffffffffu, big_scale, 2));
+                is_split = is_split && big_scale <= 0.0625f;
+            }
             const int n_pv = __any_sync(0xffffffffu, is_split) ? 2 : 1;
             const float sa_inv = is_split ? __frcp_rn(sa) : 1.0f;
             // ---- P.V: per block 4 n-tiles of 8 channels (+ one all-ones MMA for the code offset) ----

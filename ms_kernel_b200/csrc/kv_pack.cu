@@ -22,6 +22,7 @@ struct RowMap {
     const int32_t* pos;      // optional per-sequence slot (varlen append)
     int64_t heads_per_seq;   // Hkv, used with pos
     int* sticky;             // the library's per-device status word: bit BAD_APPEND_POS when a pos[] entry is out of range
+    Rope rope;               // rotary embedding applied (before the Hadamard rotation) to jobs that ask for it
 };
 
 // 2^k as a double, k in [-1022, 1023].
@@ -35,6 +36,7 @@ struct QuantJob {
     uint8_t* upper;
     uint8_t* shared;
     int rot;
+    int rope;                // apply map.rope at the row's slot (= its token position) first
 };
 struct QuantJobs { QuantJob j[2]; };
 
@@ -57,21 +59,6 @@ quantize_rows_kernel(const QuantJobs jobs, RowMap map, Fmt f) {
     const int64_t row = (int64_t)blockIdx.x * ROWS_PER_CTA + warp;
     if (row >= map.rows) return;
 
-    float v[EPL];
-    const __nv_bfloat16* src = X + row * D + lane * EPL;
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) v[i] = __bfloat162float(src[i]);
-    if (ROT) {
-        fwht_warp<EPL>(v, lane);
-        const float inv = (float)(1.0 / sqrt((double)D));
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) v[i] = v[i] * inv;
-    }
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) rowbuf[warp][lane * EPL + i] = v[i];
-    for (int i = lane; i < NB * CW; i += 32) (&codes[warp][0][0])[i] = 0u;
-    __syncwarp();
-
     const int64_t head = row / map.rows_per_head;
     int64_t key = map.key0 + row % map.rows_per_head;
     if (map.pos) {
@@ -83,6 +70,23 @@ quantize_rows_kernel(const QuantJobs jobs, RowMap map, Fmt f) {
             return;
         }
     }
+
+    float v[EPL];
+    const __nv_bfloat16* src = X + row * D + lane * EPL;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) v[i] = __bfloat162float(src[i]);
+    if (job.rope && map.rope.cos) rope_warp<EPL>(v, lane, map.rope, map.rope.rows == 1 ? 0 : key);
+    if (ROT) {
+        fwht_warp<EPL>(v, lane);
+        const float inv = (float)(1.0 / sqrt((double)D));
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) v[i] = v[i] * inv;
+    }
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) rowbuf[warp][lane * EPL + i] = v[i];
+    for (int i = lane; i < NB * CW; i += 32) (&codes[warp][0][0])[i] = 0u;
+    __syncwarp();
+
     const int lim = (1 << (7 - f.u)) - 1, slo = -(1 << (f.u - 1)), shi = (1 << (f.u - 1)) - 1;
     const int g0 = lane & ~(f.gs - 1);                        // first lane of this lane's group
 
@@ -219,6 +223,14 @@ int check_rows(const RowMap& map, int64_t D, int64_t NB, int u, int gs, Fmt* f) 
     if (!map.pos && (map.key0 < 0 || map.key0 + map.rows_per_head > map.Lcap))
         return fail(MSAQ_ERR_ARG, "slots [%lld, %lld) exceed the cache capacity %lld", (long long)map.key0,
                     (long long)(map.key0 + map.rows_per_head), (long long)map.Lcap);
+    if (map.rope.cos) {
+        if (!map.rope.sin) return fail(MSAQ_ERR_ARG, "rope_sin is null");
+        // a row per position: every slot a row can go to needs its table row
+        const int64_t need = map.pos ? map.Lcap : map.key0 + map.rows_per_head;
+        if (map.rope.rows != 1 && map.rope.rows < need)
+            return fail(MSAQ_ERR_ARG, "the RoPE tables have %lld rows, positions up to %lld are possible",
+                        (long long)map.rope.rows, (long long)need - 1);
+    }
     return MSAQ_OK;
 }
 
@@ -228,7 +240,7 @@ int quantize_rows(const void* X, int8_t* se, uint8_t* up, uint8_t* sh, const Row
     if (!X || !se || !up || !sh) return fail(MSAQ_ERR_ARG, "null pointer");
     if (int rc = check_rows(map, D, NB, u, gs, &f)) return rc;
     QuantJobs jobs{};
-    jobs.j[0] = QuantJob{static_cast<const __nv_bfloat16*>(X), se, up, sh, rot ? 1 : 0};
+    jobs.j[0] = QuantJob{static_cast<const __nv_bfloat16*>(X), se, up, sh, rot ? 1 : 0, map.rope.cos ? 1 : 0};
     return launch_rows(jobs, 1, map, D, f, static_cast<cudaStream_t>(stream));
 }
 
@@ -258,29 +270,49 @@ extern "C" int msaq_kv_append_varlen(const void* X, int8_t* scale_exp, uint8_t* 
     return quantize_rows(X, scale_exp, upper, shared, m, D, NB, u, gs, rotate != 0, stream);
 }
 
+extern "C" int msaq_kv_append_pair_rope(const void* Xk, const void* Xv, int8_t* k_scale_exp, uint8_t* k_upper,
+                                        uint8_t* k_shared, int8_t* v_scale_exp, uint8_t* v_upper, uint8_t* v_shared,
+                                        int64_t B, int64_t Hkv, int64_t D, int64_t NB, int64_t pos,
+                                        const int32_t* pos_per_seq, int64_t Lcap, int u, int gs, int rotate_k,
+                                        const float* rope_cos, const float* rope_sin, int64_t rope_rows,
+                                        void* stream) {
+    if (!Xk || !Xv || !k_scale_exp || !k_upper || !k_shared || !v_scale_exp || !v_upper || !v_shared)
+        return fail(MSAQ_ERR_ARG, "null pointer");
+    if (B <= 0 || Hkv <= 0) return fail(MSAQ_ERR_ARG, "B and Hkv must be positive");
+    RowMap m{B * Hkv, 1, pos_per_seq ? 0 : pos, Lcap, pos_per_seq, Hkv, pos_per_seq ? sticky_status() : nullptr,
+             Rope{rope_cos, rope_sin, rope_rows}};
+    Fmt f;
+    if (int rc = check_rows(m, D, NB, u, gs, &f)) return rc;
+    QuantJobs jobs{};
+    jobs.j[0] = QuantJob{static_cast<const __nv_bfloat16*>(Xk), k_scale_exp, k_upper, k_shared, rotate_k ? 1 : 0,
+                         rope_cos ? 1 : 0};
+    jobs.j[1] = QuantJob{static_cast<const __nv_bfloat16*>(Xv), v_scale_exp, v_upper, v_shared, 0, 0};
+    return launch_rows(jobs, 2, m, D, f, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int msaq_kv_append_pair(const void* Xk, const void* Xv, int8_t* k_scale_exp, uint8_t* k_upper,
                                    uint8_t* k_shared, int8_t* v_scale_exp, uint8_t* v_upper, uint8_t* v_shared,
                                    int64_t B, int64_t Hkv, int64_t D, int64_t NB, int64_t pos, const int32_t* pos_per_seq,
                                    int64_t Lcap, int u, int gs, int rotate_k, void* stream) {
-    if (!Xk || !Xv || !k_scale_exp || !k_upper || !k_shared || !v_scale_exp || !v_upper || !v_shared)
-        return fail(MSAQ_ERR_ARG, "null pointer");
-    if (B <= 0 || Hkv <= 0) return fail(MSAQ_ERR_ARG, "B and Hkv must be positive");
-    RowMap m{B * Hkv, 1, pos_per_seq ? 0 : pos, Lcap, pos_per_seq, Hkv, pos_per_seq ? sticky_status() : nullptr};
-    Fmt f;
-    if (int rc = check_rows(m, D, NB, u, gs, &f)) return rc;
-    QuantJobs jobs{};
-    jobs.j[0] = QuantJob{static_cast<const __nv_bfloat16*>(Xk), k_scale_exp, k_upper, k_shared, rotate_k ? 1 : 0};
-    jobs.j[1] = QuantJob{static_cast<const __nv_bfloat16*>(Xv), v_scale_exp, v_upper, v_shared, 0};
-    return launch_rows(jobs, 2, m, D, f, static_cast<cudaStream_t>(stream));
+    return msaq_kv_append_pair_rope(Xk, Xv, k_scale_exp, k_upper, k_shared, v_scale_exp, v_upper, v_shared, B, Hkv, D, NB,
+                                    pos, pos_per_seq, Lcap, u, gs, rotate_k, nullptr, nullptr, 0, stream);
+}
+
+extern "C" int msaq_kv_write_rope(const void* X, int8_t* scale_exp, uint8_t* upper, uint8_t* shared, int64_t H,
+                                  int64_t L, int64_t D, int64_t NB, int64_t key0, int64_t Lcap, int u, int gs,
+                                  int rotate, const float* rope_cos, const float* rope_sin, int64_t rope_rows,
+                                  void* stream) {
+    if (L < 0 || H < 0) return fail(MSAQ_ERR_ARG, "negative size");
+    if (L == 0) return MSAQ_OK;
+    RowMap m{H * L, L, key0, Lcap, nullptr, 1, nullptr, Rope{rope_cos, rope_sin, rope_rows}};
+    return quantize_rows(X, scale_exp, upper, shared, m, D, NB, u, gs, rotate != 0, stream);
 }
 
 extern "C" int msaq_kv_write(const void* X, int8_t* scale_exp, uint8_t* upper, uint8_t* shared, int64_t H, int64_t L,
                              int64_t D, int64_t NB, int64_t key0, int64_t Lcap, int u, int gs, int rotate,
                              void* stream) {
-    if (L < 0 || H < 0) return fail(MSAQ_ERR_ARG, "negative size");
-    if (L == 0) return MSAQ_OK;
-    RowMap m{H * L, L, key0, Lcap, nullptr, 1};
-    return quantize_rows(X, scale_exp, upper, shared, m, D, NB, u, gs, rotate != 0, stream);
+    return msaq_kv_write_rope(X, scale_exp, upper, shared, H, L, D, NB, key0, Lcap, u, gs, rotate, nullptr, nullptr, 0,
+                              stream);
 }
 
 extern "C" int msaq_hadamard_rotate(const void* x, void* out, int64_t N, int64_t D, void* stream) {

@@ -52,10 +52,44 @@ add_residual_kernel(const __nv_bfloat16* __restrict__ h, const T* __restrict__ d
     out[i] = __float2bfloat16_rn(__bfloat162float(h[i]) + (float)d[i]);
 }
 
+// out[b,h,:] = RoPE(x[b,h,:]) at the position of sequence b; one thread per rotary pair.
+__global__ void __launch_bounds__(256)
+rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int64_t pairs, int heads, int half,
+            Rope r, int64_t pos, const int32_t* __restrict__ pos_per_seq) {
+    chain_release();
+    chain_wait();
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= pairs) return;
+    const int j = (int)(i % half);
+    const int64_t b = i / half / heads;
+    int64_t p = pos_per_seq ? pos_per_seq[b] : pos;
+    p = r.rows == 1 ? 0 : min(max(p, (int64_t)0), r.rows - 1);
+    float o1, o2;
+    rope_pair(__bfloat162float(x[2 * i]), __bfloat162float(x[2 * i + 1]), r.cos[p * half + j], r.sin[p * half + j], &o1, &o2);
+    out[2 * i] = __float2bfloat16_rn(o1);
+    out[2 * i + 1] = __float2bfloat16_rn(o2);
+}
+
 }  // namespace
 }  // namespace msaq
 
 using namespace msaq;
+
+extern "C" int msaq_rope(const void* x, void* out, int64_t B, int64_t heads, int64_t D, const float* rope_cos,
+                         const float* rope_sin, int64_t rope_rows, int64_t pos, const int32_t* pos_per_seq,
+                         void* stream) {
+    if (!x || !out || !rope_cos || !rope_sin) return fail(MSAQ_ERR_ARG, "rope: null pointer");
+    if (B <= 0 || heads <= 0 || D <= 0 || (D & 1) || heads > INT32_MAX || D > INT32_MAX || rope_rows < 1)
+        return fail(MSAQ_ERR_ARG, "rope: bad size");
+    if (!pos_per_seq && rope_rows != 1 && (pos < 0 || pos >= rope_rows))
+        return fail(MSAQ_ERR_ARG, "rope: position %lld outside the %lld table rows", (long long)pos, (long long)rope_rows);
+    const int64_t pairs = B * heads * (D / 2);
+    launch_chained(rope_kernel, dim3((unsigned)((pairs + 255) / 256)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                   static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), pairs, (int)heads, (int)(D / 2),
+                   Rope{rope_cos, rope_sin, rope_rows}, pos, pos_per_seq);
+    count_launch();
+    return check_launch("rope");
+}
 
 extern "C" int msaq_rmsnorm(const void* x, void* out, int64_t rows, int64_t n, float eps, void* stream) {
     if (!x || !out || rows <= 0 || n <= 0 || n > INT32_MAX) return fail(MSAQ_ERR_ARG, "rmsnorm: bad argument");

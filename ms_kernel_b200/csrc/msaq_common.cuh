@@ -64,7 +64,44 @@ inline cudaError_t launch_chained(void (*kernel)(P...), dim3 grid, dim3 block, s
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<A>(args)...);
 }
 
+// Rotary position embedding tables as the reference's harness builds them (tests/harness_batchsweep.py:
+// 118-137): cos/sin fp32 [rows][D/2]; rows == 1 means one position for every sequence (the harness's
+// rope_pos), otherwise the row is the token's position (rope_tables).  cos == nullptr: no RoPE.
+struct Rope {
+    const float* cos;
+    const float* sin;
+    int64_t rows;
+};
+
 // ---- small device helpers ---------------------------------------------------
+// One rotary pair, evaluated as torch evaluates rope_bthd (tests/harness_batchsweep.py:134-137): fp32
+// products and sum, each rounded separately (no fused multiply-add), then the cast to bf16.
+__device__ __forceinline__ void rope_pair(float x1, float x2, float c, float s, float* o1, float* o2) {
+    *o1 = __bfloat162float(__float2bfloat16_rn(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s))));
+    *o2 = __bfloat162float(__float2bfloat16_rn(__fadd_rn(__fmul_rn(x1, s), __fmul_rn(x2, c))));
+}
+
+// RoPE on a row held as EPL consecutive elements per lane (element index lane*EPL + i); `row` is the
+// table row.  With one element per lane the pair partner is the neighbouring lane.
+template <int EPL>
+__device__ __forceinline__ void rope_warp(float (&v)[EPL], int lane, const Rope& r, int64_t row) {
+    constexpr int HALF = 16 * EPL;                            // D / 2
+    const float* cr = r.cos + row * HALF;
+    const float* sr = r.sin + row * HALF;
+    if constexpr (EPL == 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[0], 1);
+        const float c = cr[lane >> 1], s = sr[lane >> 1];
+        float o1, o2;
+        if (lane & 1) { rope_pair(other, v[0], c, s, &o1, &o2); v[0] = o2; }
+        else { rope_pair(v[0], other, c, s, &o1, &o2); v[0] = o1; }
+    } else {
+#pragma unroll
+        for (int i = 0; i < EPL; i += 2) {
+            const int j = (lane * EPL + i) >> 1;
+            rope_pair(v[i], v[i + 1], cr[j], sr[j], &v[i], &v[i + 1]);
+        }
+    }
+}
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
 __device__ __forceinline__ float bf16_lo(uint32_t pair) { return __uint_as_float(pair << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t pair) { return __uint_as_float(pair & 0xFFFF0000u); }

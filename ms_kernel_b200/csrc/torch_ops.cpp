@@ -202,10 +202,20 @@ void kv_append_varlen(const Tensor& X, Tensor s, Tensor up, Tensor sh, const Ten
 }
 
 // K (rotated when asked) and V rows of one decode step in one launch; pos_t (int32 [B]) overrides pos when given.
-void kv_append_pair(const Tensor& Xk, const Tensor& Xv, Tensor ks, Tensor ku, Tensor kh, Tensor vs, Tensor vu, Tensor vh,
+// RoPE tables: fp32 [rows, D/2], contiguous, on x's device (rows == 1: one position for all sequences).
+void check_rope(const Tensor& cos, const Tensor& sin, const Tensor& like, int64_t D) {
+    TORCH_CHECK(cos.is_cuda() && sin.is_cuda() && cos.get_device() == like.get_device() &&
+                sin.get_device() == like.get_device(), "RoPE tables must be on the activations' device");
+    TORCH_CHECK(cos.scalar_type() == at::kFloat && sin.scalar_type() == at::kFloat && cos.is_contiguous() &&
+                sin.is_contiguous() && cos.dim() == 2 && cos.sizes() == sin.sizes() && cos.size(1) == D / 2,
+                "RoPE tables must be contiguous fp32 [rows, D/2]");
+}
+
+void kv_append_pair_impl(const Tensor& Xk, const Tensor& Xv, Tensor ks, Tensor ku, Tensor kh, Tensor vs, Tensor vu, Tensor vh,
                     const c10::optional<Tensor>& pos_t, int64_t B, int64_t Hkv, int64_t D, int64_t NB, int64_t pos,
-                    int64_t Lcap, int64_t u, int64_t gs, bool rotate_k) {
+                    int64_t Lcap, int64_t u, int64_t gs, bool rotate_k, const Tensor* cos, const Tensor* sin) {
     check_act(Xk, "Xk");
+    if (cos) check_rope(*cos, *sin, Xk, D);
     check_act(Xv, "Xv");
     int64_t UB, SB;
     fmt_sizes(u, gs, &UB, &SB);
@@ -220,11 +230,24 @@ void kv_append_pair(const Tensor& Xk, const Tensor& Xv, Tensor ks, Tensor ku, Te
     check_planes(ks, ku, kh, Xk, B * Hkv * NB * Lcap, UB, SB);
     check_planes(vs, vu, vh, Xv, B * Hkv * NB * Lcap, UB, SB);
     c10::cuda::CUDAGuard guard(Xk.device());
-    check_rc(msaq_kv_append_pair(Xk.data_ptr(), Xv.data_ptr(), ks.data_ptr<int8_t>(), ku.data_ptr<uint8_t>(),
-                                 kh.data_ptr<uint8_t>(), vs.data_ptr<int8_t>(), vu.data_ptr<uint8_t>(),
-                                 vh.data_ptr<uint8_t>(), B, Hkv, D, NB, pos, pp, Lcap, (int)u, (int)gs, rotate_k ? 1 : 0,
-                                 stream_of(Xk)),
+    check_rc(msaq_kv_append_pair_rope(Xk.data_ptr(), Xv.data_ptr(), ks.data_ptr<int8_t>(), ku.data_ptr<uint8_t>(),
+                                      kh.data_ptr<uint8_t>(), vs.data_ptr<int8_t>(), vu.data_ptr<uint8_t>(),
+                                      vh.data_ptr<uint8_t>(), B, Hkv, D, NB, pos, pp, Lcap, (int)u, (int)gs,
+                                      rotate_k ? 1 : 0, cos ? cos->data_ptr<float>() : nullptr,
+                                      sin ? sin->data_ptr<float>() : nullptr, cos ? cos->size(0) : 0, stream_of(Xk)),
              "kv_append_pair");
+}
+void kv_append_pair(const Tensor& Xk, const Tensor& Xv, Tensor ks, Tensor ku, Tensor kh, Tensor vs, Tensor vu, Tensor vh,
+                    const c10::optional<Tensor>& pos_t, int64_t B, int64_t Hkv, int64_t D, int64_t NB, int64_t pos,
+                    int64_t Lcap, int64_t u, int64_t gs, bool rotate_k) {
+    kv_append_pair_impl(Xk, Xv, ks, ku, kh, vs, vu, vh, pos_t, B, Hkv, D, NB, pos, Lcap, u, gs, rotate_k, nullptr, nullptr);
+}
+// Same with the rotary embedding applied to the K rows first (at the slot each row goes to).
+void kv_append_pair_rope(const Tensor& Xk, const Tensor& Xv, Tensor ks, Tensor ku, Tensor kh, Tensor vs, Tensor vu,
+                         Tensor vh, const c10::optional<Tensor>& pos_t, int64_t B, int64_t Hkv, int64_t D, int64_t NB,
+                         int64_t pos, int64_t Lcap, int64_t u, int64_t gs, bool rotate_k, const Tensor& cos,
+                         const Tensor& sin) {
+    kv_append_pair_impl(Xk, Xv, ks, ku, kh, vs, vu, vh, pos_t, B, Hkv, D, NB, pos, Lcap, u, gs, rotate_k, &cos, &sin);
 }
 
 std::vector<Tensor> kv_write_impl(const Tensor& X, int64_t H, int64_t L, int64_t D, int64_t NB, int64_t u, int64_t gs,
@@ -306,8 +329,17 @@ void reject_numeric_toggles() {
 Tensor decode_common(const Tensor& q, const Tensor& ks, const Tensor& ku, const Tensor& kh, const Tensor& vs,
                      const Tensor& vu, const Tensor& vh, const c10::optional<Tensor>& seq_lens, int64_t B, int64_t H,
                      int64_t Hkv, int64_t Lk, int64_t D, int64_t NB, int64_t u, int64_t gs, int64_t Lcap, int qrot,
-                     bool batched) {
+                     bool batched, const Tensor* cos = nullptr, const Tensor* sin = nullptr,
+                     const c10::optional<Tensor>& q_pos_t = c10::nullopt, int64_t q_pos = 0) {
     check_act(q, "q");
+    if (cos) check_rope(*cos, *sin, q, D);
+    const int32_t* qpp = nullptr;
+    if (q_pos_t.has_value()) {
+        const Tensor& p = *q_pos_t;
+        TORCH_CHECK(p.is_cuda() && p.scalar_type() == at::kInt && p.is_contiguous() && p.numel() == B,
+                    "q_pos must be a contiguous CUDA int32 tensor of B elements");
+        qpp = p.data_ptr<int32_t>();
+    }
     reject_numeric_toggles();
     int64_t UB, SB;
     fmt_sizes(u, gs, &UB, &SB);
@@ -327,10 +359,12 @@ Tensor decode_common(const Tensor& q, const Tensor& ks, const Tensor& ku, const 
     Tensor out = batched ? at::empty({B, H, D}, q.options()) : at::empty({H, D}, q.options());
     const size_t wsb = msaq_kv_decode_workspace(B, H, Hkv, Lk, D);
     Tensor ws = workspace(q, wsb);
-    check_rc(msaq_kv_decode_attention_batched(q.data_ptr(), ks.data_ptr<int8_t>(), ku.data_ptr<uint8_t>(),
-                                              kh.data_ptr<uint8_t>(), vs.data_ptr<int8_t>(), vu.data_ptr<uint8_t>(),
-                                              vh.data_ptr<uint8_t>(), out.data_ptr(), nullptr, lens, B, H, Hkv, Lk, D,
-                                              NB, (int)u, (int)gs, Lcap, qrot, ws.data_ptr(), wsb, stream_of(q)),
+    check_rc(msaq_kv_decode_attention_rope(q.data_ptr(), ks.data_ptr<int8_t>(), ku.data_ptr<uint8_t>(),
+                                           kh.data_ptr<uint8_t>(), vs.data_ptr<int8_t>(), vu.data_ptr<uint8_t>(),
+                                           vh.data_ptr<uint8_t>(), out.data_ptr(), nullptr, lens, B, H, Hkv, Lk, D,
+                                           NB, (int)u, (int)gs, Lcap, qrot, cos ? cos->data_ptr<float>() : nullptr,
+                                           sin ? sin->data_ptr<float>() : nullptr, cos ? cos->size(0) : 0, q_pos, qpp,
+                                           ws.data_ptr(), wsb, stream_of(q)),
              batched ? "kv_decode_attention_batched" : "kv_decode_attention");
     return out;
 }
@@ -355,6 +389,36 @@ Tensor kv_decode_attention_varlen(const Tensor& q, const Tensor& ks, const Tenso
                                   int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D, int64_t NB, int64_t u,
                                   int64_t gs, int64_t Lcap, bool qrot) {
     return decode_common(q, ks, ku, kh, vs, vu, vh, seq_lens, B, H, Hkv, Lk, D, NB, u, gs, Lcap, qrot ? 1 : 0, true);
+}
+
+// The varlen decode with the query's rotary embedding done in the kernel prologue (before the Hadamard rotation).
+Tensor kv_decode_attention_rope(const Tensor& q, const Tensor& ks, const Tensor& ku, const Tensor& kh,
+                                const Tensor& vs, const Tensor& vu, const Tensor& vh, const Tensor& seq_lens,
+                                int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D, int64_t NB, int64_t u,
+                                int64_t gs, int64_t Lcap, bool qrot, const Tensor& cos, const Tensor& sin,
+                                const c10::optional<Tensor>& q_pos_t, int64_t q_pos) {
+    return decode_common(q, ks, ku, kh, vs, vu, vh, seq_lens, B, H, Hkv, Lk, D, NB, u, gs, Lcap, qrot ? 1 : 0, true,
+                         &cos, &sin, q_pos_t, q_pos);
+}
+
+// x [B, heads, D] bf16 -> RoPE at position pos (pos_t[b] per sequence when given).
+Tensor rope(const Tensor& x, const Tensor& cos, const Tensor& sin, const c10::optional<Tensor>& pos_t, int64_t pos) {
+    check_act(x, "x");
+    TORCH_CHECK(x.dim() == 3, "x must be [B, heads, D]");
+    const int64_t B = x.size(0), heads = x.size(1), D = x.size(2);
+    check_rope(cos, sin, x, D);
+    const int32_t* pp = nullptr;
+    if (pos_t.has_value()) {
+        const Tensor& p = *pos_t;
+        TORCH_CHECK(p.is_cuda() && p.scalar_type() == at::kInt && p.is_contiguous() && p.numel() == B,
+                    "pos must be a contiguous CUDA int32 tensor of B elements");
+        pp = p.data_ptr<int32_t>();
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor out = at::empty_like(x);
+    check_rc(msaq_rope(x.data_ptr(), out.data_ptr(), B, heads, D, cos.data_ptr<float>(), sin.data_ptr<float>(), cos.size(0),
+                       pos, pp, stream_of(x)), "rope");
+    return out;
 }
 
 // ---- layer-step glue ----------------------------------------------------------
@@ -430,6 +494,13 @@ TORCH_LIBRARY(msaq, m) {
     m.def("kv_append_pair(Tensor Xk, Tensor Xv, Tensor(a!) ks, Tensor(b!) ku, Tensor(c!) kh, Tensor(d!) vs, Tensor(e!) vu, "
           "Tensor(f!) vh, Tensor? pos_t, int B, int Hkv, int D, int NB, int pos, int Lcap, int u, int gs, bool rotate_k) -> ()",
           &kv_append_pair);
+    m.def("kv_append_pair_rope(Tensor Xk, Tensor Xv, Tensor(a!) ks, Tensor(b!) ku, Tensor(c!) kh, Tensor(d!) vs, Tensor(e!) vu, "
+          "Tensor(f!) vh, Tensor? pos_t, int B, int Hkv, int D, int NB, int pos, int Lcap, int u, int gs, bool rotate_k, "
+          "Tensor cos, Tensor sin) -> ()", &kv_append_pair_rope);
+    m.def("kv_decode_attention_rope(Tensor q, Tensor ks, Tensor ku, Tensor kh, Tensor vs, Tensor vu, Tensor vh, "
+          "Tensor seq_lens, int B, int H, int Hkv, int Lk, int D, int NB, int u, int gs, int Lcap, bool qrot, "
+          "Tensor cos, Tensor sin, Tensor? q_pos_t, int q_pos) -> Tensor", &kv_decode_attention_rope);
+    m.def("rope(Tensor x, Tensor cos, Tensor sin, Tensor? pos_t, int pos) -> Tensor", &rope);
     m.def("kv_decode_attention_varlen(Tensor q, Tensor ks, Tensor ku, Tensor kh, "
           "Tensor vs, Tensor vu, Tensor vh, Tensor seq_lens, "
           "int B, int H, int Hkv, int Lk, int D, int NB, int u, int gs, int Lcap, bool qrot) -> Tensor",

@@ -172,25 +172,38 @@ class KVCache:
             _OPS.kv_write_into(X.contiguous(), pl[0], pl[1], pl[2], B * Hkv, L, D, self.nb, key0,
                                self.Lcap, self.u, self.gs, rot)
 
-    def append(self, k_new, v_new, pos):
-        """k_new, v_new [B,Hkv,D] bf16; pos an int (all sequences) or int32 tensor [B]."""
+    def append(self, k_new, v_new, pos, rope=None):
+        """k_new, v_new [B,Hkv,D] bf16; pos an int (all sequences) or int32 tensor [B].
+
+        rope = (cos, sin), fp32 [rows, D/2] as the reference's harness builds them
+        (tests/harness_batchsweep.py:118-131; rows == 1: the one position of this step, else indexed
+        by position): the K rows get the rotary embedding inside the same launch, before the
+        Hadamard rotation, exactly as rope_bthd followed by kv_append_rot would."""
         H = self.B * self.Hkv
         k_new = k_new.reshape(H, self.D).contiguous()
         v_new = v_new.reshape(H, self.D).contiguous()
         # one launch for both tensors (kv_append_rot + kv_append of the reference write the same bytes)
-        if isinstance(pos, int):
-            _OPS.kv_append_pair(k_new, v_new, *self.k, *self.v, None, self.B, self.Hkv, self.D, self.nb, pos,
+        pos_t, pos_i = (None, pos) if isinstance(pos, int) else (pos, 0)
+        if rope is None:
+            _OPS.kv_append_pair(k_new, v_new, *self.k, *self.v, pos_t, self.B, self.Hkv, self.D, self.nb, pos_i,
                                 self.Lcap, self.u, self.gs, self.rotate)
         else:
-            _OPS.kv_append_pair(k_new, v_new, *self.k, *self.v, pos, self.B, self.Hkv, self.D, self.nb, 0,
-                                self.Lcap, self.u, self.gs, self.rotate)
+            _OPS.kv_append_pair_rope(k_new, v_new, *self.k, *self.v, pos_t, self.B, self.Hkv, self.D, self.nb, pos_i,
+                                     self.Lcap, self.u, self.gs, self.rotate, rope[0], rope[1])
 
-    def attend(self, q, Lk, seq_lens=None):
-        """q [B,Hq,D] bf16 -> [B,Hq,D] bf16 over the first Lk keys (seq_lens[b] if given)."""
+    def attend(self, q, Lk, seq_lens=None, rope=None, q_pos=None):
+        """q [B,Hq,D] bf16 -> [B,Hq,D] bf16 over the first Lk keys (seq_lens[b] if given).
+
+        rope = (cos, sin) with q_pos (int or int32 tensor [B], the position of the query token):
+        the query rows get the rotary embedding in the kernel prologue."""
         Hq = int(q.shape[1])
         if seq_lens is None:
             seq_lens = self._full_lens.get(Lk)
             if seq_lens is None:
                 seq_lens = self._full_lens[Lk] = torch.full((self.B,), Lk, dtype=torch.int32, device=q.device)
-        return _OPS.kv_decode_attention_varlen(q, *self.k, *self.v, seq_lens, self.B, Hq, self.Hkv, Lk, self.D,
-                                               self.nb, self.u, self.gs, self.Lcap, self.rotate)
+        if rope is None:
+            return _OPS.kv_decode_attention_varlen(q, *self.k, *self.v, seq_lens, self.B, Hq, self.Hkv, Lk, self.D,
+                                                   self.nb, self.u, self.gs, self.Lcap, self.rotate)
+        pos_t, pos_i = (None, int(q_pos)) if isinstance(q_pos, int) else (q_pos, 0)
+        return _OPS.kv_decode_attention_rope(q, *self.k, *self.v, seq_lens, self.B, Hq, self.Hkv, Lk, self.D, self.nb,
+                                             self.u, self.gs, self.Lcap, self.rotate, rope[0], rope[1], pos_t, pos_i)

@@ -37,11 +37,13 @@ def split_range(total, parts, idx):
 
 
 def shard_rows(p, lo, hi):
-    """Rows [lo, hi) of a packed weight: a pack dict of the slice (views where possible)."""
+    """Rows [lo, hi) of a packed weight: a pack dict of the slice (views where possible).  The row-major
+    planes are optional: a dict that carries only the column-major ones (what the kernels read) shards too."""
     out = dict(p)
     out["scale_exp"] = p["scale_exp"][:, lo:hi]
-    out["upper"] = p["upper"][:, :, lo:hi]
-    out["shared"] = p["shared"][:, :, lo:hi]
+    if "upper" in p:
+        out["upper"] = p["upper"][:, :, lo:hi]
+        out["shared"] = p["shared"][:, :, lo:hi]
     out["upper_cm"] = p["upper_cm"][:, lo:hi, :]
     out["shared_cm"] = p["shared_cm"][:, lo:hi, :]
     out["OUT"] = hi - lo
@@ -52,7 +54,8 @@ def shard_kblocks(p, b_lo, b_hi):
     """K blocks [b_lo, b_hi) of a packed weight (input features b_lo*32 .. b_hi*32)."""
     out = dict(p)
     for k in ("scale_exp", "upper", "shared", "upper_cm", "shared_cm"):
-        out[k] = p[k][b_lo:b_hi]
+        if k in p:
+            out[k] = p[k][b_lo:b_hi]
     out["nb"] = b_hi - b_lo
     out["K"] = (b_hi - b_lo) * BLOCK
     return out
@@ -69,8 +72,9 @@ def concat_rows(parts):
         kw = lambda a: dict(axis=a)
     out = dict(parts[0])
     out["scale_exp"] = cat([q["scale_exp"] for q in parts], **kw(1))
-    out["upper"] = cat([q["upper"] for q in parts], **kw(2))
-    out["shared"] = cat([q["shared"] for q in parts], **kw(2))
+    if "upper" in parts[0]:
+        out["upper"] = cat([q["upper"] for q in parts], **kw(2))
+        out["shared"] = cat([q["shared"] for q in parts], **kw(2))
     out["upper_cm"] = cat([q["upper_cm"] for q in parts], **kw(1))
     out["shared_cm"] = cat([q["shared_cm"] for q in parts], **kw(1))
     out["OUT"] = sum(int(q["OUT"]) for q in parts)
@@ -160,51 +164,52 @@ def peer_all_reduce(group, numel, dtype, device, slots=2):
 # --------------------------------------------------------------------------
 # the step
 # --------------------------------------------------------------------------
+class MsaqGlue:
+    """The element-wise steps between the linears on this library's CUDA kernels (msaq_rmsnorm,
+    msaq_add_residual, msaq_silu_mul); raises when the operator module is not built."""
+
+    def __init__(self):
+        from . import ops
+        ops._require()
+        import torch
+        self._ops = torch.ops.msaq
+
+    def rmsnorm(self, x, eps):
+        return self._ops.rmsnorm(x.contiguous(), eps)
+
+    def add(self, h, delta):
+        return self._ops.add_residual(h.contiguous(), delta.contiguous())
+
+    def silu_mul(self, gu):
+        return self._ops.silu_mul(gu.contiguous())
+
+
 class DecoderLayerTP:
     """One rank's share of a decoder layer decode step.
 
     linears : {'qkv','o','gate_up','down'} objects with .fwd(x[B,K]) -> [B,OUT]
-    cache   : object with .append(k[B,kv,D], v[B,kv,D], pos) and .attend(q[B,q,D], Lk, seq_lens)
+    cache   : object with .append(k[B,kv,D], v[B,kv,D], pos, rope) and .attend(q[B,q,D], Lk, seq_lens, rope, q_pos)
     all_reduce : callable(tensor) summing in place over the ranks (identity when world == 1)
+    glue    : object with rmsnorm(x, eps), add(h, delta), silu_mul(gu) for the element-wise steps between
+              the linears; default: this library's CUDA kernels (there is no other compute path in the
+              package -- the CPU tests of the host logic bring their own stand-in)
     """
 
-    def __init__(self, shape, world, linears, cache, all_reduce=None, eps=1e-5):
+    def __init__(self, shape, world, linears, cache, all_reduce=None, eps=1e-5, glue=None):
         self.shape, self.world = shape, world
         self.q_heads, self.kv_heads, self.ffn_rows = shape.local(world)
         self.lin, self.cache, self.eps = linears, cache, eps
         self.all_reduce = all_reduce if all_reduce is not None else (lambda t: t)
+        self.glue = glue if glue is not None else MsaqGlue()
 
-    @staticmethod
-    def _fused(x):
-        """The fused glue ops of this library, when x lives on a GPU and they are registered."""
-        import torch
-        if x.is_cuda and hasattr(torch.ops, "msaq") and hasattr(torch.ops.msaq, "rmsnorm"):
-            return torch.ops.msaq
-        return None
+    def _rmsnorm(self, x, eps):
+        return self.glue.rmsnorm(x, eps)
 
-    @classmethod
-    def _rmsnorm(cls, x, eps):
-        import torch
-        f = cls._fused(x)
-        if f is not None:
-            return f.rmsnorm(x.contiguous(), eps)
-        xf = x.float()
-        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+    def _add(self, h, delta):
+        return self.glue.add(h, delta)
 
-    @classmethod
-    def _add(cls, h, delta):
-        f = cls._fused(h)
-        if f is not None:
-            return f.add_residual(h.contiguous(), delta.contiguous())
-        return (h.float() + delta.float()).to(h.dtype)
-
-    @classmethod
-    def _silu_mul(cls, gu, F):
-        import torch
-        f = cls._fused(gu)
-        if f is not None:
-            return f.silu_mul(gu.contiguous())
-        return (torch.nn.functional.silu(gu[:, :F].float()) * gu[:, F:].float()).to(gu.dtype)
+    def _silu_mul(self, gu, F):
+        return self.glue.silu_mul(gu)
 
     def _partial(self, lin, x):
         """A K-sharded linear's contribution: fp32 when it goes into an all-reduce (straight from the
@@ -215,11 +220,14 @@ class DecoderLayerTP:
             return lin.fwd_f32(x)
         return lin.fwd(x).float()
 
-    def step(self, h, pos, Lk, seq_lens=None):
+    def step(self, h, pos, Lk, seq_lens=None, rope=None):
         """h [B, hidden] bf16 (replicated on every rank) -> new h [B, hidden] bf16 (replicated).
 
         pos: slot the new token's K/V go to (int, or int32 tensor [B]); Lk: keys attended
-        after the append (seq_lens[b] per sequence if given).
+        after the append (seq_lens[b] per sequence if given).  rope = (cos, sin) fp32 [rows, D/2]
+        (tests/harness_batchsweep.py:118-131 of the reference): q and k get the rotary embedding at
+        `pos` between the QKV projection and the append, as the reference's decode_step does (:237) --
+        inside the append and the attention kernels, not as launches of their own.
 
         Linears that offer fwd_fused (ops.PackedLinear on a GPU) take the rmsnorm, the
         residual add + rmsnorm and the SiLU*mul inside their activation staging; any other
@@ -234,8 +242,12 @@ class DecoderLayerTP:
         q = qkv[:, : self.q_heads * d].reshape(B, self.q_heads, d)
         k = qkv[:, self.q_heads * d:(self.q_heads + self.kv_heads) * d].reshape(B, self.kv_heads, d)
         v = qkv[:, (self.q_heads + self.kv_heads) * d:].reshape(B, self.kv_heads, d)
-        self.cache.append(k, v, pos)
-        a = self.cache.attend(q.contiguous(), Lk, seq_lens)            # [B, q, d], heads local
+        if rope is None:
+            self.cache.append(k, v, pos)
+            a = self.cache.attend(q.contiguous(), Lk, seq_lens)        # [B, q, d], heads local
+        else:
+            self.cache.append(k, v, pos, rope)
+            a = self.cache.attend(q.contiguous(), Lk, seq_lens, rope, pos)
         o = self._partial(self.lin["o"], a.reshape(B, self.q_heads * d))   # partial over the local K range
         o = self.all_reduce(o) if self.world > 1 else o
         if fused:

@@ -16,6 +16,9 @@ What is recorded
   rot_*   the fp32 butterfly rotation written out as plain loops (the formula of
           the reference's append/rotate kernels), reference pack_kv() of those
           values, and the reference's host formulation bf16(K) @ H/sqrt(n)
+  rope_*  the rotary embedding of the reference's harness (tests/harness_batchsweep.py:
+          rope_tables, rope_pos, rope_bthd, executed from its source with torch on the CPU):
+          tables, rotated rows, and reference pack_kv() of rope -> butterfly rotation
 """
 
 import math
@@ -50,6 +53,20 @@ def butterfly_rows(x):
             h <<= 1
         out[r] = np.array(v, np.float32) * inv
     return out
+
+
+def harness_namespace(ref_root, names):
+    """The named top-level definitions of the reference's tests/harness_batchsweep.py, executed from
+    its source in a namespace of their own (the module itself needs a GPU to import)."""
+    import ast
+    import torch
+    with open(os.path.join(ref_root, "tests", "harness_batchsweep.py")) as f:
+        tree = ast.parse(f.read())
+    ns = {"torch": torch, "np": np}
+    for node in tree.body:
+        if isinstance(node, (ast.FunctionDef, ast.ClassDef)) and node.name in names:
+            exec(compile(ast.Module([node], []), "harness_batchsweep.py", "exec"), ns)
+    return ns
 
 
 def edge_blocks(rng):
@@ -135,6 +152,33 @@ def main():
         p = rp.pack_kv(rot, u, gs)
         for k in ("scale_exp", "upper", "shared"):
             out[f"rot_{k}_u{u}_gs{gs}"] = p[k]
+
+    # ---- rotary embedding (own generator: the arrays above keep their values) ----
+    import torch
+    hs = harness_namespace(ref_root, ("Cfg", "rope_tables", "rope_pos", "rope_bthd"))
+    rng2 = np.random.default_rng(20251126)
+    Lp, Hh, hd = 40, 3, hs["Cfg"].head_dim
+    cos, sin = hs["rope_tables"](Lp, "cpu")
+    out["rope_cos"], out["rope_sin"] = cos.numpy(), sin.numpy()
+    xr = torch.from_numpy(rng2.standard_normal((2, Lp, Hh, hd)).astype(np.float32))
+    xr[..., [3, 40, 77, 120]] *= 20
+    xr = xr.to(torch.bfloat16)
+    out["rope_x"] = xr.float().numpy()
+    yr = hs["rope_bthd"](xr, cos, sin)
+    assert yr.dtype == torch.bfloat16
+    out["rope_y"] = yr.float().numpy()
+    c1, s1 = hs["rope_pos"](8191, "cpu")                   # the single-position tables of a decode step
+    out["rope_cos_8191"], out["rope_sin_8191"] = c1.numpy(), s1.numpy()
+    x1 = torch.from_numpy(rng2.standard_normal((4, 1, Hh, hd)).astype(np.float32)).to(torch.bfloat16)
+    out["rope_x1"] = x1.float().numpy()
+    out["rope_y1"] = hs["rope_bthd"](x1, c1, s1).float().numpy()
+    # rope -> butterfly rotation -> pack: what a fused RoPE + rotate + append must write
+    kro = out["rope_y"][0].transpose(1, 0, 2)              # [H, L, D]
+    rotk = butterfly_rows(np.ascontiguousarray(kro).reshape(-1, hd)).reshape(Hh, Lp, hd)
+    for u, gs in ((4, 2), (3, 8), (2, 4)):
+        p = rp.pack_kv(rotk, u, gs)
+        for k in ("scale_exp", "upper", "shared"):
+            out[f"ropek_{k}_u{u}_gs{gs}"] = p[k]
 
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "msaq_golden.npz")
     np.savez_compressed(dst, **out)

@@ -91,14 +91,18 @@ class _F64Cache:
             self.K[b, :, : K.shape[2]] = orc.dequant_kv(orc.pack_kv_rotated(K[b], u, gs))
             self.V[b, :, : V.shape[2]] = orc.dequant_kv(orc.pack_kv(V[b], u, gs))
 
-    def append(self, k, v, pos):
+    def append(self, k, v, pos, rope=None):
         k, v = k.float().numpy(), v.float().numpy()
+        if rope is not None:
+            k = orc.rope(k, rope[0].cpu().numpy()[0], rope[1].cpu().numpy()[0])
         for b in range(k.shape[0]):
             self.K[b, :, pos] = orc.dequant_kv(orc.pack_kv_rotated(k[b][:, None, :], self.u, self.gs))[:, 0]
             self.V[b, :, pos] = orc.dequant_kv(orc.pack_kv(v[b][:, None, :], self.u, self.gs))[:, 0]
 
-    def attend(self, q, Lk, seq_lens=None):
+    def attend(self, q, Lk, seq_lens=None, rope=None, q_pos=None):
         qn = q.float().numpy()
+        if rope is not None:
+            qn = orc.rope(qn, rope[0].cpu().numpy()[0], rope[1].cpu().numpy()[0])
         out = []
         for b in range(qn.shape[0]):
             qr = orc.rotate_f32(qn[b]).astype(np.float64)
@@ -106,10 +110,32 @@ class _F64Cache:
         return torch.from_numpy(orc.to_bf16(np.stack(out).astype(np.float32))).to(torch.bfloat16)
 
 
+class _F64Glue:
+    """The element-wise steps in float64 with the bf16 roundings of the layer's intermediates."""
+
+    @staticmethod
+    def _bf(a):
+        return torch.from_numpy(orc.to_bf16(np.asarray(a, np.float32))).to(torch.bfloat16)
+
+    def rmsnorm(self, x, eps):
+        xf = x.double().numpy()
+        return self._bf(xf / np.sqrt((xf ** 2).mean(-1, keepdims=True) + eps))
+
+    def add(self, h, delta):
+        return self._bf(h.double().numpy() + delta.double().numpy())
+
+    def silu_mul(self, gu):
+        g = gu.double().numpy()
+        F = g.shape[1] // 2
+        return self._bf(g[:, :F] / (1.0 + np.exp(-g[:, :F])) * g[:, F:])
+
+
+@pytest.mark.parametrize("with_rope", [False, True], ids=["no_rope", "rope"])
 @pytest.mark.parametrize("B", [1, 3])
-def test_layer_step_matches_float64_restatement(rng, B):
-    """One decode step of a small Llama-shaped layer: packed GEMVs, rotated append, flash-decode,
-    fused glue -- against the same step in float64 on the dequantised tensors."""
+def test_layer_step_matches_float64_restatement(rng, B, with_rope):
+    """One decode step of a small Llama-shaped layer: packed GEMVs, RoPE on q and k, rotated append,
+    flash-decode, fused glue -- against the same step in float64 on the dequantised tensors (the wiring of
+    the reference's decode_step, tests/harness_batchsweep.py:230-243)."""
     from ms_kernel_b200 import ops, tp
     u, gs = 4, 2
     shape = tp.LayerShape(hidden=512, n_q=8, n_kv=2, head_dim=128, ffn=1024)
@@ -127,10 +153,16 @@ def test_layer_step_matches_float64_restatement(rng, B):
     cache = ops.KVCache(B, shape.n_kv, d, Lcap, u, gs, "cuda", rotate=True)
     cache.fill(_bf(K0), _bf(V0), 0)
     layer = tp.DecoderLayerTP(shape, 1, {k: ops.PackedLinear(v, "cuda") for k, v in sh.items()}, cache)
-    got = layer.step(_bf(h), L - 1, L).float().cpu().numpy()
+    rope_dev = rope_cpu = None
+    if with_rope:
+        cos, sin = orc.rope_tables(np.array([L - 1]), d)
+        rope_cpu = (torch.from_numpy(cos), torch.from_numpy(sin))
+        rope_dev = (rope_cpu[0].cuda(), rope_cpu[1].cuda())
+    got = layer.step(_bf(h), L - 1, L, rope=rope_dev).float().cpu().numpy()
 
-    ref_layer = tp.DecoderLayerTP(shape, 1, {k: _F64Linear(v) for k, v in sh.items()}, _F64Cache(K0, V0, u, gs, Lcap))
-    ref = ref_layer.step(torch.from_numpy(h).to(torch.bfloat16), L - 1, L).float().numpy()
+    ref_layer = tp.DecoderLayerTP(shape, 1, {k: _F64Linear(v) for k, v in sh.items()}, _F64Cache(K0, V0, u, gs, Lcap),
+                                  glue=_F64Glue())
+    ref = ref_layer.step(torch.from_numpy(h).to(torch.bfloat16), L - 1, L, rope=rope_cpu).float().numpy()
     # the residual stream carries h through unchanged, so compare the update the layer made
     assert orc.rel_fro(got - h, ref - h) < 2e-2
     assert orc.rel_fro(got, ref) < 4 * REL_FRO_TOL

@@ -87,3 +87,25 @@ def test_to_bf16_matches_torch(rng):
     x = (rng.standard_normal(4096) * rng.uniform(1e-3, 1e3, 4096)).astype(np.float32)
     ref = torch.from_numpy(x).to(torch.bfloat16).float().numpy()
     assert np.array_equal(orc.to_bf16(x), ref)
+
+
+def test_rope_matches_reference_harness(golden):
+    """The harness's rope_bthd on its own tables, bit for bit; the table formula to float32 rounding."""
+    x, y = golden["rope_x"], golden["rope_y"]                      # [B, L, H, D]
+    cos, sin = golden["rope_cos"], golden["rope_sin"]              # [L, D/2]
+    got = orc.rope(x, cos[None, :, None, :], sin[None, :, None, :])
+    assert np.array_equal(got, y)
+    got1 = orc.rope(golden["rope_x1"], golden["rope_cos_8191"][None, :, None, :],
+                    golden["rope_sin_8191"][None, :, None, :])
+    assert np.array_equal(got1, golden["rope_y1"])
+    c, s = orc.rope_tables(np.arange(cos.shape[0]), 2 * cos.shape[1])
+    assert np.abs(c - cos).max() < 1e-5 and np.abs(s - sin).max() < 1e-5
+    # at an angle of ~8191 rad the last bit of the float32 product pos * inv already moves the cosine
+    c1, s1 = orc.rope_tables(np.array([8191]), 2 * cos.shape[1])
+    assert np.abs(c1 - golden["rope_cos_8191"]).max() < 2e-3
+    # rope -> rotation -> pack equals the reference's pack_kv of the same chain
+    k = np.ascontiguousarray(y[0].transpose(1, 0, 2))              # [H, L, D]
+    for u, gs in ((4, 2), (3, 8), (2, 4)):
+        p = orc.pack_kv_rotated(k, u, gs)
+        for key in ("scale_exp", "upper", "shared"):
+            assert np.array_equal(p[key], golden[f"ropek_{key}_u{u}_gs{gs}"]), (u, gs, key)

@@ -57,6 +57,27 @@ class _OracleLinear:
         return (x.double() @ self.W.T).to(torch.bfloat16)
 
 
+class _TorchGlue:
+    """Element-wise steps of the layer in plain PyTorch: the CPU stand-in for the library's CUDA glue kernels."""
+
+    def rmsnorm(self, x, eps):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+
+    def add(self, h, delta):
+        return (h.float() + delta.float()).to(h.dtype)
+
+    def silu_mul(self, gu):
+        F = gu.shape[1] // 2
+        return (torch.nn.functional.silu(gu[:, :F].float()) * gu[:, F:].float()).to(gu.dtype)
+
+
+def _rope(x, rope):
+    """x [B, heads, D] bf16 -> rotary embedding with tables (cos, sin) [1, D/2] (one position)."""
+    c, s = rope[0][0].numpy(), rope[1][0].numpy()
+    return torch.from_numpy(orc.rope(x.float().numpy(), c, s)).to(torch.bfloat16)
+
+
 class _OracleCache:
     """Float KV cache with the layer's interface (append / attend); keys kept un-rotated,
     which is equivalent for attention since rotation preserves q.k."""
@@ -65,11 +86,15 @@ class _OracleCache:
         self.K = torch.zeros(B, kv, L, D, dtype=torch.float64)
         self.V = torch.zeros(B, kv, L, D, dtype=torch.float64)
 
-    def append(self, k, v, pos):
+    def append(self, k, v, pos, rope=None):
+        if rope is not None:
+            k = _rope(k, rope)
         self.K[:, :, pos] = k.double()
         self.V[:, :, pos] = v.double()
 
-    def attend(self, q, Lk, seq_lens=None):
+    def attend(self, q, Lk, seq_lens=None, rope=None, q_pos=None):
+        if rope is not None:
+            q = _rope(q, rope)
         B, Hq, D = q.shape
         out = np.stack([orc.decode_attention(q[b].double().numpy(), self.K[b, :, :Lk].numpy(), self.V[b, :, :Lk].numpy())
                         for b in range(B)])
@@ -97,9 +122,10 @@ def _run_rank(rank, world, port, seed, q, shape_args=None):
         dist.all_reduce(t)
         return t
 
-    layer = tp.DecoderLayerTP(SHAPE, world, lin, cache, all_reduce)
+    layer = tp.DecoderLayerTP(SHAPE, world, lin, cache, all_reduce, glue=_TorchGlue())
     h = torch.from_numpy(rng.standard_normal((B, SHAPE.hidden)).astype(np.float32)).to(torch.bfloat16)
-    out = layer.step(h, L - 1, L)
+    cos, sin = orc.rope_tables(np.array([L - 1]), SHAPE.head_dim)
+    out = layer.step(h, L - 1, L, rope=(torch.from_numpy(cos), torch.from_numpy(sin)))
     if rank == 0:
         q.put(out.float().numpy())
     if world > 1:
@@ -138,8 +164,8 @@ def test_gloo_step_matches_single_rank(worlds, shape_args):
 
 def test_algorithmic_bytes_add_up():
     shape = tp.LayerShape.llama31_70b()
-    one = tp.DecoderLayerTP(shape, 1, {}, None).algorithmic_bytes(1, 8192, 4, 2)
-    eight = tp.DecoderLayerTP(shape, 8, {}, None).algorithmic_bytes(1, 8192, 4, 2)
+    one = tp.DecoderLayerTP(shape, 1, {}, None, glue=_TorchGlue()).algorithmic_bytes(1, 8192, 4, 2)
+    eight = tp.DecoderLayerTP(shape, 8, {}, None, glue=_TorchGlue()).algorithmic_bytes(1, 8192, 4, 2)
     weights = (10240 * 8192 + 8192 * 8192 + 57344 * 8192 + 8192 * 28672) // 32 * 25
     assert abs(one - weights - 8 * 8192 * 200) < 2e6          # + activations
     assert abs(8 * eight - one) < 3e6                         # replicated activations only
