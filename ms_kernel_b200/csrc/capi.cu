@@ -1,5 +1,6 @@
 // Error plumbing, launch accounting and device queries shared by the entry points.
 #include <atomic>
+#include <chrono>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -34,6 +35,8 @@ namespace {
 std::atomic<int> g_opt_chained{-1};
 std::atomic<int> g_opt_tmem{1};
 std::atomic<int> g_opt_polls{1 << 20};
+std::atomic<int> g_opt_inkernel{1};
+std::atomic<uint32_t> g_call_tag{0};
 std::atomic<int> g_opt_skip{-1};
 
 // One status word per GPU that loads the library: kernels OR a bit into it when a bounded wait
@@ -41,6 +44,23 @@ std::atomic<int> g_opt_skip{-1};
 __device__ int g_sticky_status;
 std::atomic<int*> g_sticky_ptr[64];
 }  // namespace
+
+bool option_inkernel_staging() { return g_opt_inkernel.load(std::memory_order_relaxed) != 0; }
+
+uint32_t next_call_tag() {
+    uint32_t t = g_call_tag.load(std::memory_order_relaxed);
+    if (t == 0) {
+        // first use: start somewhere unpredictable, so that whatever a fresh workspace holds is unlikely to look like a tag
+        uint32_t seed = (uint32_t)std::chrono::steady_clock::now().time_since_epoch().count() * 2654435761u;
+        seed ^= (uint32_t)(uintptr_t)&g_call_tag;
+        uint32_t expected = 0;
+        g_call_tag.compare_exchange_strong(expected, seed | 1u);
+    }
+    for (;;) {
+        t = (g_call_tag.fetch_add(1, std::memory_order_relaxed) + 1) & 0x7FFFFFFFu;      // 31 bits: the top bit marks "being cleared"
+        if (t != 0) return t;
+    }
+}
 
 unsigned option_wait_polls() { return (unsigned)g_opt_polls.load(std::memory_order_relaxed); }
 int option_test_skip_stage() { return g_opt_skip.load(std::memory_order_relaxed); }
@@ -118,6 +138,7 @@ extern "C" int msaq_set_option(int option, int value) {
             msaq::g_opt_polls.store(value, std::memory_order_relaxed);
             return MSAQ_OK;
         case MSAQ_OPT_TEST_SKIP_STAGE: msaq::g_opt_skip.store(value < 0 ? -1 : value, std::memory_order_relaxed); return MSAQ_OK;
+        case MSAQ_OPT_INKERNEL_STAGING: msaq::g_opt_inkernel.store(value ? 1 : 0, std::memory_order_relaxed); return MSAQ_OK;
         default: return msaq::fail(MSAQ_ERR_ARG, "unknown option %d", option);
     }
 }
@@ -127,6 +148,7 @@ extern "C" int msaq_get_option(int option) {
         case MSAQ_OPT_TENSOR_MEMORY: return msaq::option_tensor_memory() ? 1 : 0;
         case MSAQ_OPT_WAIT_POLLS: return (int)msaq::option_wait_polls();
         case MSAQ_OPT_TEST_SKIP_STAGE: return msaq::option_test_skip_stage();
+        case MSAQ_OPT_INKERNEL_STAGING: return msaq::option_inkernel_staging() ? 1 : 0;
         default: return msaq::fail(MSAQ_ERR_ARG, "unknown option %d", option);
     }
 }

@@ -19,7 +19,7 @@ namespace {
 struct MmaPlan {
     GemvSchedule sch;        // sch.nb counts units of `kb` K blocks
     int kb;
-    size_t xprep_bytes, ctl_off, partial_off, total;
+    size_t xprep_off, xprep_bytes, partial_off, total;      // status word at 0, counters at 256, then these
 };
 
 bool mma_eligible(int64_t OUT, int u, int gs, bool cm) { return cm && u == 4 && gs == 2 && OUT % 16 == 0; }
@@ -64,27 +64,36 @@ MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB) {
     if (stages < 2) stages = 2;
     s.stages = stages;
     p.xprep_bytes = ((size_t)NB * passes * GM_XREC + 255) & ~(size_t)255;
-    p.ctl_off = p.xprep_bytes;                                        // status word, then the tile counters
-    p.partial_off = p.ctl_off + ((256 + (size_t)s.col_tiles * GM_WARPS * sizeof(int) + 255) & ~(size_t)255);
+    const size_t ctl = (256 + (size_t)s.col_tiles * GM_WARPS * sizeof(unsigned long long) + 255) & ~(size_t)255;
+    p.xprep_off = ctl > WS_CTL_BYTES ? ctl : WS_CTL_BYTES;            // the control region: status word, then the tile counters
+    p.partial_off = p.xprep_off + p.xprep_bytes;
     p.total = p.partial_off + (((size_t)s.max_slots * rows * OUT * sizeof(float) + 255) & ~(size_t)255);
     return p;
 }
 
-template <int PASSES, int TC, int KB = 1>
-int launch_mma(const GemvMmaArgs& a, cudaStream_t st) {
+template <int PASSES, int TC, int KB, bool INK>
+int launch_mma_ink(const GemvMmaArgs& a, cudaStream_t st) {
     static int configured[64] = {};                      // largest dynamic smem size set per device
-    const int smem = a.sch.stages * KB * gm_stage_bytes(TC, PASSES);
+    const int smem = a.sch.stages * KB * gm_stage_bytes(TC, PASSES) + a.table_bytes;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && configured[dev] < smem) {
-        if (cudaFuncSetAttribute(gemv_u4gs2_mma_kernel<PASSES, TC, KB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(gemv_u4gs2_mma_kernel<PASSES, TC, KB, INK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  smem) != cudaSuccess)
             return fail(MSAQ_ERR_CUDA, "cannot reserve %d bytes of shared memory", smem);
         configured[dev] = smem;
     }
-    launch_chained(gemv_u4gs2_mma_kernel<PASSES, TC, KB>, dim3(a.sch.grid), dim3(GM_THREADS), smem, st, a);
+    launch_chained(gemv_u4gs2_mma_kernel<PASSES, TC, KB, INK>, dim3(a.sch.grid), dim3(GM_THREADS), smem, st, a);
     count_launch();
     return check_launch("gemv_u4gs2_mma");
+}
+
+template <int PASSES, int TC, int KB = 1>
+int launch_mma(const GemvMmaArgs& a, cudaStream_t st) {
+    if constexpr (PASSES == 1) {
+        if (a.xmode >= 0) return launch_mma_ink<PASSES, TC, KB, true>(a, st);
+    }
+    return launch_mma_ink<PASSES, TC, KB, false>(a, st);
 }
 
 template <int PASSES>
@@ -149,7 +158,7 @@ int launch_umma(const GemvUmmaArgs& a, int smem, cudaStream_t st) {
 int run_umma(const __nv_bfloat16* X, const int8_t* se, const uint8_t* up, const uint8_t* sh, void* Y, float* Yf,
              int64_t M, int64_t OUT, int64_t NB, int u, void* ws, cudaStream_t st) {
     const UmmaPlan p = plan_umma(M, OUT, NB, u);
-    uint8_t* base = static_cast<uint8_t*>(ws);
+    uint8_t* base = static_cast<uint8_t*>(ws) + WS_CTL_BYTES;
     int* status = reinterpret_cast<int*>(base + p.ctl_off);
     float* partial = reinterpret_cast<float*>(base + p.partial_off);
     for (int64_t m0 = 0; m0 < M; m0 += GU_MAX_N) {        // more than 128 rows: one launch pair per 128-row tile
@@ -201,8 +210,9 @@ int run_mma(const __nv_bfloat16* X, const Prologue& pro, const int8_t* se, const
             void* Y, float* Yf, int64_t M, int64_t OUT, int64_t NB, void* ws, cudaStream_t st) {
     const MmaPlan p = plan_mma(M, OUT, NB);
     uint8_t* base = static_cast<uint8_t*>(ws);
-    int* status = reinterpret_cast<int*>(base + p.ctl_off);
-    int* counters = status + 64;
+    int* status = reinterpret_cast<int*>(base);
+    unsigned long long* counters = reinterpret_cast<unsigned long long*>(base + 256);
+    uint8_t* xprep = base + p.xprep_off;
     float* partial = reinterpret_cast<float*>(base + p.partial_off);
     const int64_t tile_rows = GM_MP * GM_MAX_PASSES, K = NB * BLOCK;
     const int64_t ldx = pro.mode == XP_SILU_MUL ? 2 * K : K;
@@ -214,20 +224,35 @@ int run_mma(const __nv_bfloat16* X, const Prologue& pro, const int8_t* se, const
         xa.X = X + m0 * ldx;
         xa.R = pro.r ? static_cast<const uint8_t*>(pro.r) + m0 * K * (pro.r_is_f32 ? 4 : 2) : nullptr;
         xa.h_out = pro.h_out ? static_cast<__nv_bfloat16*>(pro.h_out) + m0 * K : nullptr;
-        xa.xprep = base;
-        xa.status = status;
-        xa.tile_counters = counters;
-        xa.n_counters = p.sch.col_tiles * GM_WARPS;
-        xa.reset_status = m0 == 0 ? 1 : 0;
+        xa.xprep = xprep;
         xa.M = rows;
         xa.NB = (int)NB;
         xa.passes = passes;
         xa.ldx = (int)ldx;
         xa.r_is_f32 = pro.r_is_f32;
         xa.eps = pro.eps;
-        if (int rc = launch_xprep(xa, pro.mode, (unsigned)((warps * 32 + 127) / 128), st)) return rc;
-        GemvMmaArgs a{se, up, sh, base, partial, counters, status, sticky_status(), static_cast<__nv_bfloat16*>(Y), Yf,
-                      (int)m0, rows, (int)OUT, (int)NB, p.sch, option_wait_polls(), option_test_skip_stage()};
+        // Up to four rows, no prologue, and no CTA streams more than nine K blocks (the small problems, where fixed
+        // costs are most of the time): the main kernel stages the activations itself -- each of its nine warps writes
+        // one record into a table in shared memory while the first copies are in flight -- and no launch runs in
+        // front (4096x4096, one row: 11.8 -> 10.3 us).  With a prologue in front, or more blocks per CTA, the
+        // separate staging kernel is the faster arrangement: it runs under the tail of the kernel before it, while
+        // staging inside delays the consumers' start (measured on the 70B layer's GEMVs, one and eight GPUs).
+        GemvSchedule sch = p.sch;
+        const long long max_iter = (sch.units() + sch.grid - 1) / sch.grid;
+        const long long table = max_iter * p.kb * GM_XREC;
+        const bool in_kernel = passes == 1 && pro.mode == XP_PLAIN && option_inkernel_staging() && table <= GM_MAX_TABLE;
+        const uint32_t tag = next_call_tag();
+        if (in_kernel) {
+            const int per_sm = (sch.grid + sm_count() - 1) / sm_count();
+            int stages = (200 * 1024 / per_sm - (int)table) / (p.kb * gm_stage_bytes(sch.tc, passes));
+            sch.stages = stages > GM_MAX_STAGES ? GM_MAX_STAGES : stages < 2 ? 2 : stages;
+        } else if (int rc = launch_xprep(xa, pro.mode, (unsigned)((warps * 32 + 127) / 128), st)) {
+            return rc;
+        }
+        GemvMmaArgs a{se, up, sh, xprep, partial, counters, status, sticky_status(), static_cast<__nv_bfloat16*>(Y), Yf,
+                      (int)m0, rows, (int)OUT, (int)NB, sch, option_wait_polls(), option_test_skip_stage(),
+                      in_kernel ? pro.mode : -1, xa.X, xa.R, xa.h_out, (int)ldx, pro.r_is_f32, pro.eps, tag,
+                      in_kernel ? (int)table : 0};
         // the ring depth was planned for the first tile's pass count; a last, smaller tile may go deeper but need not
         int rc;
         switch (passes) {
@@ -274,7 +299,7 @@ int gemv_dispatch(const void* X, const int8_t* se, const uint8_t* up, const uint
     if (mma_usable(se, up, sh, ws, OUT, u, gs, cm))
         return run_mma(x, Prologue{XP_PLAIN, nullptr, 0, nullptr, 0.0f}, se, up, sh, Y, Yf, M, OUT, NB, ws, st);
 
-    return gemv_run_generic(x, se, up, sh, Y, Yf, M, OUT, NB, f, cm, ws, st);
+    return gemv_run_generic(x, se, up, sh, Y, Yf, M, OUT, NB, f, cm, static_cast<uint8_t*>(ws) + WS_CTL_BYTES, st);
 }
 
 }  // namespace
@@ -284,13 +309,13 @@ using namespace msaq;
 
 extern "C" size_t msaq_wonly_gemv_workspace(int64_t M, int64_t OUT, int64_t NB, int u, int gs) {
     if (M <= 0 || OUT <= 0 || NB <= 0) return 0;
-    size_t bytes = gemv_generic_workspace(M, OUT, NB);
+    size_t bytes = gemv_generic_workspace(M, OUT, NB) + WS_CTL_BYTES;
     if (mma_eligible(OUT, u, gs, true)) {
         const size_t tuned = plan_mma(M, OUT, NB).total;
         if (tuned > bytes) bytes = tuned;
     }
     if (umma_eligible(OUT, u, gs, true) && (u != 4 || M >= GU_MIN_M)) {
-        const size_t tm = plan_umma(M, OUT, NB, u).total;
+        const size_t tm = plan_umma(M, OUT, NB, u).total + WS_CTL_BYTES;
         if (tm > bytes) bytes = tm;
     }
     return bytes;

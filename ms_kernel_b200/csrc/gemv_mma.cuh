@@ -38,6 +38,7 @@ constexpr int GM_MP = 4;             // activation rows per MMA pass
 constexpr int GM_MAX_PASSES = 4;     // -> at most 16 rows per launch
 constexpr int GM_XREC = 320;         // bytes of staged activations per (block, pass)
 constexpr int GM_CTAS_PER_SM = 3;
+constexpr int GM_MAX_TABLE = (GM_WARPS + 1) * GM_XREC;   // largest in-kernel record table: one record per warp of the CTA
 
 // Stage layout for a tile of TC columns x one K block:
 //   upper [TC][16] | shared [TC][8] | scale [TC] | activations [passes][GM_XREC]
@@ -79,9 +80,6 @@ struct XprepArgs {
     const void* R;               // XP_ADD_NORM: the addend, bf16 or fp32, [M][K]
     __nv_bfloat16* h_out;        // XP_ADD_NORM: the sum, [M][K]
     uint8_t* xprep;
-    int* status;
-    int* tile_counters;
-    int n_counters, reset_status;
     int M, NB, passes, ldx, r_is_f32;
     float eps;
 };
@@ -94,8 +92,6 @@ gemv_xprep_kernel(const XprepArgs a) {
     __shared__ float red[GM_MP][4];
     const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
     const int warp = gtid >> 5, lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
-    if (a.reset_status && gtid == 0) *a.status = 0;
-    for (int i = gtid; i < a.n_counters; i += gridDim.x * blockDim.x) a.tile_counters[i] = 0;
     // a CTA is the four row slots (mm = 0..3) of one (block, pass)
     const int mm = warp % GM_MP, pass = (warp / GM_MP) % a.passes, blk = warp / (GM_MP * a.passes);
     const int m = pass * GM_MP + mm;
@@ -224,10 +220,10 @@ struct GemvMmaArgs {
     const int8_t* scale_exp;
     const uint8_t* upper_cm;
     const uint8_t* shared_cm;
-    const uint8_t* xprep;
+    const uint8_t* xprep;    // activation records written by gemv_xprep_kernel (xmode < 0)
     float* partial;          // [max_slots][rows][OUT]
-    int* tile_counters;      // [col_tiles], zeroed by the staging kernel
-    int* status;             // set to 1 when a bounded wait gave up
+    unsigned long long* tile_counters;   // [col_tiles][GM_WARPS] words {marker, count}, see gemv_count_arrival
+    int* status;             // holds the call tag when a bounded wait gave up during this call
     int* sticky;             // the library's per-device status word (may be null)
     __nv_bfloat16* y;        // [M][OUT]
     float* y_f32;            // optional
@@ -237,7 +233,124 @@ struct GemvMmaArgs {
     GemvSchedule sch;
     uint32_t max_polls;      // limit of every mbarrier wait (see mbar_wait_bounded)
     int skip_stage;          // test hook: the producer of CTA 0 stops before this stage (-1: never)
+    // Launches of up to four rows stage their activations themselves: the producer warp evaluates the
+    // XprepMode `xmode` (>= 0) for each K block it streams and writes the record straight into the
+    // ring stage, so no staging kernel runs in front.  X, R, h_out point at row m0.
+    int xmode;
+    const __nv_bfloat16* X;
+    const void* R;
+    __nv_bfloat16* h_out;
+    int ldx, r_is_f32;
+    float eps;
+    uint32_t tag;            // identifies this call in the counters and the status word; 31 bits, never 0
+    int table_bytes;         // shared memory in front of the ring that holds the in-kernel record table
 };
+
+// Sums of squares of the launch's rows (of X, or of bf16(X + R) for XP_ADD_NORM) by all threads of the
+// CTA in an order that depends on nothing but K: every CTA arrives at the same bits.
+__device__ __forceinline__ void gemv_row_sumsq(const GemvMmaArgs& a, int K, float (*red)[GM_WARPS + 1]) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool add = a.xmode == XP_ADD_NORM;
+    const float* Rf = static_cast<const float*>(a.R);
+    const __nv_bfloat16* Rh = static_cast<const __nv_bfloat16*>(a.R);
+    for (int r = 0; r < a.rows; ++r) {
+        float ss = 0.0f;
+        const uint4* xr = reinterpret_cast<const uint4*>(a.X + (int64_t)r * a.ldx);
+        for (int i0 = tid; i0 < K / 8; i0 += 4 * GM_THREADS) {
+            uint4 hv[4], dv[4], dv2[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const int i = i0 + b * GM_THREADS;
+                const bool in = i < K / 8;
+                hv[b] = in ? xr[i] : make_uint4(0u, 0u, 0u, 0u);
+                dv[b] = dv2[b] = make_uint4(0u, 0u, 0u, 0u);
+                if (add && in) {
+                    const int64_t o = (int64_t)r * K + i * 8;
+                    if (a.r_is_f32) {
+                        dv[b] = *reinterpret_cast<const uint4*>(Rf + o);
+                        dv2[b] = *reinterpret_cast<const uint4*>(Rf + o + 4);
+                    } else {
+                        dv[b] = *reinterpret_cast<const uint4*>(Rh + o);
+                    }
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const uint32_t w[4] = {hv[b].x, hv[b].y, hv[b].z, hv[b].w};
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { f[2 * j] = bf16_lo(w[j]); f[2 * j + 1] = bf16_hi(w[j]); }
+                if (add) {
+                    float d[8];
+                    if (a.r_is_f32) {
+                        d[0] = __uint_as_float(dv[b].x); d[1] = __uint_as_float(dv[b].y);
+                        d[2] = __uint_as_float(dv[b].z); d[3] = __uint_as_float(dv[b].w);
+                        d[4] = __uint_as_float(dv2[b].x); d[5] = __uint_as_float(dv2[b].y);
+                        d[6] = __uint_as_float(dv2[b].z); d[7] = __uint_as_float(dv2[b].w);
+                    } else {
+                        const uint32_t dw[4] = {dv[b].x, dv[b].y, dv[b].z, dv[b].w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) { d[2 * j] = bf16_lo(dw[j]); d[2 * j + 1] = bf16_hi(dw[j]); }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(__float2bfloat16_rn(f[j] + d[j]));
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);       // chunks past the row's end are zero
+            }
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) red[r][warp] = ss;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(GM_THREADS) : "memory");
+}
+
+// The activation record of K block `kb` (all rows of the launch), written by one warp into a ring
+// stage; same values and layout as gemv_xprep_kernel produces.  The planes of the rows beyond the
+// launch's are left as they are: an MMA column only feeds its own row's sums, and those are never stored.
+__device__ __forceinline__ void gemv_stage_block(const GemvMmaArgs& a, uint8_t* rec, int kb, int K, int lane,
+                                                 bool write_h, const float (&inv_rms)[GM_MP]) {
+    const int k = kb * BLOCK + lane;
+#pragma unroll
+    for (int m = 0; m < GM_MP; ++m) {
+        if (m >= a.rows) break;
+        const __nv_bfloat16* xr = a.X + (int64_t)m * a.ldx;
+        float x;
+        if (a.xmode == XP_PLAIN) {
+            x = __bfloat162float(xr[k]);
+        } else if (a.xmode == XP_SILU_MUL) {
+            const float g = __bfloat162float(xr[k]), u = __bfloat162float(xr[K + k]);
+            x = __bfloat162float(__float2bfloat16_rn(g / (1.0f + __expf(-g)) * u));
+        } else {
+            float hv = __bfloat162float(xr[k]);
+            if (a.xmode == XP_ADD_NORM) {
+                const int64_t o = (int64_t)m * K + k;
+                const float d = a.r_is_f32 ? static_cast<const float*>(a.R)[o]
+                                           : __bfloat162float(static_cast<const __nv_bfloat16*>(a.R)[o]);
+                const __nv_bfloat16 hb = __float2bfloat16_rn(hv + d);
+                if (write_h) a.h_out[o] = hb;
+                hv = __bfloat162float(hb);
+            }
+            x = __bfloat162float(__float2bfloat16_rn(hv * inv_rms[m]));
+        }
+        const uint32_t ax = __reduce_max_sync(0xffffffffu, __float_as_uint(x) & 0x7FFFFFFFu);
+        int E = (int)(ax >> 23) - 127;
+        E = ax == 0u ? 0 : max(-100, min(127, E));
+        int xi = __float2int_rn(x * __int_as_float((14 - E + 127) << 23));
+        xi = min(xi, 32639);
+        const int lo = (int)(int8_t)(xi & 0xFF), hi = (xi - lo) >> 8;
+        const int e = lane, t = 2 * (e >> 4) + ((e >> 1) & 1), j = (e & 1) * 4 + ((e & 15) >> 2);
+        rec[(2 * m) * 32 + t * 8 + j] = (uint8_t)hi;
+        rec[(2 * m + 1) * 32 + t * 8 + j] = (uint8_t)lo;
+        const int sx = __reduce_add_sync(0xffffffffu, xi);          // = 256 * sum(hi) + sum(lo)
+        if (lane == 0) {
+            int* tc = reinterpret_cast<int*>(rec + 256 + m * 16);
+            tc[0] = -8 * sx;
+            tc[1] = ax >= 0x7F800000u ? 0x7FC00000 : (int)((uint32_t)(E - 14 + 127) << 23);
+        }
+    }
+}
 
 // One 16-column x 32-element step of a warp: decode both columns' codes into the
 // int8 operand, one integer MMA per activation pass, scale and accumulate.
@@ -288,14 +401,93 @@ __device__ __forceinline__ void gemv_groups(int nq, uint32_t wb, uint32_t sbs, u
     }
 }
 
+// Counts one published partial sum on a (tile, warp) counter and returns how many there are now.
+// The 64-bit word is {marker, count}.  At rest a valid word is {GM_MARKER, 0}: the warp that finishes a
+// tile puts the count back to zero, so neither the next call nor a replay of a captured launch needs a
+// reset in front, and an arrival is a single atomic add (`seen` is the marker as the caller read it when
+// it started on the tile).  A workspace that was never used, or whose control region something else
+// wrote to, shows another marker: the first arrival to notice claims the word (marker -> GM_MARKER_BUSY),
+// clears the count and publishes GM_MARKER; arrivals that meet a claimed word wait for that.
+// (A tag-and-count compare-and-swap loop needs no marker but collapses when the thirty-odd CTAs of a tile
+// arrive together, +27 us on a 13 MB GEMV; per-slot flags with a sequentially consistent fence cost +3 us.)
+constexpr unsigned int GM_MARKER = 0x9E3779B9u, GM_MARKER_BUSY = 0x1E3779B9u;
+__device__ __forceinline__ unsigned int gemv_count_arrival(const GemvMmaArgs& a, unsigned long long* word, unsigned int seen) {
+    unsigned int* marker = reinterpret_cast<unsigned int*>(word);
+    unsigned int* count = marker + 1;
+    if (seen != GM_MARKER) {
+        bool ok = false;
+        for (uint32_t i = 0; i < a.max_polls; ++i) {
+            unsigned int m;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(m) : "l"(marker) : "memory");
+            if (m == GM_MARKER) { ok = true; break; }
+            if (m != GM_MARKER_BUSY && atomicCAS(marker, m, GM_MARKER_BUSY) == m) {
+                *reinterpret_cast<volatile unsigned int*>(count) = 0u;
+                __threadfence();
+                asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(marker), "r"(GM_MARKER) : "memory");
+                ok = true;
+                break;
+            }
+            __nanosleep(64);
+        }
+        if (!ok) {
+            report_wait_failure(a.status, (int)a.tag, a.sticky, WAIT_FAIL_GEMV_MMA);
+            return 0u;
+        }
+    }
+    unsigned int old;
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(count) : "memory");
+    return old + 1u;
+}
+
+// In-kernel staging (launches of up to four rows).  The activation records of the K blocks a CTA streams
+// live in a table in shared memory; record `i` belongs to the CTA's unit i / KB, K block i % KB of it.
+// gemv_stage_records writes the records [i_begin, i_end) that fall to this warp (every i_step-th).
+template <int KB>
+__device__ __forceinline__ void gemv_stage_records(const GemvMmaArgs& a, uint8_t* table, int i_begin, int i_end, int i_step,
+                                                   long long n_lo, int K, int lane, const float (&inv_rms)[GM_MP]) {
+    for (int i = i_begin; i < i_end; i += i_step) {
+        const long long n = n_lo + i / KB;
+        const int uc = (int)(n / a.sch.nb), ub = (int)(n % a.sch.nb), kb = ub * KB + i % KB;
+        if (kb < a.NB) gemv_stage_block(a, table + (size_t)i * GM_XREC, kb, K, lane, uc == 0, inv_rms);
+    }
+}
+
+// The start of a CTA: all nine warps take the row norms (where the prologue has one) and then one record
+// each, while the first copies are in flight.  The host uses this path only where a CTA streams at most nine
+// K blocks, i.e. where one round covers the table: staging more than that in the kernel delays the
+// consumers' start by more than the separate staging kernel costs (it overlaps the tail of the kernel before
+// it), and records written by the producer warp one unit ahead of its copies slow a two-stage ring down
+// (both measured: 57344x8192 70.5 and 77.0 us against 69.1 us behind the staging kernel).
+template <int KB>
+__device__ __forceinline__ void gemv_stage_start(const GemvMmaArgs& a, uint8_t* table, int units_a, long long n_lo, int K,
+                                                 float (*red)[GM_WARPS + 1], float (&inv_rms)[GM_MP]) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (a.xmode == XP_RMSNORM || a.xmode == XP_ADD_NORM) {
+        gemv_row_sumsq(a, K, red);
+#pragma unroll
+        for (int r = 0; r < GM_MP; ++r) {
+            float tot = 0.0f;
+#pragma unroll
+            for (int w = 0; w <= GM_WARPS; ++w) tot += red[r][w];
+            if (r < a.rows) inv_rms[r] = rsqrtf(tot / (float)K + a.eps);
+        }
+    }
+    gemv_stage_records<KB>(a, table, warp, units_a * KB, GM_WARPS + 1, n_lo, K, lane, inv_rms);
+    asm volatile("bar.sync 2, %0;" ::"n"(GM_THREADS) : "memory");
+}
+
 // KB = K blocks per ring stage (per unit).  Two halve the barrier hand-offs per byte where the tile
 // cannot get wider (few column tiles, many K blocks).
-template <int PASSES, int TC, int KB>
+// INK = the activation records come from this CTA's own table (in-kernel staging, PASSES == 1 only).
+template <int PASSES, int TC, int KB, bool INK = false>
 __global__ void __launch_bounds__(GM_THREADS, GM_CTAS_PER_SM)
 gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
-    extern __shared__ __align__(128) uint8_t smem[];
+    static_assert(!INK || PASSES == 1, "in-kernel staging serves launches of up to four rows");
+    extern __shared__ __align__(128) uint8_t smem_all[];
     __shared__ __align__(8) uint64_t bar_full[GM_MAX_STAGES];
     __shared__ __align__(8) uint64_t bar_empty[GM_MAX_STAGES];
+    __shared__ float norm_red[GM_MP][GM_WARPS + 1];
+    __shared__ unsigned int marker_sh[GM_WARPS];               // each warp's (tile, warp) counter marker, fetched early
 
     constexpr int GROUPS = TC / GM_GROUP;
     constexpr int OFF_SH = TC * 16, OFF_SC = TC * 24, OFF_X = TC * 25;
@@ -308,6 +500,11 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
     const long long n_lo = sch.lo(blockIdx.x), n_hi = sch.lo(blockIdx.x + 1);
     const int n_iter = (int)(n_hi - n_lo);
     int c = (int)(n_lo / sch.nb), blk = (int)(n_lo % sch.nb);
+    const int K = a.NB * BLOCK;
+    // In-kernel staging: the records live in a table in front of the ring (a.table_bytes of it), written once
+    // by all warps; otherwise they arrive with each stage's copies from the staging kernel's output.
+    constexpr bool stage_here = INK;
+    uint8_t* const smem = smem_all + (INK ? a.table_bytes : 0);
 
     if (tid == 0) {
         for (int s = 0; s < sch.stages; ++s) {
@@ -319,35 +516,58 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
     __syncthreads();
 
     if (warp == GM_WARPS) {
-        // ------------------------------ producer ------------------------------
+        // ------------------------------ producer warp ------------------------------
+        chain_wait();                              // activations (or their records) come from the kernel before this one
+        const bool inject = a.skip_stage >= 0 && blockIdx.x == 0;
+        int s = 0, issued = 0;
+        uint32_t ph = 1;                           // parity of the "previous" empty phase: passes at once on a fresh barrier
+        int ci = c, bi = blk;                      // the next unit to issue
+        auto issue = [&](int uc, int ub, int us) {
+            const int o0 = uc * TC, cv = min(TC, a.OUT - o0);
+            const uint32_t bar = smem_u32(&bar_full[us]);
+            const int b0 = ub * KB, nblk = min(KB, a.NB - b0);          // `ub` counts units within the tile
+            mbar_expect_tx(bar, (uint32_t)(nblk * (cv * 25 + (stage_here ? 0 : PASSES * GM_XREC))));
+#pragma unroll
+            for (int j = 0; j < KB; ++j) {
+                if (j < nblk) {
+                    const uint32_t base = smem_u32(smem) + us * STAGE_BYTES + j * SUB_BYTES;
+                    const int64_t col = (int64_t)(b0 + j) * a.OUT + o0;
+                    bulk_g2s(base, a.upper_cm + col * 16, (uint32_t)cv * 16, bar);
+                    bulk_g2s(base + OFF_SH, a.shared_cm + col * 8, (uint32_t)cv * 8, bar);
+                    bulk_g2s(base + OFF_SC, a.scale_exp + col, (uint32_t)cv, bar);
+                    if (!stage_here)
+                        bulk_g2s(base + OFF_X, a.xprep + (int64_t)(b0 + j) * PASSES * GM_XREC, (uint32_t)(PASSES * GM_XREC), bar);
+                }
+            }
+        };
+        int pre = 0;
+        if constexpr (INK) {
+            // The first ring-full of weights goes out at once; the whole warp then helps with the records (the
+            // CTA-wide barrier at the end of that round orders them before the consumers' reads).
+            float inv_rms[GM_MP] = {1.0f, 1.0f, 1.0f, 1.0f};
+            pre = min(sch.stages, n_iter);
+            if (inject) pre = min(pre, a.skip_stage);
+            if (lane == 0) {
+                for (int it = 0; it < pre; ++it) {
+                    issue(ci, bi, it);
+                    if (++bi == sch.nb) { bi = 0; ++ci; }
+                }
+            }
+            gemv_stage_start<KB>(a, smem_all, n_iter, n_lo, K, norm_red, inv_rms);
+            issued = pre;
+            s = pre;
+            if (s == sch.stages) { s = 0; ph ^= 1u; }
+        }
         if (lane == 0) {
-            chain_wait();                          // the staged activations come from the kernel before this one
-            int s = 0, issued = 0;
-            uint32_t ph = 1;                       // parity of the "previous" empty phase: passes at once on a fresh barrier
-            const bool inject = a.skip_stage >= 0 && blockIdx.x == 0;
-            for (int it = 0; it < n_iter; ++it) {
+            for (int it = pre; it < n_iter; ++it) {
                 if (inject && it == a.skip_stage) break;          // the consumers' wait for this stage runs out
                 if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ph, a.max_polls)) {
-                    report_wait_failure(a.status, a.sticky, WAIT_FAIL_GEMV_MMA);
+                    report_wait_failure(a.status, (int)a.tag, a.sticky, WAIT_FAIL_GEMV_MMA);
                     break;
                 }
                 ++issued;
-                const int o0 = c * TC, cv = min(TC, a.OUT - o0);
-                const uint32_t bar = smem_u32(&bar_full[s]);
-                const int b0 = blk * KB, nblk = min(KB, a.NB - b0);         // `blk` counts units within the tile
-                mbar_expect_tx(bar, (uint32_t)(nblk * (cv * 25 + PASSES * GM_XREC)));
-#pragma unroll
-                for (int j = 0; j < KB; ++j) {
-                    if (j < nblk) {
-                        const uint32_t base = smem_u32(smem) + s * STAGE_BYTES + j * SUB_BYTES;
-                        const int64_t col = (int64_t)(b0 + j) * a.OUT + o0;
-                        bulk_g2s(base, a.upper_cm + col * 16, (uint32_t)cv * 16, bar);
-                        bulk_g2s(base + OFF_SH, a.shared_cm + col * 8, (uint32_t)cv * 8, bar);
-                        bulk_g2s(base + OFF_SC, a.scale_exp + col, (uint32_t)cv, bar);
-                        bulk_g2s(base + OFF_X, a.xprep + (int64_t)(b0 + j) * PASSES * GM_XREC, (uint32_t)(PASSES * GM_XREC), bar);
-                    }
-                }
-                if (++blk == sch.nb) { blk = 0; ++c; }
+                issue(ci, bi, s);
+                if (++bi == sch.nb) { bi = 0; ++ci; }
                 if (++s == sch.stages) { s = 0; ph ^= 1u; }
             }
             // Leave only when every copy this thread issued has landed: shared memory must not be
@@ -359,6 +579,11 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
     }
 
     // -------------------------------- consumers --------------------------------
+    chain_wait();
+    if constexpr (INK) {                                        // before anything of the main loop is live
+        float inv_rms[GM_MP] = {1.0f, 1.0f, 1.0f, 1.0f};
+        gemv_stage_start<KB>(a, smem_all, n_iter, n_lo, K, norm_red, inv_rms);
+    }
     const int g = lane >> 2, t = lane & 3, h = t >> 1, odd = t & 1;
     const int r0 = warp * 16 + g;                            // group-local columns r0 and r0 + 8
     const uint32_t sel = odd ? 0x7531u : 0x6420u;            // bytes {odd, 2+odd} of both upper words
@@ -367,8 +592,9 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
     const uint32_t aW = sb + r0 * 16 + h * 8;                // upper words 2h, 2h+1 of column r0
     const uint32_t aS = sb + OFF_SH + r0 * 8 + h * 4;        // shared word h
     const uint32_t aE = sb + OFF_SC + r0;
-    const uint32_t aB = sb + OFF_X + g * 32 + t * 8;
-    const uint32_t aC = sb + OFF_X + 256 + t * 16;
+    // activation records: inside each stage (from the staging kernel), or in this CTA's table
+    const uint32_t aB = (stage_here ? smem_u32(smem_all) : sb + OFF_X) + g * 32 + t * 8;
+    const uint32_t aC = aB - g * 32 - t * 8 + 256 + t * 16;
     float acc[GROUPS][PASSES][2];
 #pragma unroll
     for (int q = 0; q < GROUPS; ++q)
@@ -378,13 +604,15 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
     // computing, still releases its stages and still takes part in the tile hand-off, where its
     // outputs become NaN (directly, or through the status word the finishing warp reads).
     bool aborted = false;
-    chain_wait();
 
     int s = 0;
     uint32_t ph = 0;
     for (int it = 0; it < n_iter; ++it) {
+        // the (tile, warp) counter's marker, fetched long before the hand-off needs it and parked in shared memory
+        if ((it == 0 || blk == 0) && lane == 0)
+            marker_sh[warp] = *reinterpret_cast<volatile unsigned int*>(a.tile_counters + c * GM_WARPS + warp);
         if (!aborted && !mbar_wait_bounded(smem_u32(&bar_full[s]), ph, a.max_polls)) {
-            report_wait_failure(a.status, a.sticky, WAIT_FAIL_GEMV_MMA);
+            report_wait_failure(a.status, (int)a.tag, a.sticky, WAIT_FAIL_GEMV_MMA);
             aborted = true;
         }
         const int cv = min(TC, a.OUT - c * TC);
@@ -395,15 +623,16 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
             for (int j = 0; j < KB; ++j) {
                 if (j < nblk) {
                     const uint32_t so = s * STAGE_BYTES + j * SUB_BYTES;
+                    const uint32_t ro = stage_here ? (uint32_t)((it * KB + j) * GM_XREC) : so;      // this K block's record
                     uint2 bq[PASSES];
                     int corr[PASSES];
                     float cx[PASSES];
 #pragma unroll
                     for (int p = 0; p < PASSES; ++p) {
-                        const uint32_t rb = aB + so + p * GM_XREC;
+                        const uint32_t rb = aB + ro + p * GM_XREC;
                         bq[p] = lds64<0>(rb);
-                        corr[p] = (int)lds32<0>(aC + so + p * GM_XREC);
-                        cx[p] = __uint_as_float(lds32<4>(aC + so + p * GM_XREC));
+                        corr[p] = (int)lds32<0>(aC + ro + p * GM_XREC);
+                        cx[p] = __uint_as_float(lds32<4>(aC + ro + p * GM_XREC));
                     }
                     const uint32_t wb = aW + so, sbs = aS + so, eb = aE + so;
                     if (nq >= GROUPS) gemv_groups<PASSES, 0, GROUPS, true>(nq, wb, sbs, eb, sel, nshift, bq, corr, cx, acc);
@@ -417,7 +646,7 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
 
         // ---- end of this CTA's run over tile c: publish the partial, maybe finish the tile ----
         // Each warp owns 16 columns of every 128-column group of the tile, so the hand-off is
-        // per warp: store the partial, bump the (tile, warp) counter with release semantics, and
+        // per warp: store the partial, count it on the (tile, warp) counter with release semantics, and
         // the warp that arrives last adds the slots up in slot order and writes the output.
         const bool tile_end = (blk == sch.nb - 1);
         if (tile_end || it == n_iter - 1) {
@@ -464,14 +693,12 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
                         }
                     }
                     __syncwarp();
-                    int old = 0;
-                    if (lane == 0)
-                        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;"
-                                     : "=r"(old) : "l"(a.tile_counters + c * GM_WARPS + warp) : "memory");
-                    old = __shfl_sync(0xffffffffu, old, 0);
-                    if (old == nslots - 1) {
+                    unsigned int arrived = 0;
+                    if (lane == 0) arrived = gemv_count_arrival(a, a.tile_counters + c * GM_WARPS + warp, marker_sh[warp]);
+                    arrived = __shfl_sync(0xffffffffu, arrived, 0);
+                    if (arrived == (unsigned int)nslots) {
                         __threadfence();
-                        const bool poison = __ldcg(a.status) != 0;        // a wait gave up somewhere
+                        const bool poison = __ldcg(a.status) == (int)a.tag;        // a wait gave up somewhere in this call
                         const int ncol = nq * 16;
                         const int64_t sstride = (int64_t)a.rows * a.OUT;
                         const int total = a.rows * ncol;
@@ -513,6 +740,8 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
                                 if (yf) yf[y1] = sum1;
                             }
                         }
+                        // back to zero at rest: the next call (or the next replay of this launch) counts from 0 again
+                        if (lane == 0) reinterpret_cast<unsigned int*>(a.tile_counters + c * GM_WARPS + warp)[1] = 0u;
                     }
                 }
             }

@@ -353,7 +353,7 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
         for (int it = 0; it < n_iter; ++it) {
             bool stop = abort_flag != 0;
             if (!stop && !mbar_wait_bounded(smem_u32(&bar_empty[s]), ph)) {
-                report_wait_failure(a.status, a.sticky, WAIT_FAIL_GEMV_UMMA);
+                report_wait_failure(a.status, 1, a.sticky, WAIT_FAIL_GEMV_UMMA);
                 abort_flag = 1;
                 stop = true;
             }
@@ -386,7 +386,7 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
                 bool ok = mbar_wait_bounded(smem_u32(&bar_afull[buf]), (aph >> buf) & 1u);
                 if (ok && fresh) ok = mbar_wait_bounded(smem_u32(&bar_accempty), accph);
                 if (!ok) {
-                    report_wait_failure(a.status, a.sticky, WAIT_FAIL_GEMV_UMMA);
+                    report_wait_failure(a.status, 1, a.sticky, WAIT_FAIL_GEMV_UMMA);
                     abort_flag = 1;
                     break;
                 }
@@ -432,7 +432,7 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
             const int cv = min(GU_TR, a.OUT - o0);
             if (!aborted && abort_flag) aborted = true;
             if (!aborted && !mbar_wait_bounded(smem_u32(&bar_accfull), accfph)) {
-                report_wait_failure(a.status, a.sticky, WAIT_FAIL_GEMV_UMMA);
+                report_wait_failure(a.status, 1, a.sticky, WAIT_FAIL_GEMV_UMMA);
                 abort_flag = 1;
                 aborted = true;
             }
@@ -499,7 +499,7 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
                 bool ok = mbar_wait_bounded(smem_u32(&bar_full[s]), ph);
                 ok = ok && mbar_wait_bounded(smem_u32(&bar_aempty[buf]), (aeph >> bsel) & 1u);
                 if (!ok) {
-                    report_wait_failure(a.status, a.sticky, WAIT_FAIL_GEMV_UMMA);
+                    report_wait_failure(a.status, 1, a.sticky, WAIT_FAIL_GEMV_UMMA);
                     abort_flag = 1;
                     aborted = true;
                 }
@@ -531,7 +531,7 @@ gemv_umma_kernel(const GemvUmmaArgs a) {
     __syncthreads();
     if (warp >= GU_WARP_MMA && lane == 0) tc_commit(smem_u32(&bar_done));   // arrives once this issuer's MMAs have completed
     if (warp == GU_WARP_MMA) {
-        if (lane == 0 && !mbar_wait_bounded(smem_u32(&bar_done), 0)) report_wait_failure(a.status, a.sticky, WAIT_FAIL_GEMV_UMMA);
+        if (lane == 0 && !mbar_wait_bounded(smem_u32(&bar_done), 0)) report_wait_failure(a.status, 1, a.sticky, WAIT_FAIL_GEMV_UMMA);
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, tmem_cols);

@@ -88,7 +88,7 @@ int run_mma(const __nv_bfloat16* q, KvPlanes kp, KvPlanes vp, void* out, float* 
             int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t Lcap, int qrot, const QRope& qr, void* ws,
             cudaStream_t st) {
     const KvMmaPlan p = plan_mma(B, H, Hkv, Lk);
-    uint8_t* base = static_cast<uint8_t*>(ws);
+    uint8_t* base = static_cast<uint8_t*>(ws) + WS_CTL_BYTES;
     int* status = reinterpret_cast<int*>(base + p.status_off);
     KvMmaArgs a{q, kp, vp, reinterpret_cast<float*>(base), seq_lens, status, sticky_status(), (int)H, (int)Hkv, (int)Lk,
                 (int)Lcap, p.key_tile, p.S, qrot, (float)(1.4426950408889634 / sqrt(128.0)), qr.rope, qr.q_pos,
@@ -143,7 +143,7 @@ int decode_dispatch(const void* q, KvPlanes kp, KvPlanes vp, void* out, float* o
                        qr, ws, st);
     const KvPlan p = plan_generic(B, H, Lk);
     const float sm_scale = (float)(1.0 / sqrt((double)D));
-    float* partial = static_cast<float*>(ws);
+    float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + WS_CTL_BYTES);
     const __nv_bfloat16* qq = static_cast<const __nv_bfloat16*>(q);
     dim3 grid((unsigned)H, (unsigned)p.S, (unsigned)B);
     const size_t smem = ((size_t)D + KVG_CHUNK) * sizeof(float);
@@ -174,7 +174,7 @@ extern "C" size_t msaq_kv_decode_workspace(int64_t B, int64_t H, int64_t Hkv, in
         const size_t tuned = plan_mma(B, H, Hkv, Lk).total;
         if (tuned > bytes) bytes = tuned;
     }
-    return bytes;
+    return bytes + WS_CTL_BYTES;
 }
 
 extern "C" int msaq_kv_decode_attention(const void* q, const int8_t* ks, const uint8_t* ku, const uint8_t* kh,

@@ -99,7 +99,7 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
             for (int it = 0; it < n_stage; ++it) {
                 if (inject && it == a.skip_stage) break;               // the consumers' wait for this stage runs out
                 if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ph, a.max_polls)) {
-                    report_wait_failure(a.status, a.sticky, WAIT_FAIL_KV_DECODE);
+                    report_wait_failure(a.status, 1, a.sticky, WAIT_FAIL_KV_DECODE);
                     break;
                 }
                 ++issued;
@@ -198,7 +198,7 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
     uint32_t ph = 0;
     for (int it = 0; it < n_stage; ++it) {
         if (!aborted && !mbar_wait_bounded(smem_u32(&bar_full[s]), ph, a.max_polls)) {
-            report_wait_failure(a.status, a.sticky, WAIT_FAIL_KV_DECODE);
+            report_wait_failure(a.status, 1, a.sticky, WAIT_FAIL_KV_DECODE);
             aborted = true;
         }
         const uint32_t so = sb + s * KVM_STAGE_BYTES;

@@ -34,6 +34,12 @@ inline bool make_fmt(int u, int gs, Fmt* f) {
     return true;
 }
 
+// Every workspace starts with a control region that only the integer-MMA GEMV's tile hand-off uses
+// (status word, then the (tile, warp) counters, which are zero at rest): the other kernels keep their
+// scratch behind it, so that a caller (or an allocator) that hands the same memory to one call after
+// another never puts the counters under another kernel's partial sums.
+constexpr size_t WS_CTL_BYTES = 64 * 1024;
+
 // ---- host-side error plumbing (defined in capi.cu) -------------------------
 int fail(int code, const char* fmt, ...);
 int check_launch(const char* what);
@@ -42,6 +48,8 @@ int sm_count();               // SM count of the current device (cached per devi
 int require_sm100();          // MSAQ_OK or MSAQ_ERR_DEVICE
 bool option_chained_launch(); // kernels are launched with programmatic stream serialisation
 bool option_tensor_memory();  // batched GEMVs of 9 rows and more run on tcgen05 with tensor-memory accumulators
+bool option_inkernel_staging(); // GEMVs of up to four rows stage their activations inside the main kernel
+uint32_t next_call_tag();     // a process-wide 31-bit sequence number, never 0: tags a call's counters and status word
 unsigned option_wait_polls(); // poll limit of the bounded mbarrier waits
 int option_test_skip_stage(); // test hook: pipeline stage whose copy the first CTA's producer leaves out (-1: none)
 int* sticky_status();         // device address of the per-device status word on the current device (null on failure)

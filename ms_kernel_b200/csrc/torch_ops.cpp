@@ -54,8 +54,13 @@ void fmt_sizes(int64_t u, int64_t gs, int64_t* UB, int64_t* SB) {
 
 void* stream_of(const Tensor& t) { return at::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
 
+// Scratch for one call.  Always more than 1 MiB, so that torch's caching allocator serves it from its
+// large-block pool: the control region at the start of a workspace (the GEMV's tile counters, zero at
+// rest) then shares memory only with other workspaces, which leave that region alone, and not with
+// small output tensors.
 Tensor workspace(const Tensor& like, size_t bytes) {
-    return at::empty({(int64_t)(bytes ? bytes : 256)}, like.options().dtype(at::kByte));
+    const size_t floor_bytes = (1u << 20) + 512;
+    return at::empty({(int64_t)(bytes > floor_bytes ? bytes : floor_bytes)}, like.options().dtype(at::kByte));
 }
 
 // ---- GEMV ---------------------------------------------------------------

@@ -148,3 +148,67 @@ def test_gemv_rejects_bad_arguments():
     rc = L.msaq_wonly_gemv_wide(x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), None,
                                 8, 2, 4, 2, None, 0, None)
     assert rc == -3
+
+
+@pytest.mark.parametrize("M", (1, 2, 3, 4))
+@pytest.mark.parametrize("OUT,K", [(384, 512), (4096, 4096), (1040, 2048), (8192, 1024)])
+def test_gemv_in_kernel_staging_equals_staging_kernel(rng, M, OUT, K):
+    """Up to four rows, u4/gs2, small problems: the main kernel stages the activations itself (one
+    launch); the same launch behind the separate staging kernel must give the same bits."""
+    import cabi
+    from ms_kernel_b200 import _lib
+    W, X, p = _case(rng, OUT, K, 4, 2, M=M)
+    pd = cabi.planes_to_dev(p)
+    L = _lib.lib()
+    assert L.msaq_get_option(5) == 1
+    n0 = L.msaq_launch_count()
+    got, gotf = cabi.gemv("batched", cabi.bf16_dev(X), pd, M=M)
+    # where no thread block streams more than nine K blocks the staging kernel in front is gone
+    launches = L.msaq_launch_count() - n0
+    assert launches in (1, 2)
+    if (OUT, K) in ((384, 512), (4096, 4096)):
+        assert launches == 1
+    _check(got, gotf, orc.wonly_matmul(p, X))
+    assert L.msaq_set_option(5, 0) == 0
+    try:
+        got2, gotf2 = cabi.gemv("batched", cabi.bf16_dev(X), pd, M=M)
+    finally:
+        L.msaq_set_option(5, 1)
+    assert np.array_equal(gotf, gotf2) and np.array_equal(got, got2)
+
+
+def test_gemv_graph_replay_on_a_dirty_workspace(rng):
+    """The split-K hand-off must not depend on what the workspace holds before its first use, and a
+    captured launch must leave it ready for its own replay (the call's tag is baked into the graph)."""
+    import cabi
+    from ms_kernel_b200 import _lib
+    L = _lib.lib()
+    OUT, K, u, gs = 4096, 4096, 4, 2
+    W, X, p = _case(rng, OUT, K, u, gs, M=1)
+    pd = cabi.planes_to_dev(p)
+    ref = orc.wonly_matmul(p, X)[0]
+    x = cabi.bf16_dev(X[0])
+    y = torch.zeros(OUT, dtype=torch.bfloat16, device="cuda")
+    yf = torch.zeros(OUT, dtype=torch.float32, device="cuda")
+    wsb = L.msaq_wonly_gemv_workspace(1, OUT, K // 32, u, gs)
+    for fill in (0xFF, 0x00, 0x5A):
+        ws = torch.full((wsb,), fill, dtype=torch.uint8, device="cuda")
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(s):
+            with torch.cuda.graph(g, stream=s):
+                _lib.check(L.msaq_wonly_gemv_wide(x.data_ptr(), pd["scale_exp"].data_ptr(), pd["upper_cm"].data_ptr(),
+                                                  pd["shared_cm"].data_ptr(), y.data_ptr(), yf.data_ptr(), OUT, K // 32,
+                                                  u, gs, ws.data_ptr(), wsb, s.cuda_stream))
+        torch.cuda.current_stream().wait_stream(s)
+        outs = []
+        for _ in range(4):
+            yf.zero_()
+            g.replay()
+            torch.cuda.synchronize()
+            outs.append(yf.cpu().numpy().copy())
+        for o in outs:
+            assert np.array_equal(o, outs[0])
+        _check(y.float().cpu().numpy(), outs[0], ref)
+        del g
