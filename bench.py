@@ -575,8 +575,59 @@ def single_gpu_detail(dev, peak, peak_kind):
     for Lk in (4096, 16384, 32768):
         for B in (1, 8, 16, 64):
             kv_case("gqa32/8", B, 32, 8, Lk, True)
+    out["detail"]["reference_cuda"] = reference_cuda_anchor(dev, out["detail"])
     out["cpu_baseline"] = cpu_oracle_sample()
     return out
+
+
+def reference_cuda_anchor(dev, detail):
+    """The reference project's own CUDA operators (its sm_86-era kernels rebuilt for sm_100a, oracle/_ref/) timed
+    on this GPU by the same method, in a process of their own, beside this repository's numbers for the same
+    shapes: a same-box anchor, not part of the product path.  Decode is timed at full length for both (the
+    reference has one scalar Lk for the whole batch)."""
+    import torch
+    from ms_kernel_b200 import ops
+    try:
+        from oracle import ref_cuda
+        if not ref_cuda.available():
+            return {"unavailable": "oracle/_ref/ms_cuda_ref.so was not built (python oracle/build_ref.py needs the reference checkout)"}
+        gemv_cases = [{"kind": "gemv", "OUT": OUT, "K": K, "M": M, "u": 4, "gs": 2}
+                      for _, OUT, K in (("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336))
+                      for M in (1, 4, 16, 64)]
+        kv_cases = [{"kind": "kv_decode", "B": B, "Hq": Hq, "Hkv": Hkv, "Lk": Lk}
+                    for B, Hq, Hkv, Lk in ((1, 8, 8, 4096), (1, 8, 8, 16384), (1, 16, 16, 16384), (1, 32, 8, 4096),
+                                           (1, 32, 8, 16384), (8, 32, 8, 16384), (16, 32, 8, 32768))]
+        torch.cuda.empty_cache()
+        ref_us = ref_cuda.time_ops(gemv_cases + kv_cases)
+    except Exception as e:                                      # the anchor must never take the benchmark down
+        return {"unavailable": "reference CUDA run failed: %s" % str(e).splitlines()[-1][:200]}
+    rows = []
+    mine = {(r["OUT"], r["K"], r["M"]): r["us"] for r in detail["gemv"] if r["u"] == 4}
+    for c, us in zip(gemv_cases, ref_us):
+        m = mine.get((c["OUT"], c["K"], c["M"]))
+        rows.append({"op": "wonly_gemv_wide" if c["M"] == 1 else "wonly_gemv_batched", "OUT": c["OUT"], "K": c["K"],
+                     "M": c["M"], "reference_us": round(us, 2), "ours_us": m, "speedup": round(us / m, 2) if m else None})
+    g = torch.Generator(device=dev).manual_seed(3)
+    for c, us in zip(kv_cases, ref_us[len(gemv_cases):]):
+        B, Hq, Hkv, Lk, D = c["B"], c["Hq"], c["Hkv"], c["Lk"], 128
+        nbytes = B * Hkv * Lk * 2 * 4 * plane_bytes(U, GS)
+        copies = int(max(1, min(6, -(-3 * L2_BYTES // nbytes))))
+        caches = []
+        for _ in range(copies):
+            cch = ops.KVCache(B, Hkv, D, Lk, U, GS, dev, rotate=False)
+            for k0 in range(0, Lk, 4096):
+                n = min(4096, Lk - k0)
+                cch.fill(torch.randn((B, Hkv, n, D), generator=g, device=dev).to(torch.bfloat16),
+                         torch.randn((B, Hkv, n, D), generator=g, device=dev).to(torch.bfloat16), key0=k0)
+            caches.append(cch)
+        q = torch.randn((B, Hq, D), generator=g, device=dev).to(torch.bfloat16)
+        m = graph_time([(lambda cc=cc: cc.attend(q, Lk)) for cc in caches], 10, dev)
+        rows.append({"op": "kv_decode_attention_batched", "B": B, "Hq": Hq, "Hkv": Hkv, "Lk": Lk,
+                     "reference_us": round(us, 2), "ours_us": round(m, 2), "speedup": round(us / m, 2)})
+        del caches
+        torch.cuda.empty_cache()
+    return {"what": "the reference's own CUDA operators rebuilt for sm_100a (oracle/build_ref.py), same timing method, "
+                    "own process; u4/gs2; decode at full length, no append", "rows": rows}
 
 
 def cpu_oracle_sample():

@@ -311,6 +311,42 @@ int msaq_kv_decode_attention_rope(const void* q,
                                   int64_t q_pos, const int32_t* q_pos_per_seq,
                                   void* workspace, size_t workspace_bytes, void* stream);
 
+/* ------------------------------------------------- plain MXINT8 baseline -- */
+
+/*
+ * The reference's matched baseline format (ms_lib/pack.py:530-594: one int8 code per element on the block grid
+ * 2^e, e the same block exponent as MSAQ; 33 bytes per 32 values): the reference's headline metric is the time of
+ * an MSAQ kernel over the time of its MXINT8 twin at the same optimisation level (methodology.md:34-38), so the
+ * twins here run the same pipelines as the tuned MSAQ kernels with the sub-byte decode taken out.
+ *   weights   scale_exp int8 [nb,OUT]   qweight int8 [nb,32,OUT]   qweight_cm int8 [nb,OUT,32]
+ *   KV cache  scale_exp int8 [B*Hkv,nb,Lcap]   qweight int8 [B*Hkv,nb,Lcap,32]
+ * msaq_mxint8_pack_weight      device twin of pack_weight_mxint8 (ms_lib/pack.py:546-566); any plane may be NULL
+ * msaq_mxint8_gemv_wide        replaces op `msaq::mxint8_gemv_wide` (csrc/pybind.cpp:290-291, csrc/mxint8.cu:196-253)
+ * msaq_mxint8_gemv_batched_wide  replaces op `msaq::mxint8_gemv_batched_wide` (csrc/pybind.cpp:292-293); any M >= 1,
+ *                              OUT a multiple of 16
+ * msaq_mxint8_kv_append        replaces op `msaq::mxint8_kv_append` (csrc/pybind.cpp:321-322)
+ * msaq_mxint8_kv_write         replaces op `msaq::mxint8_kv_write` (csrc/pybind.cpp:320), into slots [key0, key0+L)
+ * msaq_mxint8_kv_decode_batched  replaces ops `msaq::mxint8_kv_decode[_batched]` (csrc/pybind.cpp:314-319); optional
+ *                              per-sequence lengths; head_dim 128, Hq/Hkv in {1,2,4,8}, Lcap a multiple of 16
+ *                              (workspace: msaq_kv_decode_workspace)
+ */
+int msaq_mxint8_pack_weight(const void* W, int w_is_bf16, int8_t* scale_exp, int8_t* qweight, int8_t* qweight_cm,
+                            int64_t OUT, int64_t K, void* stream);
+size_t msaq_mxint8_gemv_workspace(int64_t M, int64_t OUT, int64_t NB);
+int msaq_mxint8_gemv_wide(const void* x, const int8_t* scale_exp, const int8_t* qweight_cm, void* y, float* y_f32,
+                          int64_t OUT, int64_t NB, void* workspace, size_t workspace_bytes, void* stream);
+int msaq_mxint8_gemv_batched_wide(const void* X, const int8_t* scale_exp, const int8_t* qweight_cm, void* Y, float* Y_f32,
+                                  int64_t M, int64_t OUT, int64_t NB, void* workspace, size_t workspace_bytes,
+                                  void* stream);
+int msaq_mxint8_kv_append(const void* X, int8_t* scale_exp, int8_t* qweight, int64_t H, int64_t D, int64_t NB,
+                          int64_t pos, int64_t Lcap, void* stream);
+int msaq_mxint8_kv_write(const void* X, int8_t* scale_exp, int8_t* qweight, int64_t H, int64_t L, int64_t D, int64_t NB,
+                         int64_t key0, int64_t Lcap, void* stream);
+int msaq_mxint8_kv_decode_batched(const void* q, const int8_t* ks, const int8_t* kq, const int8_t* vs, const int8_t* vq,
+                                  void* out, float* out_f32, const int32_t* seq_lens,
+                                  int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D, int64_t NB, int64_t Lcap,
+                                  void* workspace, size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------- layer-step glue -- */
 
 /*

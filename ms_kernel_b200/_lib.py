@@ -48,6 +48,14 @@ SIGNATURES = {
                                                      _p, _sz, _p]),
     "msaq_kv_decode_attention_batched": (_int, [_p] * 7 + [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64,
                                                              _int, _int, _i64, _int, _p, _sz, _p]),
+    "msaq_mxint8_pack_weight": (_int, [_p, _int, _p, _p, _p, _i64, _i64, _p]),
+    "msaq_mxint8_gemv_workspace": (_sz, [_i64, _i64, _i64]),
+    "msaq_mxint8_gemv_wide": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _p, _sz, _p]),
+    "msaq_mxint8_gemv_batched_wide": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
+    "msaq_mxint8_kv_append": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p]),
+    "msaq_mxint8_kv_write": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p]),
+    "msaq_mxint8_kv_decode_batched": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
+                                             _p, _sz, _p]),
     "msaq_rmsnorm": (_int, [_p, _p, _i64, _i64, C.c_float, _p]),
     "msaq_silu_mul": (_int, [_p, _p, _i64, _i64, _p]),
     "msaq_add_residual": (_int, [_p, _p, _int, _p, _i64, _p]),

@@ -26,7 +26,7 @@ bool mma_eligible(int64_t OUT, int u, int gs, bool cm) { return cm && u == 4 && 
 // the tensor-memory kernel also decodes the 5+3 and 6+2 bit formats
 bool umma_eligible(int64_t OUT, int u, int gs, bool cm) { return cm && u >= 2 && u <= 4 && gs == 2 && OUT % 16 == 0; }
 
-MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB) {
+MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB, int fmt = GF_MSAQ_U4) {
     MmaPlan p;
     GemvSchedule& s = p.sch;
     const int64_t rows = M < GM_MP * GM_MAX_PASSES ? M : GM_MP * GM_MAX_PASSES;
@@ -39,17 +39,18 @@ MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB) {
     // The 1024-column tile (16 accumulators per thread, half as many barrier hand-offs per byte) pays for a
     // single row: 57344x8192 77 -> 68 us; with four rows it measured slower than 512 columns (41.7 against 32.7 us
     // on 28672x4096).
-    for (int tc = M == 1 ? GM_MAX_TC : GM_MAX_TC / 2; tc >= GM_GROUP; tc >>= 1) {
+    // (the MXINT8 twin is built for 512- and 256-column tiles, one K block per stage)
+    for (int tc = (M == 1 && fmt == GF_MSAQ_U4) ? GM_MAX_TC : GM_MAX_TC / 2; tc >= (fmt == GF_MXINT8 ? 256 : GM_GROUP); tc >>= 1) {
         s.tc = tc;
         s.col_tiles = (int)((OUT + tc - 1) / tc);
         const long long units = s.units();
         s.grid = (int)(units < slots ? units : slots);
-        if (tc == GM_GROUP || (s.grid + s.col_tiles - 1) / s.col_tiles <= 32) break;
+        if (tc == (fmt == GF_MXINT8 ? 256 : GM_GROUP) || (s.grid + s.col_tiles - 1) / s.col_tiles <= 32) break;
     }
     // Launches of one or two passes (up to eight rows) on 512- or 256-column tiles: two or four K blocks per ring stage,
     // for the same cut in hand-offs per byte the wider tile gives (8192x28672: 44.5 -> 41.3 us at one row,
     // 54.9 -> 50.8 us at four).
-    if (passes <= 2 && (s.tc == 512 || s.tc == 256) && NB >= 4) {
+    if (fmt == GF_MSAQ_U4 && passes <= 2 && (s.tc == 512 || s.tc == 256) && NB >= 4) {
         p.kb = s.tc == 512 ? 2 : 4;                    // 25.6 KB of packed bytes per stage either way
         s.nb = (int)((NB + p.kb - 1) / p.kb);
         const long long u2 = s.units();
@@ -58,7 +59,7 @@ MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB) {
     const long long units = s.units();
     s.max_slots = (int)(((long long)s.nb * s.grid + units - 1) / units) + 1;
     const int per_sm = (s.grid + sm_count() - 1) / sm_count();
-    const int stage = p.kb * gm_stage_bytes(s.tc, passes);
+    const int stage = p.kb * gm_stage_bytes(s.tc, passes, fmt);
     int stages = (200 * 1024 / per_sm) / stage;
     if (stages > GM_MAX_STAGES) stages = GM_MAX_STAGES;
     if (stages < 2) stages = 2;
@@ -71,21 +72,28 @@ MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB) {
     return p;
 }
 
-template <int PASSES, int TC, int KB, bool INK>
+template <int PASSES, int TC, int KB, bool INK, int FMT = GF_MSAQ_U4>
 int launch_mma_ink(const GemvMmaArgs& a, cudaStream_t st) {
     static int configured[64] = {};                      // largest dynamic smem size set per device
-    const int smem = a.sch.stages * KB * gm_stage_bytes(TC, PASSES) + a.table_bytes;
+    const int smem = a.sch.stages * KB * gm_stage_bytes(TC, PASSES, FMT) + a.table_bytes;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && configured[dev] < smem) {
-        if (cudaFuncSetAttribute(gemv_u4gs2_mma_kernel<PASSES, TC, KB, INK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(gemv_u4gs2_mma_kernel<PASSES, TC, KB, INK, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  smem) != cudaSuccess)
             return fail(MSAQ_ERR_CUDA, "cannot reserve %d bytes of shared memory", smem);
         configured[dev] = smem;
     }
-    launch_chained(gemv_u4gs2_mma_kernel<PASSES, TC, KB, INK>, dim3(a.sch.grid), dim3(GM_THREADS), smem, st, a);
+    launch_chained(gemv_u4gs2_mma_kernel<PASSES, TC, KB, INK, FMT>, dim3(a.sch.grid), dim3(GM_THREADS), smem, st, a);
     count_launch();
-    return check_launch("gemv_u4gs2_mma");
+    return check_launch(FMT == GF_MXINT8 ? "gemv_mxint8_mma" : "gemv_u4gs2_mma");
+}
+
+// the MXINT8 twin: 512- or 256-column tiles, one K block per stage, records from the staging kernel
+template <int PASSES>
+int launch_mma_mx(const GemvMmaArgs& a, cudaStream_t st) {
+    return a.sch.tc == 512 ? launch_mma_ink<PASSES, 512, 1, false, GF_MXINT8>(a, st)
+                           : launch_mma_ink<PASSES, 256, 1, false, GF_MXINT8>(a, st);
 }
 
 template <int PASSES, int TC, int KB = 1>
@@ -207,8 +215,8 @@ int launch_xprep(const XprepArgs& xa, int mode, unsigned grid, cudaStream_t st) 
 }
 
 int run_mma(const __nv_bfloat16* X, const Prologue& pro, const int8_t* se, const uint8_t* up, const uint8_t* sh,
-            void* Y, float* Yf, int64_t M, int64_t OUT, int64_t NB, void* ws, cudaStream_t st) {
-    const MmaPlan p = plan_mma(M, OUT, NB);
+            void* Y, float* Yf, int64_t M, int64_t OUT, int64_t NB, void* ws, cudaStream_t st, int fmt = GF_MSAQ_U4) {
+    const MmaPlan p = plan_mma(M, OUT, NB, fmt);
     uint8_t* base = static_cast<uint8_t*>(ws);
     int* status = reinterpret_cast<int*>(base);
     unsigned long long* counters = reinterpret_cast<unsigned long long*>(base + 256);
@@ -231,6 +239,7 @@ int run_mma(const __nv_bfloat16* X, const Prologue& pro, const int8_t* se, const
         xa.ldx = (int)ldx;
         xa.r_is_f32 = pro.r_is_f32;
         xa.eps = pro.eps;
+        xa.natural = fmt == GF_MXINT8 ? 1 : 0;
         // Up to four rows, no prologue, and no CTA streams more than nine K blocks (the small problems, where fixed
         // costs are most of the time): the main kernel stages the activations itself -- each of its nine warps writes
         // one record into a table in shared memory while the first copies are in flight -- and no launch runs in
@@ -240,11 +249,12 @@ int run_mma(const __nv_bfloat16* X, const Prologue& pro, const int8_t* se, const
         GemvSchedule sch = p.sch;
         const long long max_iter = (sch.units() + sch.grid - 1) / sch.grid;
         const long long table = max_iter * p.kb * GM_XREC;
-        const bool in_kernel = passes == 1 && pro.mode == XP_PLAIN && option_inkernel_staging() && table <= GM_MAX_TABLE;
+        const bool in_kernel = fmt == GF_MSAQ_U4 && passes == 1 && pro.mode == XP_PLAIN && option_inkernel_staging() &&
+                               table <= GM_MAX_TABLE;
         const uint32_t tag = next_call_tag();
         if (in_kernel) {
             const int per_sm = (sch.grid + sm_count() - 1) / sm_count();
-            int stages = (200 * 1024 / per_sm - (int)table) / (p.kb * gm_stage_bytes(sch.tc, passes));
+            int stages = (200 * 1024 / per_sm - (int)table) / (p.kb * gm_stage_bytes(sch.tc, passes, fmt));
             sch.stages = stages > GM_MAX_STAGES ? GM_MAX_STAGES : stages < 2 ? 2 : stages;
         } else if (int rc = launch_xprep(xa, pro.mode, (unsigned)((warps * 32 + 127) / 128), st)) {
             return rc;
@@ -252,9 +262,19 @@ int run_mma(const __nv_bfloat16* X, const Prologue& pro, const int8_t* se, const
         GemvMmaArgs a{se, up, sh, xprep, partial, counters, status, sticky_status(), static_cast<__nv_bfloat16*>(Y), Yf,
                       (int)m0, rows, (int)OUT, (int)NB, sch, option_wait_polls(), option_test_skip_stage(),
                       in_kernel ? pro.mode : -1, xa.X, xa.R, xa.h_out, (int)ldx, pro.r_is_f32, pro.eps, tag,
-                      in_kernel ? (int)table : 0};
+                      in_kernel ? (int)table : 0, 0};
         // the ring depth was planned for the first tile's pass count; a last, smaller tile may go deeper but need not
         int rc;
+        if (fmt == GF_MXINT8) {
+            switch (passes) {
+                case 1: rc = launch_mma_mx<1>(a, st); break;
+                case 2: rc = launch_mma_mx<2>(a, st); break;
+                case 3: rc = launch_mma_mx<3>(a, st); break;
+                default: rc = launch_mma_mx<4>(a, st); break;
+            }
+            if (rc) return rc;
+            continue;
+        }
         switch (passes) {
             case 1: rc = launch_mma_tc<1>(a, p.kb, st); break;
             case 2: rc = launch_mma_tc<2>(a, p.kb, st); break;
@@ -448,4 +468,33 @@ extern "C" int msaq_wonly_gemv_wide_static(const void* x, const int8_t* scale_ex
     if (int rc = static_scratch(&scratch)) return rc;
     return msaq_wonly_gemv_wide(x, scale_exp, upper_cm, shared_cm, y, y_f32, OUT, NB, u, gs, scratch,
                                 MSAQ_STATIC_SCRATCH_BYTES, stream);
+}
+
+// ---- plain MXINT8 GEMV (the reference's matched baseline, csrc/mxint8.cu:196-253) ----------------------
+extern "C" size_t msaq_mxint8_gemv_workspace(int64_t M, int64_t OUT, int64_t NB) {
+    if (M <= 0 || OUT <= 0 || NB <= 0) return 0;
+    return plan_mma(M, OUT, NB, GF_MXINT8).total;
+}
+
+extern "C" int msaq_mxint8_gemv_batched_wide(const void* X, const int8_t* scale_exp, const int8_t* qweight_cm, void* Y,
+                                             float* Y_f32, int64_t M, int64_t OUT, int64_t NB, void* workspace,
+                                             size_t workspace_bytes, void* stream) {
+    if (!X || !scale_exp || !qweight_cm || !Y) return fail(MSAQ_ERR_ARG, "null pointer");
+    if (M <= 0 || OUT <= 0 || NB <= 0) return fail(MSAQ_ERR_ARG, "M, OUT and NB must be positive");
+    if (M > INT32_MAX || OUT > INT32_MAX || NB * BLOCK > INT32_MAX) return fail(MSAQ_ERR_ARG, "size exceeds 2^31");
+    if (OUT % 16) return fail(MSAQ_ERR_UNSUPPORTED, "the MXINT8 GEMV needs OUT to be a multiple of 16");
+    if ((reinterpret_cast<uintptr_t>(scale_exp) | reinterpret_cast<uintptr_t>(qweight_cm) | reinterpret_cast<uintptr_t>(workspace)) & 15)
+        return fail(MSAQ_ERR_ARG, "planes and workspace must be 16-byte aligned");
+    if (int rc = require_sm100()) return rc;
+    const size_t need = msaq_mxint8_gemv_workspace(M, OUT, NB);
+    if (!workspace || workspace_bytes < need)
+        return fail(MSAQ_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", need, workspace ? workspace_bytes : (size_t)0);
+    return run_mma(static_cast<const __nv_bfloat16*>(X), Prologue{XP_PLAIN, nullptr, 0, nullptr, 0.0f}, scale_exp,
+                   reinterpret_cast<const uint8_t*>(qweight_cm), nullptr, Y, Y_f32, M, OUT, NB, workspace,
+                   static_cast<cudaStream_t>(stream), GF_MXINT8);
+}
+
+extern "C" int msaq_mxint8_gemv_wide(const void* x, const int8_t* scale_exp, const int8_t* qweight_cm, void* y, float* y_f32,
+                                     int64_t OUT, int64_t NB, void* workspace, size_t workspace_bytes, void* stream) {
+    return msaq_mxint8_gemv_batched_wide(x, scale_exp, qweight_cm, y, y_f32, 1, OUT, NB, workspace, workspace_bytes, stream);
 }

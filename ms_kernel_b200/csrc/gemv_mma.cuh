@@ -42,7 +42,14 @@ constexpr int GM_MAX_TABLE = (GM_WARPS + 1) * GM_XREC;   // largest in-kernel re
 
 // Stage layout for a tile of TC columns x one K block:
 //   upper [TC][16] | shared [TC][8] | scale [TC] | activations [passes][GM_XREC]
-__host__ __device__ inline int gm_stage_bytes(int tc, int passes) { return tc * 25 + passes * GM_XREC; }
+// The weight format the kernel streams: the MSAQ-signed u4/gs2 planes (25 bytes per column and K block: 16 of
+// upper codes, 8 of shared codes, the scale), or plain MXINT8 (33 bytes: 32 int8 codes and the scale), the
+// reference's matched baseline (csrc/mxint8.cu:196-253), whose codes are MMA operands as they are.
+constexpr int GF_MSAQ_U4 = 0, GF_MXINT8 = 1;
+__host__ __device__ constexpr int gm_col_bytes(int fmt) { return fmt == GF_MXINT8 ? 33 : 25; }
+__host__ __device__ inline int gm_stage_bytes(int tc, int passes, int fmt = GF_MSAQ_U4) {
+    return tc * gm_col_bytes(fmt) + passes * GM_XREC;
+}
 
 // Work decomposition shared by host and device.  A unit is (column tile c,
 // K block b); unit index n = c * NB + b.  CTA i of `grid` owns the units
@@ -82,6 +89,7 @@ struct XprepArgs {
     uint8_t* xprep;
     int M, NB, passes, ldx, r_is_f32;
     float eps;
+    int natural;             // record in natural element order (MXINT8 weights) instead of the nibble-matched order
 };
 
 template <int MODE>
@@ -196,7 +204,10 @@ gemv_xprep_kernel(const XprepArgs a) {
     xi = min(xi, 32639);
     const int lo = (int)(int8_t)(xi & 0xFF), hi = (xi - lo) >> 8;
     uint8_t* rec = a.xprep + ((int64_t)blk * a.passes + pass) * GM_XREC;
-    const int e = lane, t = 2 * (e >> 4) + ((e >> 1) & 1), j = (e & 1) * 4 + ((e & 15) >> 2);
+    const int e = lane;
+    // natural order: thread-slot t holds the elements 4t..4t+3 (bytes 0..3) and 16+4t..16+4t+3 (bytes 4..7)
+    const int t = a.natural ? (e & 15) >> 2 : 2 * (e >> 4) + ((e >> 1) & 1);
+    const int j = a.natural ? (e >> 4) * 4 + (e & 3) : (e & 1) * 4 + ((e & 15) >> 2);
     rec[(2 * mm) * 32 + t * 8 + j] = (uint8_t)hi;
     rec[(2 * mm + 1) * 32 + t * 8 + j] = (uint8_t)lo;
     int sh = hi, sl = lo;
@@ -244,6 +255,7 @@ struct GemvMmaArgs {
     float eps;
     uint32_t tag;            // identifies this call in the counters and the status word; 31 bits, never 0
     int table_bytes;         // shared memory in front of the ring that holds the in-kernel record table
+    int natural;             // in-kernel records in natural element order (see XprepArgs)
 };
 
 // Sums of squares of the launch's rows (of X, or of bf16(X + R) for XP_ADD_NORM) by all threads of the
@@ -340,7 +352,9 @@ __device__ __forceinline__ void gemv_stage_block(const GemvMmaArgs& a, uint8_t* 
         int xi = __float2int_rn(x * __int_as_float((14 - E + 127) << 23));
         xi = min(xi, 32639);
         const int lo = (int)(int8_t)(xi & 0xFF), hi = (xi - lo) >> 8;
-        const int e = lane, t = 2 * (e >> 4) + ((e >> 1) & 1), j = (e & 1) * 4 + ((e & 15) >> 2);
+        const int e = lane;
+        const int t = a.natural ? (e & 15) >> 2 : 2 * (e >> 4) + ((e >> 1) & 1);
+        const int j = a.natural ? (e >> 4) * 4 + (e & 3) : (e & 1) * 4 + ((e & 15) >> 2);
         rec[(2 * m) * 32 + t * 8 + j] = (uint8_t)hi;
         rec[(2 * m + 1) * 32 + t * 8 + j] = (uint8_t)lo;
         const int sx = __reduce_add_sync(0xffffffffu, xi);          // = 256 * sum(hi) + sum(lo)
@@ -354,6 +368,32 @@ __device__ __forceinline__ void gemv_stage_block(const GemvMmaArgs& a, uint8_t* 
 
 // One 16-column x 32-element step of a warp: decode both columns' codes into the
 // int8 operand, one integer MMA per activation pass, scale and accumulate.
+// Plain MXINT8: the int8 codes are the A operand as stored -- columns r0 and r0 + 8, elements 4t..4t+3 and
+// 16+4t..16+4t+3 -- and there is no code offset to take out.
+template <int PASSES, int Q>
+__device__ __forceinline__ void gemv_group_step_mx(uint32_t wbase, uint32_t ebase, const uint2 (&bq)[PASSES],
+                                                   const float (&cx)[PASSES], float (&acc)[PASSES][2]) {
+    uint32_t A[4];
+    A[0] = lds32<Q * 4096>(wbase);
+    A[1] = lds32<Q * 4096 + 256>(wbase);
+    A[2] = lds32<Q * 4096 + 16>(wbase);
+    A[3] = lds32<Q * 4096 + 256 + 16>(wbase);
+    const int e0 = lds_s8<Q * 128>(ebase);
+    const int e1 = lds_s8<Q * 128 + 8>(ebase);
+    const float sw0 = __int_as_float(e0 * (1 << 23) + (127 << 23));
+    const float sw1 = __int_as_float(e1 * (1 << 23) + (127 << 23));
+#pragma unroll
+    for (int p = 0; p < PASSES; ++p) {
+        const uint32_t B[2] = {bq[p].x, bq[p].y};
+        int Dm[4];
+        mma_s8_16832_z(Dm, A, B);
+        const float f0 = (float)(Dm[0] * 256 + Dm[1]) * cx[p];
+        const float f1 = (float)(Dm[2] * 256 + Dm[3]) * cx[p];
+        acc[p][0] = fmaf(f0, sw0, acc[p][0]);
+        acc[p][1] = fmaf(f1, sw1, acc[p][1]);
+    }
+}
+
 template <int PASSES, int Q>
 __device__ __forceinline__ void gemv_group_step(uint32_t wbase, uint32_t sbase, uint32_t ebase, uint32_t sel,
                                                 uint32_t nshift, const uint2 (&bq)[PASSES], const int (&corr)[PASSES],
@@ -391,13 +431,16 @@ __device__ __forceinline__ void gemv_group_step(uint32_t wbase, uint32_t sbase, 
 
 // The column groups Q, Q+1, ... of a tile, each with compile-time shared-memory offsets; ALL skips
 // the per-group test when the warp has columns in every group.
-template <int PASSES, int Q, int GROUPS, bool ALL>
+template <int PASSES, int Q, int GROUPS, bool ALL, int FMT = GF_MSAQ_U4>
 __device__ __forceinline__ void gemv_groups(int nq, uint32_t wb, uint32_t sbs, uint32_t eb, uint32_t sel, uint32_t nshift,
                                             const uint2 (&bq)[PASSES], const int (&corr)[PASSES], const float (&cx)[PASSES],
                                             float (&acc)[GROUPS][PASSES][2]) {
     if constexpr (Q < GROUPS) {
-        if (ALL || Q < nq) gemv_group_step<PASSES, Q>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[Q]);
-        gemv_groups<PASSES, Q + 1, GROUPS, ALL>(nq, wb, sbs, eb, sel, nshift, bq, corr, cx, acc);
+        if (ALL || Q < nq) {
+            if constexpr (FMT == GF_MXINT8) gemv_group_step_mx<PASSES, Q>(wb, eb, bq, cx, acc[Q]);
+            else gemv_group_step<PASSES, Q>(wb, sbs, eb, sel, nshift, bq, corr, cx, acc[Q]);
+        }
+        gemv_groups<PASSES, Q + 1, GROUPS, ALL, FMT>(nq, wb, sbs, eb, sel, nshift, bq, corr, cx, acc);
     }
 }
 
@@ -479,7 +522,7 @@ __device__ __forceinline__ void gemv_stage_start(const GemvMmaArgs& a, uint8_t* 
 // KB = K blocks per ring stage (per unit).  Two halve the barrier hand-offs per byte where the tile
 // cannot get wider (few column tiles, many K blocks).
 // INK = the activation records come from this CTA's own table (in-kernel staging, PASSES == 1 only).
-template <int PASSES, int TC, int KB, bool INK = false>
+template <int PASSES, int TC, int KB, bool INK = false, int FMT = GF_MSAQ_U4>
 __global__ void __launch_bounds__(GM_THREADS, GM_CTAS_PER_SM)
 gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
     static_assert(!INK || PASSES == 1, "in-kernel staging serves launches of up to four rows");
@@ -490,8 +533,9 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
     __shared__ unsigned int marker_sh[GM_WARPS];               // each warp's (tile, warp) counter marker, fetched early
 
     constexpr int GROUPS = TC / GM_GROUP;
-    constexpr int OFF_SH = TC * 16, OFF_SC = TC * 24, OFF_X = TC * 25;
-    constexpr int SUB_BYTES = TC * 25 + PASSES * GM_XREC;      // one K block of the tile with its activation record
+    constexpr int CB = gm_col_bytes(FMT);                      // bytes per (column, K block)
+    constexpr int OFF_SH = TC * 16, OFF_SC = TC * (CB - 1), OFF_X = TC * CB;
+    constexpr int SUB_BYTES = TC * CB + PASSES * GM_XREC;      // one K block of the tile with its activation record
     constexpr int STAGE_BYTES = KB * SUB_BYTES;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -526,14 +570,18 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
             const int o0 = uc * TC, cv = min(TC, a.OUT - o0);
             const uint32_t bar = smem_u32(&bar_full[us]);
             const int b0 = ub * KB, nblk = min(KB, a.NB - b0);          // `ub` counts units within the tile
-            mbar_expect_tx(bar, (uint32_t)(nblk * (cv * 25 + (stage_here ? 0 : PASSES * GM_XREC))));
+            mbar_expect_tx(bar, (uint32_t)(nblk * (cv * CB + (stage_here ? 0 : PASSES * GM_XREC))));
 #pragma unroll
             for (int j = 0; j < KB; ++j) {
                 if (j < nblk) {
                     const uint32_t base = smem_u32(smem) + us * STAGE_BYTES + j * SUB_BYTES;
                     const int64_t col = (int64_t)(b0 + j) * a.OUT + o0;
-                    bulk_g2s(base, a.upper_cm + col * 16, (uint32_t)cv * 16, bar);
-                    bulk_g2s(base + OFF_SH, a.shared_cm + col * 8, (uint32_t)cv * 8, bar);
+                    if constexpr (FMT == GF_MXINT8) {
+                        bulk_g2s(base, a.upper_cm + col * 32, (uint32_t)cv * 32, bar);      // the int8 code plane
+                    } else {
+                        bulk_g2s(base, a.upper_cm + col * 16, (uint32_t)cv * 16, bar);
+                        bulk_g2s(base + OFF_SH, a.shared_cm + col * 8, (uint32_t)cv * 8, bar);
+                    }
                     bulk_g2s(base + OFF_SC, a.scale_exp + col, (uint32_t)cv, bar);
                     if (!stage_here)
                         bulk_g2s(base + OFF_X, a.xprep + (int64_t)(b0 + j) * PASSES * GM_XREC, (uint32_t)(PASSES * GM_XREC), bar);
@@ -589,7 +637,8 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
     const uint32_t sel = odd ? 0x7531u : 0x6420u;            // bytes {odd, 2+odd} of both upper words
     const uint32_t nshift = odd * 4;
     const uint32_t sb = smem_u32(smem);
-    const uint32_t aW = sb + r0 * 16 + h * 8;                // upper words 2h, 2h+1 of column r0
+    const uint32_t aW = FMT == GF_MXINT8 ? sb + r0 * 32 + t * 4      // codes 4t..4t+3 of column r0
+                                         : sb + r0 * 16 + h * 8;     // upper words 2h, 2h+1 of column r0
     const uint32_t aS = sb + OFF_SH + r0 * 8 + h * 4;        // shared word h
     const uint32_t aE = sb + OFF_SC + r0;
     // activation records: inside each stage (from the staging kernel), or in this CTA's table
@@ -635,8 +684,8 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
                         cx[p] = __uint_as_float(lds32<4>(aC + ro + p * GM_XREC));
                     }
                     const uint32_t wb = aW + so, sbs = aS + so, eb = aE + so;
-                    if (nq >= GROUPS) gemv_groups<PASSES, 0, GROUPS, true>(nq, wb, sbs, eb, sel, nshift, bq, corr, cx, acc);
-                    else gemv_groups<PASSES, 0, GROUPS, false>(nq, wb, sbs, eb, sel, nshift, bq, corr, cx, acc);
+                    if (nq >= GROUPS) gemv_groups<PASSES, 0, GROUPS, true, FMT>(nq, wb, sbs, eb, sel, nshift, bq, corr, cx, acc);
+                    else gemv_groups<PASSES, 0, GROUPS, false, FMT>(nq, wb, sbs, eb, sel, nshift, bq, corr, cx, acc);
                 }
             }
         }

@@ -62,20 +62,21 @@ KvMmaPlan plan_mma(int64_t B, int64_t H, int64_t Hkv, int64_t Lk) {
     return p;
 }
 
-template <int G>
+template <int G, int FMT = KVF_MSAQ_U4>
 int launch_kv_mma(const KvMmaArgs& a, int S, int Hkv, int B, cudaStream_t st) {
     static bool configured[64] = {};
+    constexpr int smem = kvm_smem_bytes(FMT);
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(kv_decode_u4gs2_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, KVM_SMEM) !=
+        if (cudaFuncSetAttribute(kv_decode_u4gs2_kernel<G, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
             cudaSuccess)
-            return fail(MSAQ_ERR_CUDA, "cannot reserve %d bytes of shared memory", KVM_SMEM);
+            return fail(MSAQ_ERR_CUDA, "cannot reserve %d bytes of shared memory", smem);
         configured[dev] = true;
     }
-    launch_chained(kv_decode_u4gs2_kernel<G>, dim3((unsigned)S, (unsigned)Hkv, (unsigned)B), dim3(KVM_THREADS), KVM_SMEM, st, a);
+    launch_chained(kv_decode_u4gs2_kernel<G, FMT>, dim3((unsigned)S, (unsigned)Hkv, (unsigned)B), dim3(KVM_THREADS), smem, st, a);
     count_launch();
-    return check_launch("kv_decode_u4gs2");
+    return check_launch(FMT == KVF_MXINT8 ? "kv_decode_mxint8" : "kv_decode_u4gs2");
 }
 
 struct QRope {
@@ -86,7 +87,7 @@ struct QRope {
 
 int run_mma(const __nv_bfloat16* q, KvPlanes kp, KvPlanes vp, void* out, float* out_f32, const int32_t* seq_lens,
             int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t Lcap, int qrot, const QRope& qr, void* ws,
-            cudaStream_t st) {
+            cudaStream_t st, int fmt = KVF_MSAQ_U4) {
     const KvMmaPlan p = plan_mma(B, H, Hkv, Lk);
     uint8_t* base = static_cast<uint8_t*>(ws) + WS_CTL_BYTES;
     int* status = reinterpret_cast<int*>(base + p.status_off);
@@ -94,6 +95,14 @@ int run_mma(const __nv_bfloat16* q, KvPlanes kp, KvPlanes vp, void* out, float* 
                 (int)Lcap, p.key_tile, p.S, qrot, (float)(1.4426950408889634 / sqrt(128.0)), qr.rope, qr.q_pos,
                 qr.q_pos_per_seq, KVM_SPLIT_TAU, option_wait_polls(), option_test_skip_stage()};
     int rc;
+    if (fmt == KVF_MXINT8) {
+        switch (H / Hkv) {
+            case 1: rc = launch_kv_mma<1, KVF_MXINT8>(a, p.S, (int)Hkv, (int)B, st); break;
+            case 2: rc = launch_kv_mma<2, KVF_MXINT8>(a, p.S, (int)Hkv, (int)B, st); break;
+            case 4: rc = launch_kv_mma<4, KVF_MXINT8>(a, p.S, (int)Hkv, (int)B, st); break;
+            default: rc = launch_kv_mma<8, KVF_MXINT8>(a, p.S, (int)Hkv, (int)B, st); break;
+        }
+    } else
     switch (H / Hkv) {
         case 1: rc = launch_kv_mma<1>(a, p.S, (int)Hkv, (int)B, st); break;
         case 2: rc = launch_kv_mma<2>(a, p.S, (int)Hkv, (int)B, st); break;
@@ -206,4 +215,30 @@ extern "C" int msaq_kv_decode_attention_rope(const void* q, const int8_t* ks, co
     return decode_dispatch(q, KvPlanes{ks, ku, kh}, KvPlanes{vs, vu, vh}, out, out_f32, seq_lens, B, H, Hkv, Lk, D, NB,
                            u, gs, Lcap, qrot, QRope{Rope{rope_cos, rope_sin, rope_rows}, q_pos, q_pos_per_seq}, workspace,
                            workspace_bytes, stream);
+}
+
+// ---- plain MXINT8 caches (the reference's matched baseline, csrc/mxint8.cu:750-912) ---------------------
+extern "C" int msaq_mxint8_kv_decode_batched(const void* q, const int8_t* ks, const int8_t* kq, const int8_t* vs,
+                                             const int8_t* vq, void* out, float* out_f32, const int32_t* seq_lens,
+                                             int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D, int64_t NB,
+                                             int64_t Lcap, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!q || !ks || !kq || !vs || !vq || !out) return fail(MSAQ_ERR_ARG, "null pointer");
+    if (B <= 0 || H <= 0 || Hkv <= 0 || Lk <= 0) return fail(MSAQ_ERR_ARG, "B, H, Hkv and Lk must be positive");
+    if (H % Hkv) return fail(MSAQ_ERR_ARG, "H (%lld) must be a multiple of Hkv (%lld)", (long long)H, (long long)Hkv);
+    if (Lcap < 0) Lcap = Lk;
+    if (Lcap < Lk) return fail(MSAQ_ERR_ARG, "Lcap (%lld) is smaller than Lk (%lld)", (long long)Lcap, (long long)Lk);
+    if (Lk > INT32_MAX || Lcap > INT32_MAX || B > 65535) return fail(MSAQ_ERR_ARG, "size exceeds the supported range");
+    // the baseline twin exists for the configuration the tuned MSAQ kernel serves, so that the two compare like for like
+    if (!mma_eligible(H, Hkv, D, 4, 2, Lcap) || NB * BLOCK != D)
+        return fail(MSAQ_ERR_UNSUPPORTED, "the MXINT8 decode serves head_dim 128, Hq/Hkv in {1,2,4,8} and capacities that are multiples of 16");
+    if ((reinterpret_cast<uintptr_t>(ks) | reinterpret_cast<uintptr_t>(kq) | reinterpret_cast<uintptr_t>(vs) |
+         reinterpret_cast<uintptr_t>(vq)) & 15)
+        return fail(MSAQ_ERR_ARG, "cache planes must be 16-byte aligned");
+    if (int rc = require_sm100()) return rc;
+    const size_t need = msaq_kv_decode_workspace(B, H, Hkv, Lk, D);
+    if (!workspace || workspace_bytes < need)
+        return fail(MSAQ_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", need, workspace ? workspace_bytes : (size_t)0);
+    return run_mma(static_cast<const __nv_bfloat16*>(q), KvPlanes{ks, reinterpret_cast<const uint8_t*>(kq), nullptr},
+                   KvPlanes{vs, reinterpret_cast<const uint8_t*>(vq), nullptr}, out, out_f32, seq_lens, B, H, Hkv, Lk, Lcap, 0,
+                   QRope{}, workspace, static_cast<cudaStream_t>(stream), KVF_MXINT8);
 }

@@ -36,6 +36,17 @@ constexpr int KVM_UP = KVM_TK * 16, KVM_SH = KVM_TK * 8, KVM_SC = KVM_TK;
 constexpr int KVM_K_UP = 0, KVM_K_SH = 4 * KVM_UP, KVM_K_SC = KVM_K_SH + 4 * KVM_SH;
 constexpr int KVM_V_UP = KVM_K_SC + 4 * KVM_SC, KVM_V_SH = KVM_V_UP + 4 * KVM_UP, KVM_V_SC = KVM_V_SH + 4 * KVM_SH;
 constexpr int KVM_STAGE_BYTES = KVM_V_SC + 4 * KVM_SC;            // 25600
+// The same kernel reads plain MXINT8 caches (the reference's matched baseline, csrc/mxint8.cu:750-912): 32 int8
+// codes and a scale per (key, block).  The codes are MMA operands as stored, so the stage is K codes | K scales |
+// V codes | V scales and the nibble work drops out.
+constexpr int KVF_MSAQ_U4 = 0, KVF_MXINT8 = 1;
+constexpr int KVX_Q = KVM_TK * 32;                                // code bytes per block of a 128-key stage
+constexpr int KVX_K_Q = 0, KVX_K_SC = 4 * KVX_Q, KVX_V_Q = KVX_K_SC + 4 * KVM_SC, KVX_V_SC = KVX_V_Q + 4 * KVX_Q;
+constexpr int KVX_STAGE_BYTES = KVX_V_SC + 4 * KVM_SC;            // 33792
+__host__ __device__ constexpr int kvm_stage_bytes(int fmt) { return fmt == KVF_MXINT8 ? KVX_STAGE_BYTES : KVM_STAGE_BYTES; }
+__host__ __device__ constexpr int kvm_smem_bytes(int fmt) {      // ring + query records + probability exchange + scale table
+    return KVM_STAGES * kvm_stage_bytes(fmt) + 4 * 2 * 320 + KVM_WARPS * 8 * 40 * 4 + KVM_WARPS * 4 * 32 * 4;
+}
 constexpr int KVM_QREC = 320;               // staged query record per (block, pass); layout as in gemv_mma.cuh
 constexpr float KVM_SPLIT_TAU = 0.001953125f;  // 2^-9: boundary between the big and the small keys of a split chunk
 constexpr int KVM_PSTRIDE = 40;             // floats per head row of the probability exchange buffer
@@ -61,11 +72,16 @@ struct KvMmaArgs {
     int skip_stage;             // test hook: the producer of CTA (0,0,0) stops before this stage (-1: never)
 };
 
-template <int G>
+template <int G, int FMT = KVF_MSAQ_U4>
 __global__ void __launch_bounds__(KVM_THREADS, KVM_CTAS_PER_SM)
 kv_decode_u4gs2_kernel(const KvMmaArgs a) {
     chain_wait();
     constexpr int PASSES = (G + 3) / 4;
+    constexpr bool MX = FMT == KVF_MXINT8;
+    constexpr int KVM_STAGE_BYTES = kvm_stage_bytes(FMT);        // shadows the MSAQ constants below
+    constexpr int KVM_OFF_Q = KVM_STAGES * KVM_STAGE_BYTES;
+    constexpr int KVM_OFF_P = KVM_OFF_Q + 4 * 2 * KVM_QREC;
+    constexpr int KVM_OFF_R = KVM_OFF_P + KVM_WARPS * 8 * KVM_PSTRIDE * 4;
     extern __shared__ __align__(128) uint8_t kvm_smem[];
     uint8_t* const smem = kvm_smem;
     __shared__ __align__(8) uint64_t bar_full[KVM_STAGES];
@@ -107,10 +123,17 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
                 const int nk = min(KVM_TK, (j1 - j + 15) & ~15);       // whole 16-key groups (capacity is a multiple of 16)
                 const uint32_t bar = smem_u32(&bar_full[s]);
                 const uint32_t base = sb + s * KVM_STAGE_BYTES;
-                mbar_expect_tx(bar, (uint32_t)(2 * 4 * nk * 25));
+                mbar_expect_tx(bar, (uint32_t)(2 * 4 * nk * (MX ? 33 : 25)));
 #pragma unroll
                 for (int blk = 0; blk < 4; ++blk) {
                     const int64_t row = (head_row + blk) * a.Lcap + j;
+                    if constexpr (MX) {
+                        bulk_g2s(base + KVX_K_Q + blk * KVX_Q, a.k.u + row * 32, (uint32_t)nk * 32, bar);
+                        bulk_g2s(base + KVX_K_SC + blk * KVM_SC, a.k.s + row, (uint32_t)nk, bar);
+                        bulk_g2s(base + KVX_V_Q + blk * KVX_Q, a.v.u + row * 32, (uint32_t)nk * 32, bar);
+                        bulk_g2s(base + KVX_V_SC + blk * KVM_SC, a.v.s + row, (uint32_t)nk, bar);
+                        continue;
+                    }
                     bulk_g2s(base + KVM_K_UP + blk * KVM_UP, a.k.u + row * 16, (uint32_t)nk * 16, bar);
                     bulk_g2s(base + KVM_K_SH + blk * KVM_SH, a.k.h + row * 8, (uint32_t)nk * 8, bar);
                     bulk_g2s(base + KVM_K_SC + blk * KVM_SC, a.k.s + row, (uint32_t)nk, bar);
@@ -163,7 +186,9 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
             const int lo = (int)(int8_t)(xi & 0xFF), hi = (xi - lo) >> 8;
             sum += xi;
             const int e = (lane & 7) * 4 + i;
-            const int ts = 2 * (e >> 4) + ((e >> 1) & 1), jj = (e & 1) * 4 + ((e & 15) >> 2);
+            // MXINT8 keys are operands in their stored order, so the query record is in natural element order
+            const int ts = MX ? (e & 15) >> 2 : 2 * (e >> 4) + ((e >> 1) & 1);
+            const int jj = MX ? (e >> 4) * 4 + (e & 3) : (e & 1) * 4 + ((e & 15) >> 2);
             rec[(2 * mm) * 32 + ts * 8 + jj] = (uint8_t)hi;
             rec[(2 * mm + 1) * 32 + ts * 8 + jj] = (uint8_t)lo;
         }
@@ -223,6 +248,27 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
 #pragma unroll
                 for (int mt = 0; mt < 2; ++mt) {
                     const int kk = ck + mt * 16 + g;
+                    if constexpr (MX) {
+                        const uint32_t kb = so + KVX_K_Q + blk * KVX_Q + kk * 32 + t * 4;
+                        uint32_t A[4];
+                        A[0] = lds32<0>(kb);
+                        A[1] = lds32<256>(kb);                      // key + 8
+                        A[2] = lds32<16>(kb);
+                        A[3] = lds32<256 + 16>(kb);
+                        const int e0 = lds_s8<0>(so + KVX_K_SC + blk * KVM_SC + kk);
+                        const int e1 = lds_s8<8>(so + KVX_K_SC + blk * KVM_SC + kk);
+                        const float sw0 = __int_as_float(e0 * (1 << 23) + (127 << 23));
+                        const float sw1 = __int_as_float(e1 * (1 << 23) + (127 << 23));
+#pragma unroll
+                        for (int p = 0; p < PASSES; ++p) {
+                            const uint32_t B[2] = {bq[p].x, bq[p].y};
+                            int Dm[4];
+                            mma_s8_16832_z(Dm, A, B);
+                            S[p][mt][0] = fmaf((float)(Dm[0] * 256 + Dm[1]) * cx[p], sw0, S[p][mt][0]);
+                            S[p][mt][1] = fmaf((float)(Dm[2] * 256 + Dm[3]) * cx[p], sw1, S[p][mt][1]);
+                        }
+                        continue;
+                    }
                     const uint2 w0 = lds64<0>(so + KVM_K_UP + blk * KVM_UP + kk * 16 + h2 * 8);
                     const uint2 w1 = lds64<128>(so + KVM_K_UP + blk * KVM_UP + kk * 16 + h2 * 8);
                     const uint32_t s0 = lds32<0>(so + KVM_K_SH + blk * KVM_SH + kk * 8 + h2 * 4);
@@ -301,7 +347,7 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
             int emax[4];
 #pragma unroll
             for (int blk = 0; blk < 4; ++blk) {
-                const int ev = lds_s8<0>(so + KVM_V_SC + blk * KVM_SC + ck + lane);
+                const int ev = lds_s8<0>(so + (MX ? KVX_V_SC : KVM_V_SC) + blk * KVM_SC + ck + lane);
                 const int evm = (jbase + lane < j1) ? ev : -128;
                 emax[blk] = __reduce_max_sync(0xffffffffu, evm);
                 const int sh = min(emax[blk] - ev, 31);
@@ -396,6 +442,23 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
                     PA[2] = prmt(u1, u2, 0x7632u);      // hi bytes, odd keys   (row g,   k 16+4t..)
                     PA[3] = prmt(u1, u2, 0x5410u);      // lo bytes, odd keys
                 }
+                if constexpr (MX) {
+                    // codes as stored: two transposing loads deliver channels g, g+8 and 16+g, 24+g of the 32 keys
+                    uint32_t va[4], vb[4];
+                    ldmatrix_t8_x2(va, so + KVX_V_Q + blk * KVX_Q + (ck + vkey) * 32);
+                    ldmatrix_t8_x2(vb, so + KVX_V_Q + blk * KVX_Q + (ck + vkey) * 32 + 16);
+                    const float oscx = __int_as_float((emax[blk] + 127) << 23) * (1.0f / 65535.0f) * bsc;
+#pragma unroll
+                    for (int n = 0; n < 4; ++n) {
+                        const uint32_t Bv[2] = {n == 0 ? va[0] : n == 1 ? va[1] : n == 2 ? vb[0] : vb[1],
+                                                n == 0 ? va[2] : n == 1 ? va[3] : n == 2 ? vb[2] : vb[3]};
+                        int Dv[4];
+                        mma_u8s8_16832_z(Dv, PA, Bv);
+                        acc[blk][n][0] = fmaf((float)(Dv[0] * 256 + Dv[2]), oscx, acc[blk][n][0]);
+                        acc[blk][n][1] = fmaf((float)(Dv[1] * 256 + Dv[3]), oscx, acc[blk][n][1]);
+                    }
+                    continue;
+                }
                 uint32_t vr[4], sr[2];
                 ldmatrix_t8_x2(vr, so + KVM_V_UP + blk * KVM_UP + (ck + vkey) * 16);
                 ldmatrix_t8_x1(sr, so + KVM_V_SH + blk * KVM_SH + (ck + 2 * lrow) * 8);
@@ -456,7 +519,8 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     const int col = 2 * t + c;                                  // B column = byte column of the V tile
-                    const int d = blk * 32 + ((n < 2) ? 0 : 16) + 2 * col + ((n & 1) ? 0 : 1);
+                    const int d = MX ? blk * 32 + 8 * n + col
+                                     : blk * 32 + ((n < 2) ? 0 : 16) + 2 * col + ((n & 1) ? 0 : 1);
                     mb[(warp * G + g) * 130 + d] = acc[blk][n][c];
                 }
     }

@@ -37,6 +37,7 @@ struct QuantJob {
     uint8_t* shared;
     int rot;
     int rope;                // apply map.rope at the row's slot (= its token position) first
+    int mx;                  // plain MXINT8 planes: `upper` is the int8 code plane [.., 32], `shared` is unused
 };
 struct QuantJobs { QuantJob j[2]; };
 
@@ -101,6 +102,15 @@ quantize_rows_kernel(const QuantJobs jobs, RowMap map, Fmt f) {
         for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
         const int e = block_exponent(amax);
         const double xv = (double)x;
+        if (job.mx) {
+            // plain MXINT8 (ms_lib/pack.py:538-543 of the reference): one int8 code per element on the grid 2^e
+            double qm = rint(xv * pow2d(-e));
+            qm = fmin(fmax(qm, -127.0), 127.0);
+            const int64_t slot = (head * NB + b) * map.Lcap + key;
+            reinterpret_cast<int8_t*>(upper)[slot * BLOCK + lane] = (int8_t)(int)qm;
+            if (lane == 0) scale_exp[slot] = (int8_t)e;
+            continue;
+        }
         double q = rint(xv * pow2d(-(e + f.u)));
         q = fmin(fmax(q, (double)-lim), (double)lim);
         const double res = xv - q * pow2d(e + f.u);
@@ -158,6 +168,36 @@ hadamard_rotate_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __res
     const float inv = (float)(1.0 / sqrt((double)D));
 #pragma unroll
     for (int i = 0; i < EPL; ++i) out[row * D + lane * EPL + i] = __float2bfloat16_rn(v[i] * inv);
+}
+
+// One thread per (output row o, block) of the plain-MXINT8 weight packer (ms_lib/pack.py:546-566 of the
+// reference): q = clip(rint(x / 2^e), +-127) in float64, planes [nb,32,OUT] and [nb,OUT,32].
+__global__ void __launch_bounds__(128)
+pack_weight_mxint8_kernel(const void* __restrict__ W, int w_is_bf16, int8_t* __restrict__ scale_exp,
+                          int8_t* __restrict__ qweight, int8_t* __restrict__ qweight_cm, int64_t OUT, int64_t nb) {
+    chain_release();
+    chain_wait();
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= OUT * nb) return;
+    const int64_t blk = t / OUT, o = t % OUT;
+    float x[BLOCK];
+    const int64_t base = o * nb * BLOCK + blk * BLOCK;
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < BLOCK; ++k) {
+        x[k] = w_is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(W)[base + k]) : static_cast<const float*>(W)[base + k];
+        amax = fmaxf(amax, fabsf(x[k]));
+    }
+    const int e = block_exponent(amax);
+    const double inv = pow2d(-e);
+    if (scale_exp) scale_exp[blk * OUT + o] = (int8_t)e;
+#pragma unroll
+    for (int k = 0; k < BLOCK; ++k) {
+        double q = rint((double)x[k] * inv);
+        q = fmin(fmax(q, -127.0), 127.0);
+        if (qweight) qweight[(blk * BLOCK + k) * OUT + o] = (int8_t)(int)q;
+        if (qweight_cm) qweight_cm[(blk * OUT + o) * BLOCK + k] = (int8_t)(int)q;
+    }
 }
 
 // One thread per (output row o, block): quantise 32 weights and scatter the
@@ -240,7 +280,7 @@ int quantize_rows(const void* X, int8_t* se, uint8_t* up, uint8_t* sh, const Row
     if (!X || !se || !up || !sh) return fail(MSAQ_ERR_ARG, "null pointer");
     if (int rc = check_rows(map, D, NB, u, gs, &f)) return rc;
     QuantJobs jobs{};
-    jobs.j[0] = QuantJob{static_cast<const __nv_bfloat16*>(X), se, up, sh, rot ? 1 : 0, map.rope.cos ? 1 : 0};
+    jobs.j[0] = QuantJob{static_cast<const __nv_bfloat16*>(X), se, up, sh, rot ? 1 : 0, map.rope.cos ? 1 : 0, 0};
     return launch_rows(jobs, 1, map, D, f, static_cast<cudaStream_t>(stream));
 }
 
@@ -285,8 +325,8 @@ extern "C" int msaq_kv_append_pair_rope(const void* Xk, const void* Xv, int8_t* 
     if (int rc = check_rows(m, D, NB, u, gs, &f)) return rc;
     QuantJobs jobs{};
     jobs.j[0] = QuantJob{static_cast<const __nv_bfloat16*>(Xk), k_scale_exp, k_upper, k_shared, rotate_k ? 1 : 0,
-                         rope_cos ? 1 : 0};
-    jobs.j[1] = QuantJob{static_cast<const __nv_bfloat16*>(Xv), v_scale_exp, v_upper, v_shared, 0, 0};
+                         rope_cos ? 1 : 0, 0};
+    jobs.j[1] = QuantJob{static_cast<const __nv_bfloat16*>(Xv), v_scale_exp, v_upper, v_shared, 0, 0, 0};
     return launch_rows(jobs, 2, m, D, f, static_cast<cudaStream_t>(stream));
 }
 
@@ -344,4 +384,41 @@ extern "C" int msaq_pack_weight(const void* W, int w_is_bf16, int8_t* scale_exp,
     launch_chained(pack_weight_kernel, dim3((unsigned)((total + 127) / 128)), dim3(128), 0, static_cast<cudaStream_t>(stream), W, w_is_bf16, scale_exp, upper, shared, upper_cm, shared_cm, OUT, nb, f);
     count_launch();
     return check_launch("pack_weight");
+}
+
+// ---- plain MXINT8 (the reference's matched baseline format, csrc/mxint8.cu) ----------------------------
+extern "C" int msaq_mxint8_pack_weight(const void* W, int w_is_bf16, int8_t* scale_exp, int8_t* qweight, int8_t* qweight_cm,
+                                       int64_t OUT, int64_t K, void* stream) {
+    if (!W) return fail(MSAQ_ERR_ARG, "W is null");
+    if (OUT <= 0 || K <= 0 || K % BLOCK) return fail(MSAQ_ERR_ARG, "K must be a positive multiple of 32");
+    const int64_t nb = K / BLOCK, total = OUT * nb;
+    launch_chained(pack_weight_mxint8_kernel, dim3((unsigned)((total + 127) / 128)), dim3(128), 0,
+                   static_cast<cudaStream_t>(stream), W, w_is_bf16, scale_exp, qweight, qweight_cm, OUT, nb);
+    count_launch();
+    return check_launch("pack_weight_mxint8");
+}
+
+namespace {
+int mxint8_rows(const void* X, int8_t* se, int8_t* qw, const RowMap& map, int64_t D, int64_t NB, void* stream) {
+    Fmt f;
+    if (!X || !se || !qw) return fail(MSAQ_ERR_ARG, "null pointer");
+    if (int rc = check_rows(map, D, NB, 4, 2, &f)) return rc;        // the format argument is unused by the MXINT8 rows
+    QuantJobs jobs{};
+    jobs.j[0] = QuantJob{static_cast<const __nv_bfloat16*>(X), se, reinterpret_cast<uint8_t*>(qw), nullptr, 0, 0, 1};
+    return launch_rows(jobs, 1, map, D, f, static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+extern "C" int msaq_mxint8_kv_append(const void* X, int8_t* scale_exp, int8_t* qweight, int64_t H, int64_t D, int64_t NB,
+                                     int64_t pos, int64_t Lcap, void* stream) {
+    RowMap m{H, 1, pos, Lcap, nullptr, 1, nullptr};
+    return mxint8_rows(X, scale_exp, qweight, m, D, NB, stream);
+}
+
+extern "C" int msaq_mxint8_kv_write(const void* X, int8_t* scale_exp, int8_t* qweight, int64_t H, int64_t L, int64_t D,
+                                    int64_t NB, int64_t key0, int64_t Lcap, void* stream) {
+    if (L < 0 || H < 0) return fail(MSAQ_ERR_ARG, "negative size");
+    if (L == 0) return MSAQ_OK;
+    RowMap m{H * L, L, key0, Lcap, nullptr, 1, nullptr};
+    return mxint8_rows(X, scale_exp, qweight, m, D, NB, stream);
 }

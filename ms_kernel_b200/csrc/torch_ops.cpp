@@ -426,6 +426,119 @@ Tensor rope(const Tensor& x, const Tensor& cos, const Tensor& sin, const c10::op
     return out;
 }
 
+// ---- plain MXINT8 baseline (schemas of the reference, csrc/pybind.cpp:290-293,314-322) -------------------
+void check_i8(const Tensor& t, const Tensor& like, int64_t numel, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.get_device() == like.get_device() && t.scalar_type() == at::kChar && t.is_contiguous() &&
+                t.numel() == numel, name, " must be a contiguous CUDA int8 tensor of ", numel, " elements");
+}
+
+Tensor mxint8_gemv_impl(const Tensor& x, const Tensor& s, const Tensor& qw, int64_t M, int64_t OUT, int64_t NB, bool batched) {
+    check_act(x, "x");
+    TORCH_CHECK(M >= 1 && OUT >= 1 && NB >= 1, "M, OUT and NB must be positive");
+    TORCH_CHECK(x.numel() == M * NB * 32, "x has ", x.numel(), " elements, expected M*K = ", M * NB * 32);
+    check_i8(s, x, NB * OUT, "scale_exp");
+    check_i8(qw, x, NB * OUT * 32, "qweight_cm");
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor y = batched ? at::empty({M, OUT}, x.options()) : at::empty({OUT}, x.options());
+    const size_t wsb = msaq_mxint8_gemv_workspace(M, OUT, NB);
+    Tensor ws = workspace(x, wsb);
+    check_rc(msaq_mxint8_gemv_batched_wide(x.data_ptr(), s.data_ptr<int8_t>(), qw.data_ptr<int8_t>(), y.data_ptr(), nullptr,
+                                           M, OUT, NB, ws.data_ptr(), wsb, stream_of(x)), "mxint8_gemv");
+    return y;
+}
+Tensor mxint8_gemv_wide(const Tensor& x, const Tensor& s, const Tensor& qw, int64_t OUT, int64_t NB) {
+    return mxint8_gemv_impl(x, s, qw, 1, OUT, NB, false);
+}
+Tensor mxint8_gemv_batched_wide(const Tensor& x, const Tensor& s, const Tensor& qw, int64_t M, int64_t OUT, int64_t NB) {
+    return mxint8_gemv_impl(x, s, qw, M, OUT, NB, true);
+}
+
+std::vector<Tensor> mxint8_pack_weight(const Tensor& W) {
+    TORCH_CHECK(W.is_cuda() && W.dim() == 2 && W.is_contiguous(), "W must be a contiguous 2-D CUDA tensor");
+    TORCH_CHECK(W.scalar_type() == at::kBFloat16 || W.scalar_type() == at::kFloat, "W must be bf16 or fp32");
+    const int64_t OUT = W.size(0), K = W.size(1);
+    TORCH_CHECK(K % 32 == 0, "K must be a multiple of 32");
+    const int64_t nb = K / 32;
+    c10::cuda::CUDAGuard guard(W.device());
+    auto o = W.options().dtype(at::kChar);
+    Tensor s = at::empty({nb, OUT}, o), qw = at::empty({nb, 32, OUT}, o), qwc = at::empty({nb, OUT, 32}, o);
+    check_rc(msaq_mxint8_pack_weight(W.data_ptr(), W.scalar_type() == at::kBFloat16, s.data_ptr<int8_t>(), qw.data_ptr<int8_t>(),
+                                     qwc.data_ptr<int8_t>(), OUT, K, stream_of(W)), "mxint8_pack_weight");
+    return {s, qw, qwc};
+}
+
+std::vector<Tensor> mxint8_kv_write(const Tensor& X, int64_t H, int64_t L, int64_t D, int64_t NB) {
+    check_act(X, "X");
+    TORCH_CHECK(X.numel() == H * L * D, "X must hold H*L*D elements");
+    c10::cuda::CUDAGuard guard(X.device());
+    Tensor s = at::empty({H, NB, L}, X.options().dtype(at::kChar));
+    Tensor qw = at::empty({H, NB, L, 32}, X.options().dtype(at::kChar));
+    check_rc(msaq_mxint8_kv_write(X.data_ptr(), s.data_ptr<int8_t>(), qw.data_ptr<int8_t>(), H, L, D, NB, 0, L, stream_of(X)),
+             "mxint8_kv_write");
+    return {s, qw};
+}
+
+void mxint8_kv_write_into(const Tensor& X, Tensor s, Tensor qw, int64_t H, int64_t L, int64_t D, int64_t NB, int64_t key0,
+                          int64_t Lcap) {
+    check_act(X, "X");
+    TORCH_CHECK(X.numel() == H * L * D, "X must hold H*L*D elements");
+    check_i8(s, X, H * NB * Lcap, "scale_exp");
+    check_i8(qw, X, H * NB * Lcap * 32, "qweight");
+    c10::cuda::CUDAGuard guard(X.device());
+    check_rc(msaq_mxint8_kv_write(X.data_ptr(), s.data_ptr<int8_t>(), qw.data_ptr<int8_t>(), H, L, D, NB, key0, Lcap,
+                                  stream_of(X)), "mxint8_kv_write_into");
+}
+
+void mxint8_kv_append(const Tensor& X, Tensor s, Tensor qw, int64_t H, int64_t D, int64_t NB, int64_t pos, int64_t Lcap) {
+    check_act(X, "X");
+    TORCH_CHECK(X.numel() == H * D, "X must hold H*D elements");
+    check_i8(s, X, H * NB * Lcap, "scale_exp");
+    check_i8(qw, X, H * NB * Lcap * 32, "qweight");
+    c10::cuda::CUDAGuard guard(X.device());
+    check_rc(msaq_mxint8_kv_append(X.data_ptr(), s.data_ptr<int8_t>(), qw.data_ptr<int8_t>(), H, D, NB, pos, Lcap, stream_of(X)),
+             "mxint8_kv_append");
+}
+
+Tensor mxint8_decode_impl(const Tensor& q, const Tensor& ks, const Tensor& kq, const Tensor& vs, const Tensor& vq,
+                          const c10::optional<Tensor>& seq_lens, int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D,
+                          int64_t NB, int64_t Lcap, bool batched) {
+    check_act(q, "q");
+    if (Lcap < 0) Lcap = Lk;
+    TORCH_CHECK(q.numel() == B * H * D, "q must hold B*H*D elements");
+    check_i8(ks, q, B * Hkv * NB * Lcap, "ks");
+    check_i8(vs, q, B * Hkv * NB * Lcap, "vs");
+    check_i8(kq, q, B * Hkv * NB * Lcap * 32, "kq");
+    check_i8(vq, q, B * Hkv * NB * Lcap * 32, "vq");
+    const int32_t* lens = nullptr;
+    if (seq_lens.has_value()) {
+        const Tensor& sl = *seq_lens;
+        TORCH_CHECK(sl.is_cuda() && sl.scalar_type() == at::kInt && sl.is_contiguous() && sl.numel() == B,
+                    "seq_lens must be a contiguous CUDA int32 tensor of B elements");
+        lens = sl.data_ptr<int32_t>();
+    }
+    c10::cuda::CUDAGuard guard(q.device());
+    Tensor out = batched ? at::empty({B, H, D}, q.options()) : at::empty({H, D}, q.options());
+    const size_t wsb = msaq_kv_decode_workspace(B, H, Hkv, Lk, D);
+    Tensor ws = workspace(q, wsb);
+    check_rc(msaq_mxint8_kv_decode_batched(q.data_ptr(), ks.data_ptr<int8_t>(), kq.data_ptr<int8_t>(), vs.data_ptr<int8_t>(),
+                                           vq.data_ptr<int8_t>(), out.data_ptr(), nullptr, lens, B, H, Hkv, Lk, D, NB, Lcap,
+                                           ws.data_ptr(), wsb, stream_of(q)), "mxint8_kv_decode");
+    return out;
+}
+Tensor mxint8_kv_decode(const Tensor& q, const Tensor& ks, const Tensor& kq, const Tensor& vs, const Tensor& vq, int64_t H,
+                        int64_t Hkv, int64_t Lk, int64_t D, int64_t NB, int64_t Lcap) {
+    return mxint8_decode_impl(q, ks, kq, vs, vq, c10::nullopt, 1, H, Hkv, Lk, D, NB, Lcap, false);
+}
+Tensor mxint8_kv_decode_batched(const Tensor& q, const Tensor& ks, const Tensor& kq, const Tensor& vs, const Tensor& vq,
+                                int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D, int64_t NB, int64_t Lcap) {
+    return mxint8_decode_impl(q, ks, kq, vs, vq, c10::nullopt, B, H, Hkv, Lk, D, NB, Lcap, true);
+}
+Tensor mxint8_kv_decode_varlen(const Tensor& q, const Tensor& ks, const Tensor& kq, const Tensor& vs, const Tensor& vq,
+                               const Tensor& seq_lens, int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D, int64_t NB,
+                               int64_t Lcap) {
+    return mxint8_decode_impl(q, ks, kq, vs, vq, seq_lens, B, H, Hkv, Lk, D, NB, Lcap, true);
+}
+
 // ---- layer-step glue ----------------------------------------------------------
 Tensor rmsnorm(const Tensor& x, double eps) {
     check_act(x, "x");
@@ -515,6 +628,26 @@ TORCH_LIBRARY(msaq, m) {
     m.def("wonly_gemv_batched_f32(Tensor x, Tensor scale_exp, Tensor upper_cm, Tensor shared_cm, "
           "int M, int OUT, int NB, int u, int gs) -> Tensor", &wonly_gemv_batched_f32);
     m.def("pack_weight(Tensor W, int u, int gs) -> Tensor[]", &pack_weight);
+    // the reference's MXINT8 baseline operators on the decode path (schemas as in csrc/pybind.cpp:290-293,314-322)
+    m.def("mxint8_gemv_wide(Tensor x, Tensor scale_exp, Tensor qweight_cm, "
+          "int OUT, int NB) -> Tensor", &mxint8_gemv_wide);
+    m.def("mxint8_gemv_batched_wide(Tensor x, Tensor scale_exp, Tensor qweight_cm, "
+          "int M, int OUT, int NB) -> Tensor", &mxint8_gemv_batched_wide);
+    m.def("mxint8_kv_decode(Tensor q, Tensor ks, Tensor kq, "
+          "Tensor vs, Tensor vq, int H, int Hkv, int Lk, int D, int NB, int Lcap=-1) -> Tensor",
+          &mxint8_kv_decode);
+    m.def("mxint8_kv_decode_batched(Tensor q, Tensor ks, Tensor kq, Tensor vs, Tensor vq, "
+          "int B, int H, int Hkv, int Lk, int D, int NB, int Lcap=-1) -> Tensor",
+          &mxint8_kv_decode_batched);
+    m.def("mxint8_kv_write(Tensor X, int H, int L, int D, int NB) -> Tensor[]", &mxint8_kv_write);
+    m.def("mxint8_kv_append(Tensor X, Tensor(a!) scale_exp, Tensor(b!) qweight, "
+          "int H, int D, int NB, int pos, int Lcap) -> ()", &mxint8_kv_append);
+    // additions of this library
+    m.def("mxint8_pack_weight(Tensor W) -> Tensor[]", &mxint8_pack_weight);
+    m.def("mxint8_kv_write_into(Tensor X, Tensor(a!) scale_exp, Tensor(b!) qweight, int H, int L, int D, int NB, int key0, "
+          "int Lcap) -> ()", &mxint8_kv_write_into);
+    m.def("mxint8_kv_decode_varlen(Tensor q, Tensor ks, Tensor kq, Tensor vs, Tensor vq, Tensor seq_lens, "
+          "int B, int H, int Hkv, int Lk, int D, int NB, int Lcap) -> Tensor", &mxint8_kv_decode_varlen);
     m.def("rmsnorm(Tensor x, float eps) -> Tensor", &rmsnorm);
     m.def("silu_mul(Tensor gate_up) -> Tensor", &silu_mul);
     m.def("add_residual(Tensor h, Tensor delta) -> Tensor", &add_residual);

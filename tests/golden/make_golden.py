@@ -16,6 +16,8 @@ What is recorded
   rot_*   the fp32 butterfly rotation written out as plain loops (the formula of
           the reference's append/rotate kernels), reference pack_kv() of those
           values, and the reference's host formulation bf16(K) @ H/sqrt(n)
+  mx_*    plain MXINT8 (pack_weight_mxint8 / pack_kv_mxint8 / dequant / wonly_matmul_mxint8 /
+          kv_attention_mxint8): planes and outputs of the reference's baseline format
   rope_*  the rotary embedding of the reference's harness (tests/harness_batchsweep.py:
           rope_tables, rope_pos, rope_bthd, executed from its source with torch on the CPU):
           tables, rotated rows, and reference pack_kv() of rope -> butterfly rotation
@@ -179,6 +181,23 @@ def main():
         p = rp.pack_kv(rotk, u, gs)
         for k in ("scale_exp", "upper", "shared"):
             out[f"ropek_{k}_u{u}_gs{gs}"] = p[k]
+
+    # ---- plain MXINT8, the reference's matched baseline format ----
+    rng3 = np.random.default_rng(20251127)
+    Wm = bf16_round((rng3.standard_normal((40, 96)) * rng3.uniform(0.005, 0.08, (40, 1))).astype(np.float32))
+    Wm[:14, :32] = blocks[:14]                                # the hand-made edge blocks as weight blocks
+    Xm = bf16_round(rng3.standard_normal((3, 96)).astype(np.float32))
+    pm = rp.pack_weight_mxint8(Wm)
+    out["mx_W"], out["mx_X"] = Wm, Xm
+    for k in ("scale_exp", "qweight", "qweight_cm"):
+        out[f"mx_w_{k}"] = pm[k]
+    out["mx_w_deq"] = rp.dequant_weight_mxint8(pm)
+    out["mx_w_y"] = rr.wonly_matmul_mxint8(pm, Xm)
+    pKm, pVm = rp.pack_kv_mxint8(Kt), rp.pack_kv_mxint8(Vt)
+    for k in ("scale_exp", "qweight"):
+        out[f"mx_kv_K{k}"], out[f"mx_kv_V{k}"] = pKm[k], pVm[k]
+    out["mx_kv_prefill"] = rr.kv_attention_mxint8(Qp, pKm, pVm, causal=True)
+    out["mx_kv_decode"] = rr.kv_attention_mxint8(Qp[:, -1:, :], pKm, pVm, causal=True)[:, 0]
 
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "msaq_golden.npz")
     np.savez_compressed(dst, **out)

@@ -109,3 +109,19 @@ def test_rope_matches_reference_harness(golden):
         p = orc.pack_kv_rotated(k, u, gs)
         for key in ("scale_exp", "upper", "shared"):
             assert np.array_equal(p[key], golden[f"ropek_{key}_u{u}_gs{gs}"]), (u, gs, key)
+
+
+def test_mxint8_matches_reference(golden):
+    """The plain-MXINT8 baseline format: planes, dequantisation, matmul and attention of the reference."""
+    p = orc.pack_weight_mxint8(golden["mx_W"])
+    for k in ("scale_exp", "qweight", "qweight_cm"):
+        assert p[k].dtype == golden[f"mx_w_{k}"].dtype and np.array_equal(p[k], golden[f"mx_w_{k}"]), k
+    assert np.array_equal(orc.dequant_weight_mxint8(p), golden["mx_w_deq"])
+    assert np.allclose(orc.wonly_matmul_mxint8(p, golden["mx_X"]), golden["mx_w_y"], rtol=1e-12, atol=0)
+    pK, pV = orc.pack_kv_mxint8(golden["kv_K"]), orc.pack_kv_mxint8(golden["kv_V"])
+    for k in ("scale_exp", "qweight"):
+        assert np.array_equal(pK[k], golden[f"mx_kv_K{k}"]) and np.array_equal(pV[k], golden[f"mx_kv_V{k}"]), k
+    Q = golden["kv_Q"]
+    dec = orc.decode_attention_planes_mxint8(Q[:, -1, :], (pK["scale_exp"], pK["qweight"]), (pV["scale_exp"], pV["qweight"]),
+                                             Q.shape[1])
+    assert np.allclose(dec, golden["mx_kv_decode"], rtol=1e-10, atol=1e-12)
