@@ -48,7 +48,7 @@ __host__ __device__ constexpr int kvm_smem_bytes(int fmt) {      // ring + query
     return KVM_STAGES * kvm_stage_bytes(fmt) + 4 * 2 * 320 + KVM_WARPS * 8 * 40 * 4 + KVM_WARPS * 4 * 32 * 4;
 }
 constexpr int KVM_QREC = 320;               // staged query record per (block, pass); layout as in gemv_mma.cuh
-constexpr float KVM_SPLIT_TAU = 0.001953125f;  // 2^-9: boundary between the big and the small keys of a split chunk
+constexpr float KVM_SPLIT_TAU = 0.001953125f;  // 2^-9: a chunk is split when all keys but its maximum sum to less than this
 constexpr int KVM_PSTRIDE = 40;             // floats per head row of the probability exchange buffer
 constexpr int KVM_OFF_Q = KVM_STAGES * KVM_STAGE_BYTES;
 constexpr int KVM_OFF_P = KVM_OFF_Q + 4 * 2 * KVM_QREC;
@@ -302,10 +302,10 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
             // the P.V operand always spans the chunk's largest key) and the factor 2^(chunk max -
             // running max) is applied in fp32 to the chunk's integer result: a chunk far below an
             // earlier dominant key keeps its full relative precision.
-            // A chunk whose probabilities fall into a "big" set (within 2^-9 of the chunk maximum, e.g. an
-            // attention sink) and a "small" set whose sum is itself below 2^-9 would leave the small keys
-            // under the resolution of the 16-bit operand.  Such a chunk (split[p] > 0, rare) takes two P.V
-            // passes: the small keys relative to their own sum, then the big keys relative to the maximum.
+            // A chunk that one key dominates -- every other key together below 2^-9 of it, e.g. an attention
+            // sink -- would leave the others under the resolution of the 16-bit operand.  Such a chunk
+            // (split[p] > 0, rare) takes two P.V passes: the small keys relative to their own sum, then the
+            // dominant key.  (The sum of the probabilities is there anyway, so looking for this costs nothing.)
             float alpha[PASSES], beta[PASSES], split[PASSES];
 #pragma unroll
             for (int p = 0; p < PASSES; ++p) {
@@ -324,22 +324,18 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
                 alpha[p] = exp2f(m_run[p] - m_use);                                          // 0 when nothing was seen before
                 const float mc = (mx == -INFINITY) ? 0.0f : mx;                              // the chunk's own maximum
                 beta[p] = (mx == -INFINITY) ? 0.0f : exp2f(mx - m_use);
-                float ps = 0.0f, psm = 0.0f;
+                float ps = 0.0f;
 #pragma unroll
                 for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
                     for (int r = 0; r < 2; ++r) {
                         const float pv = exp2f(S[p][mt][r] - mc);
                         ps += pv;
-                        psm += (pv < KVM_SPLIT_TAU) ? pv : 0.0f;
                         Pw[(4 * p + t) * KVM_PSTRIDE + mt * 16 + r * 8 + g] = pv;
                     }
 #pragma unroll
-                for (int o = 4; o <= 16; o <<= 1) {
-                    ps += __shfl_xor_sync(0xffffffffu, ps, o);
-                    psm += __shfl_xor_sync(0xffffffffu, psm, o);
-                }
-                split[p] = (psm > 0.0f && psm < a.split_limit) ? psm : 0.0f;
+                for (int o = 4; o <= 16; o <<= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+                split[p] = (ps > 1.0f && ps - 1.0f < a.split_limit) ? ps - 1.0f : 0.0f;       // the maximum itself counts 1
                 l_run[p] = fmaf(l_run[p], alpha[p], ps * beta[p]);
                 m_run[p] = m_new;
             }
@@ -363,10 +359,13 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
                 al = (g < 4) ? al : al1;
                 be = (g < 4) ? be : be1;
             }
-            float sa = __shfl_sync(0xffffffffu, split[0], g & 3);     // head g's small-set sum when its chunk is split
-            if (PASSES > 1) {
-                const float sa1 = __shfl_sync(0xffffffffu, split[PASSES - 1], g & 3);
-                sa = (g < 4) ? sa : sa1;
+            float sa = 0.0f;                                          // head g's small-set sum when its chunk is split
+            if (__any_sync(0xffffffffu, split[0] > 0.0f || split[PASSES - 1] > 0.0f)) {
+                sa = __shfl_sync(0xffffffffu, split[0], g & 3);
+                if (PASSES > 1) {
+                    const float sa1 = __shfl_sync(0xffffffffu, split[PASSES - 1], g & 3);
+                    sa = (g < 4) ? sa : sa1;
+                }
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i)
@@ -398,7 +397,7 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
                     const float4 r1 = *reinterpret_cast<const float4*>(Rw + blk * 32 + 8 * t + 4);
                     const float rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) big_scale = fmaxf(big_scale, pf[i] >= KVM_SPLIT_TAU ? rr[i] : 0.0f);
+                    for (int i = 0; i < 8; ++i) big_scale = fmaxf(big_scale, pf[i] >= 0.5f ? rr[i] : 0.0f);
                 }
                 big_scale = fmaxf(big_scale, __shfl_xor_sync(0xffffffffu, big_scale, 1));
                 big_scale = fmaxf(big_scale, __shfl_xor_sync(0xffffffffu, big_scale, 2));
@@ -415,11 +414,11 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
             float bsc;
             if (pvp == 0) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) pq[i] = is_split ? (pf[i] < KVM_SPLIT_TAU ? pf[i] * sa_inv : 0.0f) : pf[i];
+                for (int i = 0; i < 8; ++i) pq[i] = is_split ? (pf[i] < 0.5f ? fminf(pf[i] * sa_inv, 1.0f) : 0.0f) : pf[i];
                 bsc = is_split ? be * sa : be;
             } else {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) pq[i] = (is_split && pf[i] >= KVM_SPLIT_TAU) ? pf[i] : 0.0f;
+                for (int i = 0; i < 8; ++i) pq[i] = (is_split && pf[i] >= 0.5f) ? pf[i] : 0.0f;
                 bsc = be;
             }
 #pragma unroll
@@ -431,7 +430,7 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
                     const float4 r1 = *reinterpret_cast<const float4*>(Rw + blk * 32 + 8 * t + 4);
                     const float rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) pv16[i] = __float2uint_rn(fminf(pq[i] * rr[i], 1.0f) * 65535.0f);
+                    for (int i = 0; i < 8; ++i) pv16[i] = __float2uint_rn(pq[i] * rr[i] * 65535.0f);
                 }
                 uint32_t PA[4];
                 {

@@ -207,3 +207,62 @@ class KVCache:
         pos_t, pos_i = (None, int(q_pos)) if isinstance(q_pos, int) else (q_pos, 0)
         return _OPS.kv_decode_attention_rope(q, *self.k, *self.v, seq_lens, self.B, Hq, self.Hkv, Lk, self.D, self.nb,
                                              self.u, self.gs, self.Lcap, self.rotate, rope[0], rope[1], pos_t, pos_i)
+
+
+# --------------------------------------------------------------------------
+# plain MXINT8 twins (the reference's matched baseline format, ms_lib/pack.py:530-594)
+# --------------------------------------------------------------------------
+class PackedLinearMX:
+    """A weight in plain MXINT8 (int8 code per element + one scale byte per 32) kept on the device.
+    Built from a bf16 / fp32 weight on the device, or from `pack_weight_mxint8`'s dict."""
+
+    def __init__(self, w_or_pack, device):
+        _require()
+        if isinstance(w_or_pack, dict):
+            self.scale_exp = _dev(w_or_pack["scale_exp"], device).contiguous()
+            self.qweight_cm = _dev(w_or_pack["qweight_cm"], device).contiguous()
+        else:
+            self.scale_exp, _, self.qweight_cm = _OPS.mxint8_pack_weight(w_or_pack.to(device).contiguous())
+        self.nb, self.OUT = int(self.scale_exp.shape[0]), int(self.scale_exp.shape[1])
+        self.K = self.nb * 32
+
+    def nbytes(self):
+        return self.scale_exp.numel() + self.qweight_cm.numel()
+
+    def fwd(self, x):
+        """x [K] or [M,K] bf16 -> [OUT] or [M,OUT] bf16."""
+        if x.dim() == 1:
+            return _OPS.mxint8_gemv_wide(x, self.scale_exp, self.qweight_cm, self.OUT, self.nb)
+        return _OPS.mxint8_gemv_batched_wide(x, self.scale_exp, self.qweight_cm, int(x.shape[0]), self.OUT, self.nb)
+
+
+class KVCacheMX:
+    """K and V caches in plain MXINT8, planes [B,Hkv,nb,Lcap] / [B,Hkv,nb,Lcap,32] (the MXINT8 branch of the
+    reference harness's KVCache, tests/harness_batchsweep.py:139-199); head_dim 128."""
+
+    def __init__(self, B, Hkv, D, Lcap, device):
+        _require()
+        self.B, self.Hkv, self.D, self.Lcap, self.nb = B, Hkv, D, Lcap, D // 32
+
+        def planes():
+            return (torch.zeros((B, Hkv, self.nb, Lcap), dtype=torch.int8, device=device),
+                    torch.zeros((B, Hkv, self.nb, Lcap, 32), dtype=torch.int8, device=device))
+
+        self.k, self.v = planes(), planes()
+        self._full_lens = {}
+
+    def fill(self, K, V, key0=0):
+        B, Hkv, L, D = K.shape
+        for X, pl in ((K, self.k), (V, self.v)):
+            _OPS.mxint8_kv_write_into(X.contiguous(), pl[0], pl[1], B * Hkv, L, D, self.nb, key0, self.Lcap)
+
+    def append(self, k_new, v_new, pos):
+        H = self.B * self.Hkv
+        for X, pl in ((k_new, self.k), (v_new, self.v)):
+            _OPS.mxint8_kv_append(X.reshape(H, self.D).contiguous(), pl[0], pl[1], H, self.D, self.nb, int(pos), self.Lcap)
+
+    def attend(self, q, Lk, seq_lens=None):
+        Hq = int(q.shape[1])
+        if seq_lens is None:
+            return _OPS.mxint8_kv_decode_batched(q, *self.k, *self.v, self.B, Hq, self.Hkv, Lk, self.D, self.nb, self.Lcap)
+        return _OPS.mxint8_kv_decode_varlen(q, *self.k, *self.v, seq_lens, self.B, Hq, self.Hkv, Lk, self.D, self.nb, self.Lcap)

@@ -169,3 +169,56 @@ def test_algorithmic_bytes_add_up():
     weights = (10240 * 8192 + 8192 * 8192 + 57344 * 8192 + 8192 * 28672) // 32 * 25
     assert abs(one - weights - 8 * 8192 * 200) < 2e6          # + activations
     assert abs(8 * eight - one) < 3e6                         # replicated activations only
+
+
+def _run_rank_with_failure(rank, world, port, q):
+    """Two steps; rank 1 fails on the host between them (raises, never joins the second step's all-reduce)."""
+    import datetime
+    import torch.distributed as dist
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=8))
+    rng = np.random.default_rng(5)
+    W, P = _weights(rng)
+    B, L = 1, 8
+    lin = {k: _OracleLinear(v) for k, v in tp.shard_layer(P, SHAPE, world, rank).items()}
+    _, kv, _ = SHAPE.local(world)
+    cache = _OracleCache(B, kv, SHAPE.head_dim, L)
+
+    def all_reduce(t):
+        dist.all_reduce(t)
+        return t
+
+    layer = tp.DecoderLayerTP(SHAPE, world, lin, cache, all_reduce, glue=_TorchGlue())
+    h = torch.from_numpy(rng.standard_normal((B, SHAPE.hidden)).astype(np.float32)).to(torch.bfloat16)
+    h = layer.step(h, 0, 1)                       # step 1: everybody takes part
+    try:
+        if rank == 1:
+            raise RuntimeError("injected host-side failure between two steps")
+        layer.step(h, 1, 2)                       # step 2: the exchange can never complete
+        q.put((rank, "completed"))
+    except RuntimeError as e:
+        q.put((rank, "error: " + str(e).splitlines()[0][:80]))
+    q.close()
+    q.join_thread()                               # flush the result before leaving
+    os._exit(0)                                   # no collective teardown: a peer is gone
+
+
+def test_rank_failure_surfaces_as_an_error_not_a_hang():
+    """Failure detection on the host side: a rank that dies between two steps must make the survivors'
+    next exchange fail within the communicator timeout instead of blocking for ever."""
+    import time
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    t0 = time.time()
+    procs = [ctx.Process(target=_run_rank_with_failure, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=90) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got[1].startswith("error: injected")
+    assert got[0].startswith("error"), got[0]     # the survivor saw an error from its exchange ...
+    assert time.time() - t0 < 80                  # ... well within a bounded time
