@@ -311,6 +311,39 @@ int msaq_kv_decode_attention_rope(const void* q,
                                   int64_t q_pos, const int32_t* q_pos_per_seq,
                                   void* workspace, size_t workspace_bytes, void* stream);
 
+/* ------------------------------------------- W+A decode, prefill vehicle -- */
+
+/*
+ * Run-time activation quantiser: X[M,K] bf16 -> qX int8 [M,K], the MSAQ-signed words q = up*2^u + sh of each
+ * 32-block in the weights' own (u, gs) format, and sa_exp int8 [M,K/32], the block exponents; x ~ q * 2^sa_exp.
+ * Bit-exact with ms_lib/reference.py:38-52 `quant_act(share=True)`.  Replaces op `msaq::quant_act`
+ * (csrc/pybind.cpp:233, kernel csrc/wa_gemm.cu:82-108).
+ */
+int msaq_quant_act(const void* X, int8_t* qX, int8_t* sa_exp, int64_t M, int64_t K, int u, int gs, void* stream);
+
+/*
+ * W+A decode GEMV: Y[M,OUT] = sum over 32-blocks of 2^(sa+sw) * intdot(quant_act(X), q(W)), the reference's
+ * `wa_matmul(share_act=True)` (ms_lib/reference.py:55-60); column-major planes, any (u, gs), any M >= 1.
+ * Replaces ops `msaq::wa_gemv` (csrc/pybind.cpp:203-204) and `msaq::wa_gemv_batched` (:231-232; kernels
+ * csrc/w_gemv.cu:846-1098).  The quantised activations are exact bf16 values, so after the quantiser the
+ * weight-only kernels compute exactly this sum.
+ */
+size_t msaq_wa_gemv_workspace(int64_t M, int64_t OUT, int64_t NB, int u, int gs);
+int msaq_wa_gemv(const void* x, const int8_t* scale_exp, const uint8_t* upper_cm, const uint8_t* shared_cm,
+                 void* y, float* y_f32, int64_t OUT, int64_t NB, int u, int gs,
+                 void* workspace, size_t workspace_bytes, void* stream);
+int msaq_wa_gemv_batched(const void* X, const int8_t* scale_exp, const uint8_t* upper_cm, const uint8_t* shared_cm,
+                         void* Y, float* Y_f32, int64_t M, int64_t OUT, int64_t NB, int u, int gs,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * One-off dequantisation of a packed weight to bf16, Wbf[K,OUT] = bf16(dequant(W))^T, the operand the reference's
+ * prefill hands to a dense GEMM (X[M,K] @ Wbf).  Replaces op `msaq::ms_dequant_bf16` (csrc/pybind.cpp:244-245,
+ * kernel csrc/w_gemv.cu:1242-1275).
+ */
+int msaq_dequant_bf16(const int8_t* scale_exp, const uint8_t* upper_cm, const uint8_t* shared_cm, void* Wbf,
+                      int64_t OUT, int64_t K, int u, int gs, void* stream);
+
 /* ------------------------------------------------- plain MXINT8 baseline -- */
 
 /*

@@ -48,6 +48,11 @@ SIGNATURES = {
                                                      _p, _sz, _p]),
     "msaq_kv_decode_attention_batched": (_int, [_p] * 7 + [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64,
                                                              _int, _int, _i64, _int, _p, _sz, _p]),
+    "msaq_quant_act": (_int, [_p, _p, _p, _i64, _i64, _int, _int, _p]),
+    "msaq_wa_gemv_workspace": (_sz, [_i64, _i64, _i64, _int, _int]),
+    "msaq_wa_gemv": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _int, _int, _p, _sz, _p]),
+    "msaq_wa_gemv_batched": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _int, _int, _p, _sz, _p]),
+    "msaq_dequant_bf16": (_int, [_p, _p, _p, _p, _i64, _i64, _int, _int, _p]),
     "msaq_mxint8_pack_weight": (_int, [_p, _int, _p, _p, _p, _i64, _i64, _p]),
     "msaq_mxint8_gemv_workspace": (_sz, [_i64, _i64, _i64]),
     "msaq_mxint8_gemv_wide": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _p, _sz, _p]),

@@ -174,6 +174,45 @@ __device__ inline int quantize_block(const float* x, const Fmt& f, int* up, int*
     return e;
 }
 
+// 2^k as a double, k in [-1022, 1023].
+__device__ __forceinline__ double pow2_f64(int k) { return __hiloint2double((1023 + k) << 20, 0); }
+
+// The same block quantiser with one lane per element (lane = element index of the 32-block, all 32 lanes
+// take part): returns the block exponent, this element's upper code in *up and its group's shared code in
+// *sh.  Float64 in NumPy's order, like quantize_block, so the codes equal the reference's bit for bit
+// (scalings by powers of two are exact, so a multiply stands in for each divide).
+__device__ __forceinline__ int quantize_lane(float x, int lane, const Fmt& f, int* up, int* sh) {
+    float amax = fmaxf(0.0f, fabsf(x));
+#pragma unroll
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const int e = block_exponent(amax);
+    const int lim = (1 << (7 - f.u)) - 1, slo = -(1 << (f.u - 1)), shi = (1 << (f.u - 1)) - 1;
+    const int g0 = lane & ~(f.gs - 1);                        // first lane of this lane's group
+    const double xv = (double)x;
+    double q = rint(xv * pow2_f64(-(e + f.u)));
+    q = fmin(fmax(q, (double)-lim), (double)lim);
+    const double res = xv - q * pow2_f64(e + f.u);
+    double sum;
+    if (f.gs < 8) {                                           // NumPy: plain running sum below 8 terms
+        sum = 0.0;
+        for (int t = 0; t < f.gs; ++t) sum += __shfl_sync(0xffffffffu, res, g0 + t);
+    } else {                                                  // NumPy: 8 interleaved partial sums, then a tree
+        double r[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) r[j] = __shfl_sync(0xffffffffu, res, g0 + j);
+        for (int t0 = 8; t0 < f.gs; t0 += 8) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) r[j] += __shfl_sync(0xffffffffu, res, g0 + t0 + j);
+        }
+        sum = ((r[0] + r[1]) + (r[2] + r[3])) + ((r[4] + r[5]) + (r[6] + r[7]));
+    }
+    double sq = rint(sum * pow2_f64(-f.lg_gs - e));
+    sq = fmin(fmax(sq, (double)slo), (double)shi);
+    *up = (int)q;
+    *sh = (int)sq;
+    return e;
+}
+
 // Dense LSB-first packing of n codes of `width` bits into zeroed words.
 __device__ inline void pack_codes(const int* codes, int n, int width, uint32_t* words, int nwords) {
     for (int i = 0; i < nwords; ++i) words[i] = 0u;

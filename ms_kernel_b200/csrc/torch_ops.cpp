@@ -426,6 +426,57 @@ Tensor rope(const Tensor& x, const Tensor& cos, const Tensor& sin, const c10::op
     return out;
 }
 
+// ---- W+A decode and the prefill vehicle (schemas of the reference, csrc/pybind.cpp:203-204,231-233,244-245) ----
+Tensor wa_gemv_impl(const Tensor& x, const Tensor& s, const Tensor& up, const Tensor& sh, int64_t M, int64_t OUT,
+                    int64_t NB, int64_t u, int64_t gs, bool batched) {
+    check_act(x, "x");
+    int64_t UB, SB;
+    fmt_sizes(u, gs, &UB, &SB);
+    TORCH_CHECK(M >= 1 && OUT >= 1 && NB >= 1, "M, OUT and NB must be positive");
+    TORCH_CHECK(x.numel() == M * NB * 32, "x has ", x.numel(), " elements, expected M*K = ", M * NB * 32);
+    check_planes(s, up, sh, x, NB * OUT, UB, SB);
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor y = batched ? at::empty({M, OUT}, x.options()) : at::empty({OUT}, x.options());
+    const size_t wsb = msaq_wa_gemv_workspace(M, OUT, NB, (int)u, (int)gs);
+    Tensor ws = workspace(x, wsb);
+    check_rc(msaq_wa_gemv_batched(x.data_ptr(), s.data_ptr<int8_t>(), up.data_ptr<uint8_t>(), sh.data_ptr<uint8_t>(),
+                                  y.data_ptr(), nullptr, M, OUT, NB, (int)u, (int)gs, ws.data_ptr(), wsb, stream_of(x)),
+             "wa_gemv");
+    return y;
+}
+Tensor wa_gemv(const Tensor& x, const Tensor& s, const Tensor& up, const Tensor& sh, int64_t OUT, int64_t NB, int64_t u,
+               int64_t gs) {
+    return wa_gemv_impl(x, s, up, sh, 1, OUT, NB, u, gs, false);
+}
+Tensor wa_gemv_batched(const Tensor& x, const Tensor& s, const Tensor& up, const Tensor& sh, int64_t M, int64_t OUT,
+                       int64_t NB, int64_t u, int64_t gs) {
+    return wa_gemv_impl(x, s, up, sh, M, OUT, NB, u, gs, true);
+}
+
+std::vector<Tensor> quant_act(const Tensor& X, int64_t M, int64_t K, int64_t NB, int64_t u, int64_t gs) {
+    check_act(X, "X");
+    TORCH_CHECK(X.numel() == M * K && NB * 32 == K, "X must hold M*K elements and K = 32*NB");
+    c10::cuda::CUDAGuard guard(X.device());
+    Tensor qX = at::empty({M, K}, X.options().dtype(at::kChar));
+    Tensor sa = at::empty({M, NB}, X.options().dtype(at::kChar));
+    check_rc(msaq_quant_act(X.data_ptr(), qX.data_ptr<int8_t>(), sa.data_ptr<int8_t>(), M, K, (int)u, (int)gs, stream_of(X)),
+             "quant_act");
+    return {qX, sa};
+}
+
+Tensor ms_dequant_bf16(const Tensor& s, const Tensor& up, const Tensor& sh, int64_t OUT, int64_t K, int64_t NB, int64_t u,
+                       int64_t gs) {
+    int64_t UB, SB;
+    fmt_sizes(u, gs, &UB, &SB);
+    TORCH_CHECK(s.is_cuda() && NB * 32 == K, "scale_exp must be a CUDA tensor and K = 32*NB");
+    check_planes(s, up, sh, s, NB * OUT, UB, SB);
+    c10::cuda::CUDAGuard guard(s.device());
+    Tensor W = at::empty({K, OUT}, s.options().dtype(at::kBFloat16));
+    check_rc(msaq_dequant_bf16(s.data_ptr<int8_t>(), up.data_ptr<uint8_t>(), sh.data_ptr<uint8_t>(), W.data_ptr(), OUT, K,
+                               (int)u, (int)gs, stream_of(s)), "ms_dequant_bf16");
+    return W;
+}
+
 // ---- plain MXINT8 baseline (schemas of the reference, csrc/pybind.cpp:290-293,314-322) -------------------
 void check_i8(const Tensor& t, const Tensor& like, int64_t numel, const char* name) {
     TORCH_CHECK(t.is_cuda() && t.get_device() == like.get_device() && t.scalar_type() == at::kChar && t.is_contiguous() &&
@@ -628,6 +679,14 @@ TORCH_LIBRARY(msaq, m) {
     m.def("wonly_gemv_batched_f32(Tensor x, Tensor scale_exp, Tensor upper_cm, Tensor shared_cm, "
           "int M, int OUT, int NB, int u, int gs) -> Tensor", &wonly_gemv_batched_f32);
     m.def("pack_weight(Tensor W, int u, int gs) -> Tensor[]", &pack_weight);
+    // the steps on either side of the weight-only decode path (schemas as in csrc/pybind.cpp:203-204,231-233,244-245)
+    m.def("wa_gemv(Tensor x, Tensor scale_exp, Tensor upper_cm, Tensor shared_cm, "
+          "int OUT, int NB, int u, int gs) -> Tensor", &wa_gemv);
+    m.def("wa_gemv_batched(Tensor x, Tensor scale_exp, Tensor upper_cm, Tensor shared_cm, "
+          "int M, int OUT, int NB, int u, int gs) -> Tensor", &wa_gemv_batched);
+    m.def("quant_act(Tensor X, int M, int K, int NB, int u, int gs) -> Tensor[]", &quant_act);
+    m.def("ms_dequant_bf16(Tensor scale_exp, Tensor upper_cm, Tensor shared_cm, "
+          "int OUT, int K, int NB, int u, int gs) -> Tensor", &ms_dequant_bf16);
     // the reference's MXINT8 baseline operators on the decode path (schemas as in csrc/pybind.cpp:290-293,314-322)
     m.def("mxint8_gemv_wide(Tensor x, Tensor scale_exp, Tensor qweight_cm, "
           "int OUT, int NB) -> Tensor", &mxint8_gemv_wide);

@@ -18,6 +18,7 @@ What is recorded
           values, and the reference's host formulation bf16(K) @ H/sqrt(n)
   mx_*    plain MXINT8 (pack_weight_mxint8 / pack_kv_mxint8 / dequant / wonly_matmul_mxint8 /
           kv_attention_mxint8): planes and outputs of the reference's baseline format
+  wa_*    quant_act(share=True) words and exponents, wa_matmul(share_act=True) outputs
   rope_*  the rotary embedding of the reference's harness (tests/harness_batchsweep.py:
           rope_tables, rope_pos, rope_bthd, executed from its source with torch on the CPU):
           tables, rotated rows, and reference pack_kv() of rope -> butterfly rotation
@@ -198,6 +199,19 @@ def main():
         out[f"mx_kv_K{k}"], out[f"mx_kv_V{k}"] = pKm[k], pVm[k]
     out["mx_kv_prefill"] = rr.kv_attention_mxint8(Qp, pKm, pVm, causal=True)
     out["mx_kv_decode"] = rr.kv_attention_mxint8(Qp[:, -1:, :], pKm, pVm, causal=True)[:, 0]
+
+    # ---- W+A: run-time activation quantisation and the integer-dot product ----
+    rng4 = np.random.default_rng(20251128)
+    Xa = bf16_round((rng4.standard_normal((5, K)) * rng4.uniform(0.01, 8, (5, 1))).astype(np.float32))
+    Xa[0, :32] = bf16_round(blocks[6])                      # ties
+    out["wa_X"] = Xa
+    for u in (2, 3, 4):
+        for gs in (2, 8):
+            tag = f"u{u}_gs{gs}"
+            qx, sx = rr.quant_act(Xa, u, gs, share=True)
+            out[f"wa_q_{tag}"] = qx.astype(np.int8)
+            out[f"wa_exp_{tag}"] = np.rint(np.log2(sx)).astype(np.int16)
+            out[f"wa_y_{tag}"] = rr.wa_matmul(rp.pack_weight(W, u, gs), Xa, share_act=True)
 
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "msaq_golden.npz")
     np.savez_compressed(dst, **out)

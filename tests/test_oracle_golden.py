@@ -125,3 +125,14 @@ def test_mxint8_matches_reference(golden):
     dec = orc.decode_attention_planes_mxint8(Q[:, -1, :], (pK["scale_exp"], pK["qweight"]), (pV["scale_exp"], pV["qweight"]),
                                              Q.shape[1])
     assert np.allclose(dec, golden["mx_kv_decode"], rtol=1e-10, atol=1e-12)
+
+
+@pytest.mark.parametrize("u", (2, 3, 4))
+@pytest.mark.parametrize("gs", (2, 8))
+def test_w_plus_a_matches_reference(golden, u, gs):
+    """Run-time activation quantisation (MSAQ-signed words) and the W+A integer-dot product of the reference."""
+    tag = f"u{u}_gs{gs}"
+    q, e = orc.quant_act(golden["wa_X"], u, gs)
+    assert np.array_equal(q, golden[f"wa_q_{tag}"]) and np.array_equal(e, golden[f"wa_exp_{tag}"])
+    y = orc.wa_matmul(orc.pack_weight(golden["w_W"], u, gs), golden["wa_X"])
+    assert np.allclose(y, golden[f"wa_y_{tag}"], rtol=1e-12, atol=0)
