@@ -49,7 +49,7 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-detail", action="store_true")
-    ap.add_argument("--case", default=None, choices=["gemv", "kv"],
+    ap.add_argument("--case", default=None, choices=["gemv", "gemv16", "kv", "layer"],
                     help="run a few launches of one op only (small driver for ncu captures)")
     a = ap.parse_args()
     if a.steps is None:
@@ -778,16 +778,25 @@ def run_reference(args):
 
 
 def run_case(args):
-    """A handful of launches of one op on cuda:0: the 28672x4096 u4/gs2 M=1 GEMV (92 MB per launch) or
-    the GQA 32/8 flash-decode at Lk=16384, B=8 (157 MB per launch).  Meant to be run under ncu."""
+    """A handful of launches of one op on cuda:0: the 28672x4096 u4/gs2 GEMV with one row or sixteen (92 MB per
+    launch) or the GQA 32/8 flash-decode at Lk=16384, B=8 (157 MB per launch).  Meant to be run under ncu."""
     import torch
     from ms_kernel_b200 import ops
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     g = torch.Generator(device=dev).manual_seed(1)
-    if args.case == "gemv":
+    if args.case == "layer":
+        # three eager decode steps of the 70B-shaped layer on one GPU (the launch list of a step)
+        from ms_kernel_b200 import tp
+        shape = tp.LayerShape.llama31_70b()
+        sets = [LayerSet(shape, 1, 0, args.batch, dev, 1 + i, None) for i in range(2)]
+        torch.cuda.synchronize()
+        for i in range(3):
+            y = sets[i % 2].eager()
+    elif args.case in ("gemv", "gemv16"):
         lins = [make_linear(28672, 4096, U, GS, 3 + i, dev) for i in range(4)]
-        x = torch.randn(4096, generator=g, device=dev).to(torch.bfloat16)
+        M = 1 if args.case == "gemv" else 16               # 16 rows: the tcgen05 / tensor-memory kernel
+        x = torch.randn((M, 4096) if M > 1 else (4096,), generator=g, device=dev).to(torch.bfloat16)
         for i in range(6):
             y = lins[i % 4].fwd(x)
     else:

@@ -33,7 +33,11 @@ MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB, int fmt = GF_MSAQ_U4) {
     const int passes = (int)((rows + GM_MP - 1) / GM_MP);
     s.nb = (int)NB;
     p.kb = 1;
-    const long long slots = (long long)GM_CTAS_PER_SM * sm_count();
+    long long slots = (long long)GM_CTAS_PER_SM * sm_count();
+    // The smallest problems (a tensor-parallel shard of a few MB) run one CTA per SM: fewer partial sums per tile
+    // to hand off and add up, and the whole of a CTA's share fits its ring at once (8192x1024 and 1280x8192, one
+    // row: 13.3 / 14.1 -> 11.2 us; from about 10 MB on three CTAs per SM are faster again).
+    if (OUT * NB * gm_col_bytes(fmt) <= (9LL << 20)) slots = sm_count();
     // Widest tile (fewest, largest TMA copies) that keeps the number of CTAs sharing one tile --
     // and with it the partial sums the finishing warp has to add up -- at or below 32.
     // The 1024-column tile (16 accumulators per thread, half as many barrier hand-offs per byte) pays for a
