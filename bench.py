@@ -35,9 +35,11 @@ U, GS = 4, 2
 LK = 8192                     # cached keys per sequence of the layer step
 L2_BYTES = 126 << 20
 
-# DRAM bytes (read + write) per launch of the dominant kernel from one ncu capture of
-# `gemv_u4gs2_mma_kernel` on the 28672 x 4096 u4/gs2 M=1 GEMV (summary under profiles/).
-NCU_TRAFFIC = {"kernel": "gemv_u4gs2_mma_kernel", "shape": [28672, 4096], "bytes_per_launch": 91.83e6 + 3.5e6,
+# DRAM bytes (read + write) per launch of the dominant kernel from one ncu capture (`--case gemv` below) of
+# `gemv_u4gs2_mma_kernel` on the 28672 x 4096 u4/gs2 M=1 GEMV: 91.84 MB read + 4.75 MB written (split-K partials).
+# The kernel reads every packed byte once, so the figure scales with the algorithmic bytes; it has to be
+# re-captured when the kernel's data flow changes.
+NCU_TRAFFIC = {"kernel": "gemv_u4gs2_mma_kernel", "shape": [28672, 4096], "bytes_per_launch": 91.84e6 + 4.75e6,
                "algorithmic_bytes": 91.82e6}
 
 
@@ -307,7 +309,16 @@ def run_ours(args):
     def make_all_reduce(B):
         if world == 1:
             return None
-        if os.environ.get("MSAQ_BENCH_EXCHANGE", "peer") == "peer":
+        mode = os.environ.get("MSAQ_BENCH_EXCHANGE", "push")
+        if mode == "push":
+            try:
+                ar = tp.PeerExchange(dist.group.WORLD, B * shape.hidden, dev)
+                state["exchange"] = "msaq_peer_exchange: one push kernel over NVLink peer memory (plain peer stores, one flag wait)"
+                return ar
+            except Exception as e:
+                state["exchange_note"] = "push exchange unavailable: %s" % str(e).splitlines()[0][:80]
+                mode = "peer"
+        if mode == "peer":
             try:
                 ar = tp.peer_all_reduce(dist.group.WORLD, B * shape.hidden, torch.float32, dev)
                 state["exchange"] = "one-shot all-reduce over NVLink peer memory (torch symmetric memory)"

@@ -82,6 +82,7 @@ int msaq_get_option(int option);
 #define MSAQ_STATUS_WAIT_GEMV_TM 2
 #define MSAQ_STATUS_WAIT_KV_DECODE 4
 #define MSAQ_STATUS_BAD_APPEND_POS 8
+#define MSAQ_STATUS_PEER_TIMEOUT 16     /* a rank's peers did not arrive in msaq_peer_exchange */
 int msaq_wait_status(int clear, void* stream, int* status_out);
 
 /* ------------------------------------------------------------------ GEMV -- */
@@ -112,6 +113,9 @@ int msaq_wonly_gemv_wide(const void* x, const int8_t* scale_exp, const uint8_t* 
 
 /*
  * Y[M,OUT] = X[M,K] . dequant(W)^T on column-major planes, any M >= 1.
+ * (The tensor-memory kernel -- 9 rows and more, and the u = 2, 3 formats at gs = 2 -- widens q * 2^e through an
+ * fp32 constant of about 2^23 * 2^e: block exponents above 104 overflow there.  bf16 weights of magnitude below
+ * 2^110 never produce them.)
  * Replaces op `msaq::wonly_gemv_batched` (csrc/pybind.cpp:205-206, host
  * csrc/w_gemv.cu:1514-1570).
  */
@@ -310,6 +314,25 @@ int msaq_kv_decode_attention_rope(const void* q,
                                   const float* rope_cos, const float* rope_sin, int64_t rope_rows,
                                   int64_t q_pos, const int32_t* q_pos_per_seq,
                                   void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------- tensor-parallel exchange -- */
+
+/*
+ * out[n] = sum over ranks of partial[n] (fp32, summed in rank order: the same bits on every rank); with `residual`
+ * (bf16 [n]) the result is bf16(residual + sum) instead.  No reference counterpart (the reference has no multi-GPU
+ * code): this is the all-reduce of the row-parallel O and down projections of a tensor-parallel decode layer,
+ * [B, hidden] fp32 per rank, done as one push over NVLink peer memory: plain peer stores of the partial sums into
+ * every peer's buffer, one release-counted flag per peer, one bounded wait.
+ *   peer_bufs[r]  rank r's exchange memory as mapped into THIS process (world pointers, host array); every rank
+ *                 allocates msaq_peer_exchange_bytes(world, n) bytes of peer-accessible memory, zero-filled once,
+ *                 and exchanges the mappings (torch.distributed._symmetric_memory does both)
+ *   parity        0, 1, 0, 1, ... over the successive exchanges of a process (every rank the same sequence)
+ * All ranks must call it the same number of times with the same n.  A rank whose peers do not arrive within the
+ * poll limit (MSAQ_OPT_WAIT_POLLS) writes NaN and sets MSAQ_STATUS_PEER_TIMEOUT; it never hangs.
+ */
+size_t msaq_peer_exchange_bytes(int world, int64_t n);
+int msaq_peer_exchange(const float* partial, const void* residual, void* out, void* const* peer_bufs, int rank, int world,
+                       int64_t n, int parity, void* stream);
 
 /* ------------------------------------------- W+A decode, prefill vehicle -- */
 

@@ -23,7 +23,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "_obj")
 ROOT = os.path.dirname(HERE)
 
-CU_SOURCES = ["capi.cu", "kv_pack.cu", "gemv.cu", "gemv_generic.cu", "kv_decode.cu", "layer_glue.cu", "wa_gemv.cu"]
+CU_SOURCES = ["capi.cu", "kv_pack.cu", "gemv.cu", "gemv_generic.cu", "kv_decode.cu", "layer_glue.cu", "wa_gemv.cu", "peer_exchange.cu"]
 LIB_NAME = "libmsaq_b200.so"
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -67,7 +67,8 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 
 // A wait gave up: mark this call's status word (the finishing code turns the outputs into NaN) and
 // OR `bit` into the library's sticky per-device word that msaq_wait_status() reports to the host.
-constexpr int WAIT_FAIL_GEMV_MMA = 1, WAIT_FAIL_GEMV_UMMA = 2, WAIT_FAIL_KV_DECODE = 4, BAD_APPEND_POS = 8;
+constexpr int WAIT_FAIL_GEMV_MMA = 1, WAIT_FAIL_GEMV_UMMA = 2, WAIT_FAIL_KV_DECODE = 4, BAD_APPEND_POS = 8,
+              PEER_EXCHANGE_TIMEOUT = 16;
 __device__ __forceinline__ void report_wait_failure(int* status, int value, int* sticky, int bit) {
     atomicExch(status, value);
     if (sticky) atomicOr(sticky, bit);

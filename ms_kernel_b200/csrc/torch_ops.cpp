@@ -426,6 +426,33 @@ Tensor rope(const Tensor& x, const Tensor& cos, const Tensor& sin, const c10::op
     return out;
 }
 
+// ---- tensor-parallel exchange ------------------------------------------------------------------------------
+// peer_ptrs: the ranks' exchange buffers as mapped into this process (int64 device addresses, e.g. the
+// buffer_ptrs of a torch symmetric-memory handle).  Returns the fp32 sum, or bf16(residual + sum).
+Tensor peer_exchange(const Tensor& partial, const c10::optional<Tensor>& residual, std::vector<int64_t> peer_ptrs, int64_t rank,
+                     int64_t parity) {
+    TORCH_CHECK(partial.is_cuda() && partial.scalar_type() == at::kFloat && partial.is_contiguous(),
+                "partial must be a contiguous CUDA fp32 tensor");
+    const int64_t world = (int64_t)peer_ptrs.size();
+    TORCH_CHECK(world >= 2 && world <= 8, "2 to 8 ranks");
+    void* bufs[8];
+    for (int64_t r = 0; r < world; ++r) bufs[r] = reinterpret_cast<void*>(peer_ptrs[r]);
+    c10::cuda::CUDAGuard guard(partial.device());
+    Tensor out;
+    const void* res = nullptr;
+    if (residual.has_value()) {
+        check_act(*residual, "residual");
+        TORCH_CHECK(residual->numel() == partial.numel(), "residual and partial sizes differ");
+        out = at::empty_like(*residual);
+        res = residual->data_ptr();
+    } else {
+        out = at::empty_like(partial);
+    }
+    check_rc(msaq_peer_exchange(partial.data_ptr<float>(), res, out.data_ptr(), bufs, (int)rank, (int)world, partial.numel(),
+                                (int)parity, stream_of(partial)), "peer_exchange");
+    return out;
+}
+
 // ---- W+A decode and the prefill vehicle (schemas of the reference, csrc/pybind.cpp:203-204,231-233,244-245) ----
 Tensor wa_gemv_impl(const Tensor& x, const Tensor& s, const Tensor& up, const Tensor& sh, int64_t M, int64_t OUT,
                     int64_t NB, int64_t u, int64_t gs, bool batched) {
@@ -710,6 +737,7 @@ TORCH_LIBRARY(msaq, m) {
     m.def("rmsnorm(Tensor x, float eps) -> Tensor", &rmsnorm);
     m.def("silu_mul(Tensor gate_up) -> Tensor", &silu_mul);
     m.def("add_residual(Tensor h, Tensor delta) -> Tensor", &add_residual);
+    m.def("peer_exchange(Tensor partial, Tensor? residual, int[] peer_ptrs, int rank, int parity) -> Tensor", &peer_exchange);
     m.def("launch_count() -> int", &launch_count);
     m.def("set_option(int option, int value) -> ()", &set_option);
     m.def("get_option(int option) -> int", &get_option);

@@ -161,6 +161,49 @@ def peer_all_reduce(group, numel, dtype, device, slots=2):
     return all_reduce
 
 
+class PeerExchange:
+    """The same exchange on this library's own kernel (msaq_peer_exchange): every rank stores its partial
+    sums straight into its slot of every peer's buffer, counts itself on the peer's flag and waits once
+    for the others -- one kernel, one wait, and the residual add of the step's end inside it
+    (`reduce_add`).  The buffers are torch symmetric memory (peer-mapped by its rendezvous); the kernel
+    uses plain peer stores and loads only.  Successive calls alternate between two halves of the buffer;
+    every rank must make the same calls in the same order."""
+
+    def __init__(self, group, numel, device):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        from . import _lib, ops
+        ops._require()
+        self._op = torch.ops.msaq.peer_exchange
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.numel = int(numel)
+        nbytes = _lib.lib().msaq_peer_exchange_bytes(self.world, self.numel)
+        if nbytes == 0:
+            raise ValueError("peer exchange: 2 to 8 ranks and a positive element count")
+        self._buf = symm.empty(nbytes // 4, dtype=torch.float32, device=device)
+        self._buf.zero_()
+        torch.cuda.synchronize(device)
+        hdl = symm.rendezvous(self._buf, group.group_name)
+        self._ptrs = [int(p) for p in hdl.buffer_ptrs]
+        dist.barrier(group)                     # every rank's flags are zero before anyone pushes
+        torch.cuda.synchronize(device)
+        self._calls = 0
+
+    def _parity(self):
+        p = self._calls & 1
+        self._calls += 1
+        return p
+
+    def __call__(self, t):
+        return self._op(t.reshape(-1), None, self._ptrs, self.rank, self._parity()).reshape(t.shape)
+
+    def reduce_add(self, t, h):
+        """bf16(h + sum over ranks of t), h bf16 of t's shape."""
+        return self._op(t.reshape(-1), h.contiguous(), self._ptrs, self.rank, self._parity())
+
+
 # --------------------------------------------------------------------------
 # the step
 # --------------------------------------------------------------------------
@@ -257,6 +300,8 @@ class DecoderLayerTP:
             h = self._add(h, o)
             gu = self.lin["gate_up"].fwd(self._rmsnorm(h, self.eps))   # [B, 2 * ffn_rows]
             dn = self._partial(self.lin["down"], self._silu_mul(gu, self.ffn_rows))
+        if self.world > 1 and hasattr(self.all_reduce, "reduce_add"):
+            return self.all_reduce.reduce_add(dn, h)                   # exchange + residual add in one kernel
         dn = self.all_reduce(dn) if self.world > 1 else dn
         return self._add(h, dn)
 

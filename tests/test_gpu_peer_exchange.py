@@ -1,0 +1,186 @@
+"""msaq_peer_exchange: the tensor-parallel exchange kernel (push over peer memory, one bounded wait).
+
+On one GPU no two kernels may wait on one another, so the single-GPU cases play the peer from the host: the
+peer's slot and this rank's flag are filled by plain tensor writes BEFORE the launch, the kernel never has to
+wait, and what it pushed into the "peer's" buffer is read back afterwards.  The real two-rank run (two
+processes, two GPUs) is the last test and is skipped on a one-GPU box."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from ms_kernel_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from ms_kernel_b200 import ops
+    ops._require()
+    return torch.ops.msaq
+
+
+def _bufs(world, n, dev):
+    nbytes = _lib.lib().msaq_peer_exchange_bytes(world, n)
+    assert nbytes == 2 * world * n * 4 + 256
+    return [torch.zeros(nbytes // 4, dtype=torch.float32, device=dev) for _ in range(world)]
+
+
+def _flags(buf, world, n):
+    return buf[2 * world * n:].view(torch.int32)
+
+
+@pytest.mark.parametrize("world,rank", [(2, 0), (2, 1), (4, 2), (8, 7)])
+@pytest.mark.parametrize("n", [8192, 4 * 8192 + 4])
+@pytest.mark.parametrize("residual", [False, True])
+def test_exchange_with_host_played_peers(world, rank, n, residual):
+    dev = torch.device("cuda", 0)
+    ops = _ops()
+    g = torch.Generator(device="cpu").manual_seed(world * 100 + rank + n)
+    parts = torch.randn(world, n, generator=g, dtype=torch.float32)
+    h = torch.randn(n, generator=g).to(torch.bfloat16)
+    bufs = _bufs(world, n, dev)
+    grid = -(-(n // 4) // 256)
+    for parity in (0, 1, 0):
+        mine = bufs[rank]
+        for r in range(world):                               # the peers' pushes, played by the host
+            if r != rank:
+                mine[(parity * world + r) * n:(parity * world + r + 1) * n] = parts[r].to(dev)
+        _flags(mine, world, n)[parity] = (world - 1) * grid
+        torch.cuda.synchronize()
+        out = ops.peer_exchange(parts[rank].to(dev), h.to(dev) if residual else None, [b.data_ptr() for b in bufs], rank, parity)
+        torch.cuda.synchronize()
+        want = parts[0].clone()
+        for r in range(1, world):                            # rank order, fp32
+            want += parts[r]
+        if residual:
+            want = (h.float() + want).to(torch.bfloat16)
+            assert out.dtype == torch.bfloat16
+        assert torch.equal(out.cpu(), want)
+        # re-armed for the next use of this parity
+        f = _flags(mine, world, n).cpu()
+        assert f[parity] == 0 and f[2 + parity] == 0
+        # what this rank pushed: its slot in every peer's buffer, and one count per thread block on their flags
+        for r in range(world):
+            if r == rank:
+                continue
+            got = bufs[r][(parity * world + rank) * n:(parity * world + rank + 1) * n].cpu()
+            assert torch.equal(got, parts[rank])
+            assert _flags(bufs[r], world, n)[parity].item() == grid
+            _flags(bufs[r], world, n)[parity] = 0
+    assert ops.wait_status(True) == 0
+
+
+def test_absent_peer_runs_out_and_reports():
+    """The wait has a limit: with a peer that never pushes, the kernel gives up, says so and writes NaN."""
+    dev = torch.device("cuda", 0)
+    ops = _ops()
+    L = _lib.lib()
+    n = 8192
+    bufs = _bufs(2, n, dev)
+    x = torch.ones(n, dtype=torch.float32, device=dev)
+    assert ops.wait_status(True) == 0
+    old = L.msaq_get_option(3)
+    L.msaq_set_option(3, 2000)
+    try:
+        out = ops.peer_exchange(x, None, [b.data_ptr() for b in bufs], 0, 0)
+        torch.cuda.synchronize()
+    finally:
+        L.msaq_set_option(3, old)
+    assert torch.isnan(out).all()
+    assert ops.wait_status(True) & 16
+    assert ops.wait_status(False) == 0
+    # the context is still usable
+    assert float((x + 1).sum().item()) == 2 * n
+
+
+def test_argument_checks():
+    dev = torch.device("cuda", 0)
+    ops = _ops()
+    n = 8192
+    bufs = _bufs(2, n, dev)
+    ptrs = [b.data_ptr() for b in bufs]
+    x = torch.ones(n, dtype=torch.float32, device=dev)
+    with pytest.raises(RuntimeError):
+        ops.peer_exchange(x, None, ptrs, 2, 0)               # rank outside the world
+    with pytest.raises(RuntimeError):
+        ops.peer_exchange(x, None, ptrs, 0, 2)               # parity
+    with pytest.raises(RuntimeError):
+        ops.peer_exchange(x[:6].contiguous(), None, ptrs, 0, 0)   # not a multiple of 4
+    with pytest.raises(RuntimeError):
+        ops.peer_exchange(x, None, ptrs[:1], 0, 0)           # one rank
+    assert _lib.lib().msaq_peer_exchange_bytes(9, n) == 0
+
+
+def _two_rank_worker(rank, world, port, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        import datetime
+        import torch.distributed as dist
+        from ms_kernel_b200 import tp
+        dev = torch.device("cuda", rank)
+        torch.cuda.set_device(dev)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=120))
+        n = 8192
+        ex = tp.PeerExchange(dist.group.WORLD, n, dev)
+        bad = 0
+        gens = [torch.Generator().manual_seed(7 + r) for r in range(world)]
+        for it in range(40):
+            parts = [torch.randn(n, generator=gens[r]) for r in range(world)]
+            h = torch.randn(n, generator=gens[0]).to(torch.bfloat16)
+            want = parts[0].clone()
+            for r in range(1, world):
+                want += parts[r]
+            got = ex(parts[rank].to(dev))
+            bad += int(not torch.equal(got.cpu(), want))
+            got2 = ex.reduce_add(parts[rank].to(dev), h.to(dev))
+            bad += int(not torch.equal(got2.cpu(), (h.float() + want).to(torch.bfloat16)))
+        # the same inside a CUDA graph, replayed
+        x = torch.randn(n, generator=gens[rank]).to(dev)
+        allx = [torch.zeros(n, device=dev) for _ in range(world)]
+        dist.all_gather(allx, x)
+        want = allx[0].clone()
+        for r in range(1, world):
+            want += allx[r]
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            ex(x); ex(x)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            y0 = ex(x)
+            y1 = ex(x)
+        for _ in range(50):
+            g.replay()
+        torch.cuda.synchronize()
+        bad += int(not torch.equal(y0, want)) + int(not torch.equal(y1, want))
+        status = int(torch.ops.msaq.wait_status(True))
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, bad, status))
+    except Exception as e:                                    # pragma: no cover
+        q.put((rank, -1, repr(e)))
+    q.close()
+    q.join_thread()
+
+
+@pytest.mark.timeout(300)
+def test_two_ranks_on_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29650 + os.getpid() % 200
+    procs = [ctx.Process(target=_two_rank_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(30)
+    for rank, bad, status in res:
+        assert bad == 0 and status == 0, (rank, bad, status)
