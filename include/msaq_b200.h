@@ -322,7 +322,8 @@ int msaq_kv_decode_attention_rope(const void* q,
  * (bf16 [n]) the result is bf16(residual + sum) instead.  No reference counterpart (the reference has no multi-GPU
  * code): this is the all-reduce of the row-parallel O and down projections of a tensor-parallel decode layer,
  * [B, hidden] fp32 per rank, done as one push over NVLink peer memory: plain peer stores of the partial sums into
- * every peer's buffer, one release-counted flag per peer, one bounded wait.
+ * every peer's buffer as 16-byte words that carry the exchange's sequence number beside the data, and one bounded
+ * wait of every thread on its own words (no fence, no flag, no barrier between thread blocks).
  *   peer_bufs[r]  rank r's exchange memory as mapped into THIS process (world pointers, host array); every rank
  *                 allocates msaq_peer_exchange_bytes(world, n) bytes of peer-accessible memory, zero-filled once,
  *                 and exchanges the mappings (torch.distributed._symmetric_memory does both)

@@ -1,16 +1,20 @@
 // The exchange step of the tensor-parallel decode layer: sum of one small fp32 vector per rank
 // ([B, hidden], 32 KB at B = 1) over NVLink peer memory, optionally with the residual add behind it.
-// The reference has no multi-GPU code; this replaces a library all-reduce (NCCL: 16.5 us at two ranks for this
-// message; a copy + barrier + reduce + barrier one-shot kernel: 14 us at two ranks, about 30 us at eight) with a
-// push: every rank stores its partial sums straight into its slot of every peer's buffer (plain peer stores, no
-// multicast, no TMA), counts itself on the peer's flag with a release at system scope, waits once for the other
-// ranks' counts on its own flag, and adds the slots up in rank order (so every rank gets the same bits).
+// The reference has no multi-GPU code; this replaces a library all-reduce.  For this message the cost is latency
+// (measured at two ranks, back to back in a CUDA graph: NCCL 24 us, a copy + barrier + reduce + barrier one-shot
+// kernel 13.7 us, a push with a fence and a counted flag 9.3 us), so the data carries its own flag: every rank
+// stores its partial sums into its slot of every peer's buffer as 16-byte words {x0, seq, x1, seq} (plain peer
+// stores, no multicast, no TMA; each 8-byte half is written whole and validates itself), and every thread polls its
+// own words in its own memory until they carry this exchange's sequence number -- no fence, no flag, no barrier
+// between thread blocks.  The slots are added up in rank order, so every rank gets the same bits.
 //
-// Buffers: each rank owns `2 x world x n` floats (two parities x one slot per source rank) and, behind them, two
-// flag words and two done-counters, all zero before the first call.  Successive exchanges alternate parity; a rank
-// can run at most one exchange ahead of a peer (it needs the peer's push to get past its own wait), so two parities
-// are enough, and the last thread block to leave an exchange puts that parity's flag back to zero for its next use.
-// Every wait is bounded: a rank whose peers never arrive gives up, reports through the status word and writes NaN.
+// Buffers: each rank owns `2 x world` slots of 2 n floats (two parities x one slot per source rank) and, behind
+// them, a sequence number and a done-counter per parity, all zero before the first call.  Successive exchanges
+// alternate parity; a rank can run at most one exchange ahead of a peer (it needs the peer's push to finish its
+// own), so a slot is never overwritten while its reader still wants the previous message.  The sequence number of
+// a parity lives in device memory and is advanced by the last thread block to leave, which is what lets one
+// captured launch be replayed.  Every wait is bounded: a rank whose peers never arrive gives up, reports through
+// the status word and writes NaN.
 #include "msaq_common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -31,62 +35,60 @@ struct PeerArgs {
     uint32_t max_polls;
 };
 
-__device__ __forceinline__ unsigned int* px_flag(float* base, int world, int64_t n, int parity) {
-    return reinterpret_cast<unsigned int*>(base + 2 * (int64_t)world * n) + parity;
+// control words behind the slots: [0..1] sequence number per parity, [2..3] done-counter per parity
+__device__ __forceinline__ unsigned int* px_ctl(float* base, int world, int64_t n) {
+    return reinterpret_cast<unsigned int*>(base + 4 * (int64_t)world * n);
+}
+__device__ __forceinline__ void px_store(float* dst, float x0, float x1, uint32_t seq) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(dst), "r"(__float_as_uint(x0)), "r"(seq),
+                 "r"(__float_as_uint(x1)) : "memory");
+}
+__device__ __forceinline__ bool px_load(const float* src, uint32_t seq, float& x0, float& x1) {
+    uint32_t a, fa, b, fb;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(fa), "=r"(b), "=r"(fb) : "l"(src) : "memory");
+    x0 = __uint_as_float(a);
+    x1 = __uint_as_float(b);
+    return fa == seq && fb == seq;
 }
 
 __global__ void __launch_bounds__(PX_THREADS)
 peer_exchange_kernel(const PeerArgs a) {
+    chain_release();                                         // the next kernel may be scheduled; it waits for this one
     chain_wait();
-    __shared__ int ok_sh;
+    unsigned int* ctl = px_ctl(a.buf[a.rank], a.world, a.n);
+    const uint32_t seq = *reinterpret_cast<volatile unsigned int*>(ctl + a.parity) + 1u;
     const int64_t i0 = ((int64_t)blockIdx.x * PX_THREADS + threadIdx.x) * 4;
-    const bool live = i0 < a.n;                              // n is a multiple of 4
-    float4 mine = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (live) {
-        mine = *reinterpret_cast<const float4*>(a.partial + i0);
-        // push: my slot in every peer's buffer of this parity
-        for (int r = 0; r < a.world; ++r) {
+    if (i0 < a.n) {                                          // n is a multiple of 4
+        const float4 mine = *reinterpret_cast<const float4*>(a.partial + i0);
+        for (int r = 0; r < a.world; ++r) {                  // push: my slot in every peer's buffer of this parity
             if (r == a.rank) continue;
-            float* dst = a.buf[r] + ((int64_t)a.parity * a.world + a.rank) * a.n + i0;
-            *reinterpret_cast<float4*>(dst) = mine;
+            float* dst = a.buf[r] + (((int64_t)a.parity * a.world + a.rank) * a.n + i0) * 2;
+            px_store(dst, mine.x, mine.y, seq);
+            px_store(dst + 4, mine.z, mine.w, seq);
         }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence_system();
-        for (int r = 0; r < a.world; ++r) {
-            if (r == a.rank) continue;
-            asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(px_flag(a.buf[r], a.world, a.n, a.parity)) : "memory");
-        }
-        // wait for the other ranks' thread blocks (each counts itself once per peer)
-        unsigned int* flag = px_flag(a.buf[a.rank], a.world, a.n, a.parity);
-        const unsigned int want = (unsigned int)(a.world - 1) * gridDim.x;
-        int ok = 0;
-        // ranks start a step up to a host jitter apart, so this limit is generous: 4 x the poll option, with
+        // ranks start a step up to a host jitter apart, so the limit is generous: 4 x the poll option, with
         // 2 us naps once the first thousand polls have passed (seconds at the default, milliseconds in the tests)
         const uint64_t limit = 4ull * a.max_polls;
-        for (uint64_t p = 0; p < limit; ++p) {
-            unsigned int v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-            if (v >= want) { ok = 1; break; }
-            if (p > 64) __nanosleep(p < 1024 ? 100 : 2000);
-        }
-        if (!ok && a.sticky) atomicOr(a.sticky, PEER_EXCHANGE_TIMEOUT);
-        ok_sh = ok;
-    }
-    __syncthreads();
-    if (live) {
+        uint64_t polls = 0;
+        bool ok = true;
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (ok_sh) {
-            for (int r = 0; r < a.world; ++r) {              // rank order: the same sum on every rank
-                float4 v = mine;
-                if (r != a.rank) {
-                    const float* src = a.buf[a.rank] + ((int64_t)a.parity * a.world + r) * a.n + i0;
-                    v = __ldcv(reinterpret_cast<const float4*>(src));
+        for (int r = 0; r < a.world; ++r) {                  // rank order: the same sum on every rank
+            float4 v = mine;
+            if (r != a.rank) {
+                const float* src = a.buf[a.rank] + (((int64_t)a.parity * a.world + r) * a.n + i0) * 2;
+                bool got0 = false, got1 = false;
+                while (ok) {
+                    if (!got0) got0 = px_load(src, seq, v.x, v.y);
+                    if (!got1) got1 = px_load(src + 4, seq, v.z, v.w);
+                    if (got0 && got1) break;
+                    if (++polls >= limit) ok = false;
+                    else if (polls > 64) __nanosleep(polls < 1024 ? 100 : 2000);
                 }
-                s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
             }
-        } else {
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        if (!ok) {
+            if (a.sticky) atomicOr(a.sticky, PEER_EXCHANGE_TIMEOUT);
             s.x = s.y = s.z = s.w = __int_as_float(0x7FC00000);
         }
         if (a.residual) {
@@ -101,14 +103,12 @@ peer_exchange_kernel(const PeerArgs a) {
             *reinterpret_cast<float4*>(static_cast<float*>(a.out) + i0) = s;
         }
     }
-    // the last thread block to get here re-arms this parity: flag and done-counter back to zero
+    // the last thread block to get here advances this parity's sequence number (every block has read it by then)
     __syncthreads();
     if (threadIdx.x == 0) {
-        unsigned int* done = px_flag(a.buf[a.rank], a.world, a.n, 2 + a.parity);
-        if (atomicAdd(done, 1u) == gridDim.x - 1) {
-            *px_flag(a.buf[a.rank], a.world, a.n, a.parity) = 0u;
-            *done = 0u;
-            __threadfence_system();
+        if (atomicAdd(ctl + 2 + a.parity, 1u) == gridDim.x - 1) {
+            ctl[2 + a.parity] = 0u;
+            ctl[a.parity] = seq;
         }
     }
 }
@@ -120,7 +120,7 @@ using namespace msaq;
 
 extern "C" size_t msaq_peer_exchange_bytes(int world, int64_t n) {
     if (world < 2 || world > PX_MAX_WORLD || n <= 0) return 0;
-    return (size_t)2 * world * n * sizeof(float) + 256;
+    return (size_t)4 * world * n * sizeof(float) + 256;
 }
 
 extern "C" int msaq_peer_exchange(const float* partial, const void* residual, void* out, void* const* peer_bufs, int rank,

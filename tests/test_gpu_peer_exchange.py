@@ -1,7 +1,7 @@
 """msaq_peer_exchange: the tensor-parallel exchange kernel (push over peer memory, one bounded wait).
 
 On one GPU no two kernels may wait on one another, so the single-GPU cases play the peer from the host: the
-peer's slot and this rank's flag are filled by plain tensor writes BEFORE the launch, the kernel never has to
+peers' slots (data words that carry the sequence number) are filled by plain tensor writes BEFORE the launch, the kernel never has to
 wait, and what it pushed into the "peer's" buffer is read back afterwards.  The real two-rank run (two
 processes, two GPUs) is the last test and is skipped on a one-GPU box."""
 
@@ -24,12 +24,28 @@ def _ops():
 
 def _bufs(world, n, dev):
     nbytes = _lib.lib().msaq_peer_exchange_bytes(world, n)
-    assert nbytes == 2 * world * n * 4 + 256
+    assert nbytes == 4 * world * n * 4 + 256
     return [torch.zeros(nbytes // 4, dtype=torch.float32, device=dev) for _ in range(world)]
 
 
-def _flags(buf, world, n):
-    return buf[2 * world * n:].view(torch.int32)
+def _ctl(buf, world, n):
+    """[seq parity 0, seq parity 1, done parity 0, done parity 1]"""
+    return buf[4 * world * n:].view(torch.int32)
+
+
+def _slot(buf, world, n, parity, src):
+    """One source rank's slot as [n / 2, 4] int32 words: x0, seq, x1, seq."""
+    o = (parity * world + src) * 2 * n
+    return buf[o:o + 2 * n].view(torch.int32).view(n // 2, 4)
+
+
+def _encode(x, seq):
+    w = torch.empty(x.numel() // 2, 4, dtype=torch.int32)
+    bits = x.view(torch.int32).view(-1, 2)
+    w[:, 0], w[:, 2] = bits[:, 0], bits[:, 1]
+    w[:, 1] = seq
+    w[:, 3] = seq
+    return w
 
 
 @pytest.mark.parametrize("world,rank", [(2, 0), (2, 1), (4, 2), (8, 7)])
@@ -39,16 +55,17 @@ def test_exchange_with_host_played_peers(world, rank, n, residual):
     dev = torch.device("cuda", 0)
     ops = _ops()
     g = torch.Generator(device="cpu").manual_seed(world * 100 + rank + n)
-    parts = torch.randn(world, n, generator=g, dtype=torch.float32)
     h = torch.randn(n, generator=g).to(torch.bfloat16)
     bufs = _bufs(world, n, dev)
-    grid = -(-(n // 4) // 256)
-    for parity in (0, 1, 0):
+    seqs = {0: 0, 1: 0}
+    for parity in (0, 1, 0, 0):
+        parts = torch.randn(world, n, generator=g, dtype=torch.float32)
+        seqs[parity] += 1
+        seq = seqs[parity]
         mine = bufs[rank]
         for r in range(world):                               # the peers' pushes, played by the host
             if r != rank:
-                mine[(parity * world + r) * n:(parity * world + r + 1) * n] = parts[r].to(dev)
-        _flags(mine, world, n)[parity] = (world - 1) * grid
+                _slot(mine, world, n, parity, r).copy_(_encode(parts[r], seq))
         torch.cuda.synchronize()
         out = ops.peer_exchange(parts[rank].to(dev), h.to(dev) if residual else None, [b.data_ptr() for b in bufs], rank, parity)
         torch.cuda.synchronize()
@@ -59,17 +76,13 @@ def test_exchange_with_host_played_peers(world, rank, n, residual):
             want = (h.float() + want).to(torch.bfloat16)
             assert out.dtype == torch.bfloat16
         assert torch.equal(out.cpu(), want)
-        # re-armed for the next use of this parity
-        f = _flags(mine, world, n).cpu()
-        assert f[parity] == 0 and f[2 + parity] == 0
-        # what this rank pushed: its slot in every peer's buffer, and one count per thread block on their flags
+        # the sequence number moved on and the done-counter is back at rest
+        c = _ctl(mine, world, n).cpu()
+        assert c[parity] == seq and c[2 + parity] == 0
+        # what this rank pushed: its slot in every peer's buffer, every word carrying the sequence number
         for r in range(world):
-            if r == rank:
-                continue
-            got = bufs[r][(parity * world + rank) * n:(parity * world + rank + 1) * n].cpu()
-            assert torch.equal(got, parts[rank])
-            assert _flags(bufs[r], world, n)[parity].item() == grid
-            _flags(bufs[r], world, n)[parity] = 0
+            if r != rank:
+                assert torch.equal(_slot(bufs[r], world, n, parity, rank).cpu(), _encode(parts[rank], seq))
     assert ops.wait_status(True) == 0
 
 
