@@ -28,7 +28,7 @@ LIB_NAME = "libmsaq_b200.so"
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
-]
+] + os.environ.get("MSAQ_NVCC_EXTRA", "").split()      # e.g. -DMSAQ_TRACE for the time-stamp diagnostic build
 
 
 def _nvcc():

@@ -4,6 +4,9 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
+#include <set>
+#include <utility>
 
 #include "msaq_common.cuh"
 
@@ -36,6 +39,7 @@ std::atomic<int> g_opt_chained{-1};
 std::atomic<int> g_opt_tmem{1};
 std::atomic<int> g_opt_polls{1 << 20};
 std::atomic<int> g_opt_inkernel{1};
+std::atomic<int> g_opt_early{0};
 std::atomic<uint32_t> g_call_tag{0};
 std::atomic<int> g_opt_skip{-1};
 
@@ -45,6 +49,7 @@ __device__ int g_sticky_status;
 std::atomic<int*> g_sticky_ptr[64];
 }  // namespace
 
+bool option_early_weights() { return g_opt_early.load(std::memory_order_relaxed) != 0; }
 bool option_inkernel_staging() { return g_opt_inkernel.load(std::memory_order_relaxed) != 0; }
 
 uint32_t next_call_tag() {
@@ -64,6 +69,19 @@ uint32_t next_call_tag() {
 
 unsigned option_wait_polls() { return (unsigned)g_opt_polls.load(std::memory_order_relaxed); }
 int option_test_skip_stage() { return g_opt_skip.load(std::memory_order_relaxed); }
+
+void prefer_max_shared(const void* kernel) {
+    static std::mutex mu;
+    static std::set<std::pair<const void*, int>> done;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!option_early_weights()) return;
+    if (!done.insert({kernel, dev}).second) return;
+    // a preference, not a requirement: a failure here changes nothing but the overlap
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
+        cudaGetLastError();
+}
 
 int* sticky_status() {
     int dev = -1;
@@ -139,6 +157,7 @@ extern "C" int msaq_set_option(int option, int value) {
             return MSAQ_OK;
         case MSAQ_OPT_TEST_SKIP_STAGE: msaq::g_opt_skip.store(value < 0 ? -1 : value, std::memory_order_relaxed); return MSAQ_OK;
         case MSAQ_OPT_INKERNEL_STAGING: msaq::g_opt_inkernel.store(value ? 1 : 0, std::memory_order_relaxed); return MSAQ_OK;
+        case MSAQ_OPT_EARLY_WEIGHTS: msaq::g_opt_early.store(value ? 1 : 0, std::memory_order_relaxed); return MSAQ_OK;
         default: return msaq::fail(MSAQ_ERR_ARG, "unknown option %d", option);
     }
 }
@@ -149,6 +168,7 @@ extern "C" int msaq_get_option(int option) {
         case MSAQ_OPT_WAIT_POLLS: return (int)msaq::option_wait_polls();
         case MSAQ_OPT_TEST_SKIP_STAGE: return msaq::option_test_skip_stage();
         case MSAQ_OPT_INKERNEL_STAGING: return msaq::option_inkernel_staging() ? 1 : 0;
+        case MSAQ_OPT_EARLY_WEIGHTS: return msaq::option_early_weights() ? 1 : 0;
         default: return msaq::fail(MSAQ_ERR_ARG, "unknown option %d", option);
     }
 }

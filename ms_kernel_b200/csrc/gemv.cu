@@ -44,18 +44,19 @@ MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB, int fmt = GF_MSAQ_U4) {
     // single row: 57344x8192 77 -> 68 us; with four rows it measured slower than 512 columns (41.7 against 32.7 us
     // on 28672x4096).
     // (the MXINT8 twin is built for 512- and 256-column tiles, one K block per stage)
-    for (int tc = (M == 1 && fmt == GF_MSAQ_U4) ? GM_MAX_TC : GM_MAX_TC / 2; tc >= (fmt == GF_MXINT8 ? 256 : GM_GROUP); tc >>= 1) {
+    const int min_tc = fmt == GF_MXINT8 ? GM_MAX_TC / 4 : GM_GROUP;
+    for (int tc = (M == 1 && fmt == GF_MSAQ_U4) ? GM_MAX_TC : GM_MAX_TC / 2; tc >= min_tc; tc >>= 1) {
         s.tc = tc;
         s.col_tiles = (int)((OUT + tc - 1) / tc);
         const long long units = s.units();
         s.grid = (int)(units < slots ? units : slots);
-        if (tc == (fmt == GF_MXINT8 ? 256 : GM_GROUP) || (s.grid + s.col_tiles - 1) / s.col_tiles <= 32) break;
+        if (tc == min_tc || (s.grid + s.col_tiles - 1) / s.col_tiles <= 32) break;
     }
-    // Launches of one or two passes (up to eight rows) on 512- or 256-column tiles: two or four K blocks per ring stage,
-    // for the same cut in hand-offs per byte the wider tile gives (8192x28672: 44.5 -> 41.3 us at one row,
+    // Launches of one or two passes (up to eight rows) on half- or quarter-width tiles: two or four K blocks per ring
+    // stage, for the same cut in hand-offs per byte the wider tile gives (8192x28672: 44.5 -> 41.3 us at one row,
     // 54.9 -> 50.8 us at four).
-    if (fmt == GF_MSAQ_U4 && passes <= 2 && (s.tc == 512 || s.tc == 256) && NB >= 4) {
-        p.kb = s.tc == 512 ? 2 : 4;                    // 25.6 KB of packed bytes per stage either way
+    if (fmt == GF_MSAQ_U4 && passes <= 2 && (s.tc == GM_MAX_TC / 2 || s.tc == GM_MAX_TC / 4) && NB >= 4) {
+        p.kb = s.tc == GM_MAX_TC / 2 ? 2 : 4;           // the widest tile's bytes per stage either way
         s.nb = (int)((NB + p.kb - 1) / p.kb);
         const long long u2 = s.units();
         s.grid = (int)(u2 < slots ? u2 : slots);
@@ -93,35 +94,39 @@ int launch_mma_ink(const GemvMmaArgs& a, cudaStream_t st) {
     return check_launch(FMT == GF_MXINT8 ? "gemv_mxint8_mma" : "gemv_u4gs2_mma");
 }
 
-// the MXINT8 twin: 512- or 256-column tiles, one K block per stage, records from the staging kernel
+// the MXINT8 twin: half- or quarter-width tiles, one K block per stage, records from the staging kernel
 template <int PASSES>
 int launch_mma_mx(const GemvMmaArgs& a, cudaStream_t st) {
-    return a.sch.tc == 512 ? launch_mma_ink<PASSES, 512, 1, false, GF_MXINT8>(a, st)
-                           : launch_mma_ink<PASSES, 256, 1, false, GF_MXINT8>(a, st);
+    return a.sch.tc == GM_MAX_TC / 2 ? launch_mma_ink<PASSES, GM_MAX_TC / 2, 1, false, GF_MXINT8>(a, st)
+                                     : launch_mma_ink<PASSES, GM_MAX_TC / 4, 1, false, GF_MXINT8>(a, st);
 }
 
 template <int PASSES, int TC, int KB = 1>
 int launch_mma(const GemvMmaArgs& a, cudaStream_t st) {
-    if constexpr (PASSES == 1) {
-        if (a.xmode >= 0) return launch_mma_ink<PASSES, TC, KB, true>(a, st);
+    if constexpr (TC < GM_GROUP) {
+        return fail(MSAQ_ERR_ARG, "tile narrower than a column group");
+    } else {
+        if constexpr (PASSES == 1) {
+            if (a.xmode >= 0) return launch_mma_ink<PASSES, TC, KB, true>(a, st);
+        }
+        return launch_mma_ink<PASSES, TC, KB, false>(a, st);
     }
-    return launch_mma_ink<PASSES, TC, KB, false>(a, st);
 }
 
 template <int PASSES>
 int launch_mma_tc(const GemvMmaArgs& a, int kb, cudaStream_t st) {
     if (kb > 1) {
-        if constexpr (PASSES <= 2) return kb == 2 ? launch_mma<PASSES, 512, 2>(a, st) : launch_mma<PASSES, 256, 4>(a, st);
+        if constexpr (PASSES <= 2)
+            return kb == 2 ? launch_mma<PASSES, GM_MAX_TC / 2, 2>(a, st) : launch_mma<PASSES, GM_MAX_TC / 4, 4>(a, st);
         return fail(MSAQ_ERR_ARG, "several K blocks per stage are planned for launches of up to two passes only");
     }
-    switch (a.sch.tc) {
-        case 128: return launch_mma<PASSES, 128>(a, st);
-        case 256: return launch_mma<PASSES, 256>(a, st);
-        case 1024:
-            if constexpr (PASSES == 1) return launch_mma<1, 1024>(a, st);
-            return fail(MSAQ_ERR_ARG, "1024-column tiles are planned for single-pass launches only");
-        default: return launch_mma<PASSES, 512>(a, st);
+    if (a.sch.tc == GM_MAX_TC) {
+        if constexpr (PASSES == 1) return launch_mma<1, GM_MAX_TC>(a, st);
+        return fail(MSAQ_ERR_ARG, "the widest tiles are planned for single-pass launches only");
     }
+    if (a.sch.tc == GM_MAX_TC / 2) return launch_mma<PASSES, GM_MAX_TC / 2>(a, st);
+    if (a.sch.tc == GM_MAX_TC / 4) return launch_mma<PASSES, GM_MAX_TC / 4>(a, st);
+    return launch_mma<PASSES, GM_MAX_TC / 8>(a, st);
 }
 
 // ---- tensor-memory path (u4/gs2, column-major planes, OUT % 16 == 0, M >= GU_MIN_M) ----------
@@ -266,7 +271,7 @@ int run_mma(const __nv_bfloat16* X, const Prologue& pro, const int8_t* se, const
         GemvMmaArgs a{se, up, sh, xprep, partial, counters, status, sticky_status(), static_cast<__nv_bfloat16*>(Y), Yf,
                       (int)m0, rows, (int)OUT, (int)NB, sch, option_wait_polls(), option_test_skip_stage(),
                       in_kernel ? pro.mode : -1, xa.X, xa.R, xa.h_out, (int)ldx, pro.r_is_f32, pro.eps, tag,
-                      in_kernel ? (int)table : 0, 0};
+                      in_kernel ? (int)table : 0, 0, option_early_weights() ? 1 : 0};
         // the ring depth was planned for the first tile's pass count; a last, smaller tile may go deeper but need not
         int rc;
         if (fmt == GF_MXINT8) {
@@ -502,3 +507,10 @@ extern "C" int msaq_mxint8_gemv_wide(const void* x, const int8_t* scale_exp, con
                                      int64_t OUT, int64_t NB, void* workspace, size_t workspace_bytes, void* stream) {
     return msaq_mxint8_gemv_batched_wide(x, scale_exp, qweight_cm, y, y_f32, 1, OUT, NB, workspace, workspace_bytes, stream);
 }
+
+#ifdef MSAQ_TRACE
+// diagnostic build only: the per-thread-block time stamps of the last staging and main kernel launches
+extern "C" int msaq_debug_trace(unsigned long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, msaq::g_trace, sizeof(msaq::g_trace)) == cudaSuccess ? 0 : 1;
+}
+#endif

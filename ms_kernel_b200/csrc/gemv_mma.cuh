@@ -29,15 +29,25 @@
 
 namespace msaq {
 
-constexpr int GM_WARPS = 8;          // consumer warps; each owns 16 columns of every 128-column group
+#ifndef MSAQ_GM_WARPS
+#define MSAQ_GM_WARPS 8
+#endif
+#ifndef MSAQ_GM_CTAS
+#define MSAQ_GM_CTAS 3
+#endif
+constexpr int GM_WARPS = MSAQ_GM_WARPS;   // consumer warps; each owns 16 columns of every column group
 constexpr int GM_THREADS = (GM_WARPS + 1) * 32;
-constexpr int GM_GROUP = 128;        // columns per group (8 warps x 16)
-constexpr int GM_MAX_TC = 1024;      // columns per tile (1, 2, 4 or 8 groups; 8 only for single-row launches)
+constexpr int GM_GROUP = GM_WARPS * 16;   // columns per group
+#ifndef MSAQ_GM_MAX_MULT
+#define MSAQ_GM_MAX_MULT 8
+#endif
+constexpr int GM_MAX_MULT = MSAQ_GM_MAX_MULT;   // widest tile in groups (the widest only for single-row launches)
+constexpr int GM_MAX_TC = GM_MAX_MULT * GM_GROUP;
 constexpr int GM_MAX_STAGES = 12;
 constexpr int GM_MP = 4;             // activation rows per MMA pass
 constexpr int GM_MAX_PASSES = 4;     // -> at most 16 rows per launch
 constexpr int GM_XREC = 320;         // bytes of staged activations per (block, pass)
-constexpr int GM_CTAS_PER_SM = 3;
+constexpr int GM_CTAS_PER_SM = MSAQ_GM_CTAS;
 constexpr int GM_MAX_TABLE = (GM_WARPS + 1) * GM_XREC;   // largest in-kernel record table: one record per warp of the CTA
 
 // Stage layout for a tile of TC columns x one K block:
@@ -92,11 +102,25 @@ struct XprepArgs {
     int natural;             // record in natural element order (MXINT8 weights) instead of the nibble-matched order
 };
 
+#ifdef MSAQ_TRACE
+__device__ unsigned long long g_trace[2][1024][8];
+__device__ __forceinline__ void trace_ev(int k, int ev) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (blockIdx.x < 1024) g_trace[k][blockIdx.x][ev] = t;
+}
+#define MSAQ_TR(k, ev, cond) do { if (cond) trace_ev(k, ev); } while (0)
+#else
+#define MSAQ_TR(k, ev, cond) do { } while (0)
+#endif
+
 template <int MODE>
 __global__ void __launch_bounds__(128)
 gemv_xprep_kernel(const XprepArgs a) {
+    MSAQ_TR(0, 0, threadIdx.x == 0);
     chain_release();
     chain_wait();
+    MSAQ_TR(0, 1, threadIdx.x == 0);
     __shared__ float red[GM_MP][4];
     const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
     const int warp = gtid >> 5, lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
@@ -224,6 +248,7 @@ gemv_xprep_kernel(const XprepArgs a) {
         tc[2] = 0;
         tc[3] = 0;
     }
+    MSAQ_TR(0, 2, threadIdx.x == 0);
 }
 
 // ---- main kernel ------------------------------------------------------------------
@@ -256,6 +281,7 @@ struct GemvMmaArgs {
     uint32_t tag;            // identifies this call in the counters and the status word; 31 bits, never 0
     int table_bytes;         // shared memory in front of the ring that holds the in-kernel record table
     int natural;             // in-kernel records in natural element order (see XprepArgs)
+    int early;               // first ring-full of weights goes out before the wait on the kernel in front
 };
 
 // Sums of squares of the launch's rows (of X, or of bf16(X + R) for XP_ADD_NORM) by all threads of the
@@ -374,12 +400,12 @@ template <int PASSES, int Q>
 __device__ __forceinline__ void gemv_group_step_mx(uint32_t wbase, uint32_t ebase, const uint2 (&bq)[PASSES],
                                                    const float (&cx)[PASSES], float (&acc)[PASSES][2]) {
     uint32_t A[4];
-    A[0] = lds32<Q * 4096>(wbase);
-    A[1] = lds32<Q * 4096 + 256>(wbase);
-    A[2] = lds32<Q * 4096 + 16>(wbase);
-    A[3] = lds32<Q * 4096 + 256 + 16>(wbase);
-    const int e0 = lds_s8<Q * 128>(ebase);
-    const int e1 = lds_s8<Q * 128 + 8>(ebase);
+    A[0] = lds32<Q * GM_GROUP * 32>(wbase);
+    A[1] = lds32<Q * GM_GROUP * 32 + 256>(wbase);
+    A[2] = lds32<Q * GM_GROUP * 32 + 16>(wbase);
+    A[3] = lds32<Q * GM_GROUP * 32 + 256 + 16>(wbase);
+    const int e0 = lds_s8<Q * GM_GROUP>(ebase);
+    const int e1 = lds_s8<Q * GM_GROUP + 8>(ebase);
     const float sw0 = __int_as_float(e0 * (1 << 23) + (127 << 23));
     const float sw1 = __int_as_float(e1 * (1 << 23) + (127 << 23));
 #pragma unroll
@@ -398,12 +424,12 @@ template <int PASSES, int Q>
 __device__ __forceinline__ void gemv_group_step(uint32_t wbase, uint32_t sbase, uint32_t ebase, uint32_t sel,
                                                 uint32_t nshift, const uint2 (&bq)[PASSES], const int (&corr)[PASSES],
                                                 const float (&cx)[PASSES], float (&acc)[PASSES][2]) {
-    const uint2 w0 = lds64<Q * 2048>(wbase);
-    const uint2 w1 = lds64<Q * 2048 + 128>(wbase);
-    const uint32_t s0 = lds32<Q * 1024>(sbase);
-    const uint32_t s1 = lds32<Q * 1024 + 64>(sbase);
-    const int e0 = lds_s8<Q * 128>(ebase);
-    const int e1 = lds_s8<Q * 128 + 8>(ebase);
+    const uint2 w0 = lds64<Q * GM_GROUP * 16>(wbase);
+    const uint2 w1 = lds64<Q * GM_GROUP * 16 + 128>(wbase);
+    const uint32_t s0 = lds32<Q * GM_GROUP * 8>(sbase);
+    const uint32_t s1 = lds32<Q * GM_GROUP * 8 + 64>(sbase);
+    const int e0 = lds_s8<Q * GM_GROUP>(ebase);
+    const int e1 = lds_s8<Q * GM_GROUP + 8>(ebase);
     // shared codes (even or odd nibbles of word h) as offset-binary low nibbles
     const uint32_t m0 = and_xor(s0 >> nshift, 0x0F0F0F0Fu, 0x08080808u);
     const uint32_t m1 = and_xor(s1 >> nshift, 0x0F0F0F0Fu, 0x08080808u);
@@ -420,10 +446,11 @@ __device__ __forceinline__ void gemv_group_step(uint32_t wbase, uint32_t sbase, 
     for (int p = 0; p < PASSES; ++p) {
         const uint32_t B[2] = {bq[p].x, bq[p].y};
         int Dm[4];
-        mma_s8_16832_z(Dm, A, B);
-        // (hi plane) * 256 + (lo plane) - 8 * sum(x): the offset-binary shared codes add 8 per element
-        const float f0 = (float)(Dm[0] * 256 + Dm[1] + corr[p]) * cx[p];
-        const float f1 = (float)(Dm[2] * 256 + Dm[3] + corr[p]) * cx[p];
+        // (hi plane) * 256 + (lo plane) - 8 * sum(x): the offset-binary shared codes add 8 per element; that
+        // correction rides into the lo-plane sums as the MMA's accumulator input
+        mma_s8_16832_c(Dm, A, B, corr[p]);
+        const float f0 = (float)(Dm[0] * 256 + Dm[1]) * cx[p];
+        const float f1 = (float)(Dm[2] * 256 + Dm[3]) * cx[p];
         acc[p][0] = fmaf(f0, sw0, acc[p][0]);
         acc[p][1] = fmaf(f1, sw1, acc[p][1]);
     }
@@ -539,6 +566,10 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
     constexpr int STAGE_BYTES = KB * SUB_BYTES;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    MSAQ_TR(1, 0, tid == 0);
+#ifdef MSAQ_TRACE
+    if (tid == 0 && blockIdx.x < 1024) { unsigned int sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); g_trace[1][blockIdx.x][7] = sm; }
+#endif
     const GemvSchedule sch = a.sch;
     float* const yf = a.y_f32;
     const long long n_lo = sch.lo(blockIdx.x), n_hi = sch.lo(blockIdx.x + 1);
@@ -561,51 +592,68 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
 
     if (warp == GM_WARPS) {
         // ------------------------------ producer warp ------------------------------
-        chain_wait();                              // activations (or their records) come from the kernel before this one
+        // With `early` (MSAQ_OPT_EARLY_WEIGHTS: the caller vouches that no kernel in flight writes the weight planes)
+        // the first ring-full of weights goes out BEFORE the wait on the kernel in front (the staging kernel, or
+        // whatever produced the activations): its run time and this kernel's pipeline fill overlap.  Only the
+        // activation records (or, with in-kernel staging, the reads of the activations) wait.  Nothing is written
+        // to global memory on this side of the wait.
         const bool inject = a.skip_stage >= 0 && blockIdx.x == 0;
         int s = 0, issued = 0;
         uint32_t ph = 1;                           // parity of the "previous" empty phase: passes at once on a fresh barrier
         int ci = c, bi = blk;                      // the next unit to issue
-        auto issue = [&](int uc, int ub, int us) {
+        // part 1: expect the whole stage and copy its weights; part 2: copy its activation records; 3: both
+        auto issue = [&](int uc, int ub, int us, int part) {
             const int o0 = uc * TC, cv = min(TC, a.OUT - o0);
             const uint32_t bar = smem_u32(&bar_full[us]);
             const int b0 = ub * KB, nblk = min(KB, a.NB - b0);          // `ub` counts units within the tile
-            mbar_expect_tx(bar, (uint32_t)(nblk * (cv * CB + (stage_here ? 0 : PASSES * GM_XREC))));
+            if (part & 1) mbar_expect_tx(bar, (uint32_t)(nblk * (cv * CB + (stage_here ? 0 : PASSES * GM_XREC))));
 #pragma unroll
             for (int j = 0; j < KB; ++j) {
                 if (j < nblk) {
                     const uint32_t base = smem_u32(smem) + us * STAGE_BYTES + j * SUB_BYTES;
                     const int64_t col = (int64_t)(b0 + j) * a.OUT + o0;
-                    if constexpr (FMT == GF_MXINT8) {
-                        bulk_g2s(base, a.upper_cm + col * 32, (uint32_t)cv * 32, bar);      // the int8 code plane
-                    } else {
-                        bulk_g2s(base, a.upper_cm + col * 16, (uint32_t)cv * 16, bar);
-                        bulk_g2s(base + OFF_SH, a.shared_cm + col * 8, (uint32_t)cv * 8, bar);
+                    if (part & 1) {
+                        if constexpr (FMT == GF_MXINT8) {
+                            bulk_g2s(base, a.upper_cm + col * 32, (uint32_t)cv * 32, bar);      // the int8 code plane
+                        } else {
+                            bulk_g2s(base, a.upper_cm + col * 16, (uint32_t)cv * 16, bar);
+                            bulk_g2s(base + OFF_SH, a.shared_cm + col * 8, (uint32_t)cv * 8, bar);
+                        }
+                        bulk_g2s(base + OFF_SC, a.scale_exp + col, (uint32_t)cv, bar);
                     }
-                    bulk_g2s(base + OFF_SC, a.scale_exp + col, (uint32_t)cv, bar);
-                    if (!stage_here)
+                    if (!stage_here && (part & 2))
                         bulk_g2s(base + OFF_X, a.xprep + (int64_t)(b0 + j) * PASSES * GM_XREC, (uint32_t)(PASSES * GM_XREC), bar);
                 }
             }
         };
-        int pre = 0;
-        if constexpr (INK) {
-            // The first ring-full of weights goes out at once; the whole warp then helps with the records (the
-            // CTA-wide barrier at the end of that round orders them before the consumers' reads).
-            float inv_rms[GM_MP] = {1.0f, 1.0f, 1.0f, 1.0f};
-            pre = min(sch.stages, n_iter);
-            if (inject) pre = min(pre, a.skip_stage);
-            if (lane == 0) {
-                for (int it = 0; it < pre; ++it) {
-                    issue(ci, bi, it);
-                    if (++bi == sch.nb) { bi = 0; ++ci; }
-                }
+        int pre = min(sch.stages, n_iter);
+        if (inject) pre = min(pre, a.skip_stage);
+        if (!a.early) chain_wait();
+        if (lane == 0) {
+            int cj = ci, bj = bi;
+            for (int it = 0; it < pre; ++it) {
+                issue(cj, bj, it, 1);
+                if (++bj == sch.nb) { bj = 0; ++cj; }
             }
-            gemv_stage_start<KB>(a, smem_all, n_iter, n_lo, K, norm_red, inv_rms);
-            issued = pre;
-            s = pre;
-            if (s == sch.stages) { s = 0; ph ^= 1u; }
         }
+        MSAQ_TR(1, 1, lane == 0);
+        if (a.early) chain_wait();
+        MSAQ_TR(1, 2, lane == 0);
+        if constexpr (INK) {
+            // the whole warp helps with the records (the CTA-wide barrier at the end of that round orders them
+            // before the consumers' reads)
+            float inv_rms[GM_MP] = {1.0f, 1.0f, 1.0f, 1.0f};
+            gemv_stage_start<KB>(a, smem_all, n_iter, n_lo, K, norm_red, inv_rms);
+        }
+        if (lane == 0) {
+            for (int it = 0; it < pre; ++it) {
+                if (!stage_here) issue(ci, bi, it, 2);
+                if (++bi == sch.nb) { bi = 0; ++ci; }
+            }
+        }
+        issued = pre;
+        s = pre;
+        if (s == sch.stages) { s = 0; ph ^= 1u; }
         if (lane == 0) {
             for (int it = pre; it < n_iter; ++it) {
                 if (inject && it == a.skip_stage) break;          // the consumers' wait for this stage runs out
@@ -614,7 +662,7 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
                     break;
                 }
                 ++issued;
-                issue(ci, bi, s);
+                issue(ci, bi, s, 3);
                 if (++bi == sch.nb) { bi = 0; ++ci; }
                 if (++s == sch.stages) { s = 0; ph ^= 1u; }
             }
@@ -632,6 +680,7 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
         float inv_rms[GM_MP] = {1.0f, 1.0f, 1.0f, 1.0f};
         gemv_stage_start<KB>(a, smem_all, n_iter, n_lo, K, norm_red, inv_rms);
     }
+    MSAQ_TR(1, 3, tid == 0);
     const int g = lane >> 2, t = lane & 3, h = t >> 1, odd = t & 1;
     const int r0 = warp * 16 + g;                            // group-local columns r0 and r0 + 8
     const uint32_t sel = odd ? 0x7531u : 0x6420u;            // bytes {odd, 2+odd} of both upper words
@@ -664,6 +713,7 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
             report_wait_failure(a.status, (int)a.tag, a.sticky, WAIT_FAIL_GEMV_MMA);
             aborted = true;
         }
+        MSAQ_TR(1, 4, tid == 0 && it == 0);
         const int cv = min(TC, a.OUT - c * TC);
         if (!aborted) {
             const int nblk = min(KB, a.NB - blk * KB);                      // `blk` counts units within the tile
@@ -692,6 +742,7 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_empty[s]));
         if (++s == sch.stages) { s = 0; ph ^= 1u; }
+        MSAQ_TR(1, 5, tid == 0 && it == n_iter - 1);
 
         // ---- end of this CTA's run over tile c: publish the partial, maybe finish the tile ----
         // Each warp owns 16 columns of every 128-column group of the tile, so the hand-off is
@@ -801,6 +852,7 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
         }
         if (++blk == sch.nb) { blk = 0; ++c; }
     }
+    MSAQ_TR(1, 6, tid == 0);
 }
 
 }  // namespace msaq

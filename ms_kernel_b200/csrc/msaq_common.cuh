@@ -48,6 +48,7 @@ int sm_count();               // SM count of the current device (cached per devi
 int require_sm100();          // MSAQ_OK or MSAQ_ERR_DEVICE
 bool option_chained_launch(); // kernels are launched with programmatic stream serialisation
 bool option_tensor_memory();  // batched GEMVs of 9 rows and more run on tcgen05 with tensor-memory accumulators
+bool option_early_weights();   // MSAQ_OPT_EARLY_WEIGHTS: weights are fetched before the wait on the kernel in front
 bool option_inkernel_staging(); // GEMVs of up to four rows stage their activations inside the main kernel
 uint32_t next_call_tag();     // a process-wide 31-bit sequence number, never 0: tags a call's counters and status word
 unsigned option_wait_polls(); // poll limit of the bounded mbarrier waits
@@ -57,8 +58,17 @@ int* sticky_status();         // device address of the per-device status word on
 // Launch `kernel` so that it may begin while the previous kernel in the stream drains (see
 // chain_wait / chain_release): every kernel of this library executes chain_wait() before it
 // touches memory another kernel produces or consumes.
+// An SM holds thread blocks of two kernels at once only under one split of its L1 / shared memory.  The streaming
+// kernels need the largest shared-memory share, so with MSAQ_OPT_EARLY_WEIGHTS every kernel of the chain asks for
+// it: otherwise the blocks of a GEMV launched early behind a small kernel (activation staging, cache append,
+// residual add) could not start -- and begin fetching their weights -- until the small kernel had left every SM
+// (measured with per-block time stamps: without it the GEMV's first block starts when the staging kernel's last
+// block exits; with it 0.9 us after the staging kernel starts).
+void prefer_max_shared(const void* kernel);      // once per (kernel, device), only while the option is on
+
 template <typename... P, typename... A>
 inline cudaError_t launch_chained(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A&&... args) {
+    prefer_max_shared(reinterpret_cast<const void*>(kernel));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;

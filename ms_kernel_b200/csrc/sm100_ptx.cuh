@@ -100,6 +100,14 @@ __device__ __forceinline__ void mma_s8_16832_z(int (&d)[4], const uint32_t (&a)[
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "r"(0));
 }
 
+// Same with the accumulator input {0, c, 0, c}: a per-thread constant added to the odd result columns for free.
+__device__ __forceinline__ void mma_s8_16832_c(int (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2], int c) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "r"(0), "r"(c));
+}
+
 // Shared-memory loads with a register base and a compile-time byte offset, so
 // that one address register per plane serves a whole stage.
 template <int OFF>

@@ -32,6 +32,8 @@ def available() -> bool:
 PRO_NONE, PRO_RMSNORM, PRO_SILU_MUL, PRO_ADD_RMSNORM = 0, 1, 2, 3   # include/msaq_b200.h: MSAQ_PRO_*
 OPT_TENSOR_MEMORY = 2    # batched GEMVs of 9+ rows on tcgen05 / tensor memory (default on)
 OPT_CHAINED_LAUNCH = 1   # overlap each kernel's launch and prologue with the tail of the one before it (default on)
+OPT_EARLY_WEIGHTS = 6    # GEMVs fetch weights before waiting for the kernel in front (default off: the caller vouches
+                         # that the weight planes are complete, not being written by work still in flight)
 
 
 def set_option(option: int, value: bool) -> None:

@@ -212,3 +212,33 @@ def test_gemv_graph_replay_on_a_dirty_workspace(rng):
             assert np.array_equal(o, outs[0])
         _check(y.float().cpu().numpy(), outs[0], ref)
         del g
+
+
+@pytest.mark.parametrize("OUT,K,M", [(4096, 4096, 1), (2560, 8192, 1), (8192, 2048, 4), (1024, 512, 2)])
+def test_early_weights_option_changes_no_bit(rng, OUT, K, M):
+    """MSAQ_OPT_EARLY_WEIGHTS moves the first weight copies in front of the wait for the preceding kernel; with the
+    weights complete before the call (a synchronise after packing: the option's contract) every output bit is the
+    same, plain and with a fused prologue, back to back in one stream."""
+    from ms_kernel_b200 import _lib, ops, pack
+    dev = torch.device("cuda")
+    g = torch.Generator(device="cuda").manual_seed(OUT + K + M)
+    W = (torch.randn((OUT, K), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    lin = ops.PackedLinear(pack.pack_weight(W, 4, 2, device=dev), dev)
+    x = torch.randn((M, K), generator=g, device="cuda").to(torch.bfloat16)
+    torch.cuda.synchronize()
+    L = _lib.lib()
+    outs = []
+    for early in (0, 1):
+        assert L.msaq_set_option(6, early) == 0
+        try:
+            ys = []
+            for _ in range(3):                                   # back to back: each call runs behind the one before
+                ys.append(lin.fwd(x))
+                ys.append(lin.fwd_fused(x, ops.PRO_RMSNORM))
+            torch.cuda.synchronize()
+        finally:
+            L.msaq_set_option(6, 0)
+        outs.append(ys)
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a, b)
+    assert L.msaq_get_option(6) == 0
