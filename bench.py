@@ -314,7 +314,7 @@ def run_ours(args):
         if mode == "push":
             try:
                 ar = tp.PeerExchange(dist.group.WORLD, B * shape.hidden, dev)
-                state["exchange"] = "msaq_peer_exchange: one push kernel over NVLink peer memory (plain peer stores, one flag wait)"
+                state["exchange"] = "msaq_peer_exchange: one push kernel over NVLink peer memory (plain peer stores of data words that carry the sequence number; residual add fused)"
                 return ar
             except Exception as e:
                 state["exchange_note"] = "push exchange unavailable: %s" % str(e).splitlines()[0][:80]

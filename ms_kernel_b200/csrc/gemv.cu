@@ -271,7 +271,7 @@ int run_mma(const __nv_bfloat16* X, const Prologue& pro, const int8_t* se, const
         GemvMmaArgs a{se, up, sh, xprep, partial, counters, status, sticky_status(), static_cast<__nv_bfloat16*>(Y), Yf,
                       (int)m0, rows, (int)OUT, (int)NB, sch, option_wait_polls(), option_test_skip_stage(),
                       in_kernel ? pro.mode : -1, xa.X, xa.R, xa.h_out, (int)ldx, pro.r_is_f32, pro.eps, tag,
-                      in_kernel ? (int)table : 0, 0, option_early_weights() ? 1 : 0};
+                      in_kernel ? (int)table : 0, 0, msaq_get_option(MSAQ_OPT_EARLY_WEIGHTS)};
         // the ring depth was planned for the first tile's pass count; a last, smaller tile may go deeper but need not
         int rc;
         if (fmt == GF_MXINT8) {
