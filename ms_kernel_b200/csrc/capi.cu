@@ -157,7 +157,7 @@ extern "C" int msaq_set_option(int option, int value) {
             return MSAQ_OK;
         case MSAQ_OPT_TEST_SKIP_STAGE: msaq::g_opt_skip.store(value < 0 ? -1 : value, std::memory_order_relaxed); return MSAQ_OK;
         case MSAQ_OPT_INKERNEL_STAGING: msaq::g_opt_inkernel.store(value ? 1 : 0, std::memory_order_relaxed); return MSAQ_OK;
-        case MSAQ_OPT_EARLY_WEIGHTS: msaq::g_opt_early.store(value, std::memory_order_relaxed); return MSAQ_OK;
+        case MSAQ_OPT_EARLY_WEIGHTS: msaq::g_opt_early.store(value ? 1 : 0, std::memory_order_relaxed); return MSAQ_OK;
         default: return msaq::fail(MSAQ_ERR_ARG, "unknown option %d", option);
     }
 }
