@@ -311,10 +311,14 @@ def run_ours(args):
         if world == 1:
             return None
         mode = os.environ.get("MSAQ_BENCH_EXCHANGE", "push")
-        if mode == "push":
+        if mode in ("push", "push_separate"):
             try:
-                ar = tp.PeerExchange(dist.group.WORLD, B * shape.hidden, dev)
-                state["exchange"] = "msaq_peer_exchange: one push kernel over NVLink peer memory (plain peer stores of data words that carry the sequence number; residual add fused)"
+                ar = tp.PeerExchange(dist.group.WORLD, B * shape.hidden, dev, fused=(mode == "push"))
+                state["exchange"] = ("push over NVLink peer memory, plain peer stores of data words that carry the sequence "
+                                     "number: " + ("issued by the O / down GEMVs' finishing warps tile by tile "
+                                                   "(msaq_wonly_gemv_fused_push), then one wait-and-add kernel with the "
+                                                   "residual add (msaq_peer_exchange)" if mode == "push" else
+                                                   "one kernel after the GEMV (msaq_peer_exchange)"))
                 return ar
             except Exception as e:
                 state["exchange_note"] = "push exchange unavailable: %s" % str(e).splitlines()[0][:80]

@@ -341,10 +341,28 @@ int msaq_kv_decode_attention_rope(const void* q,
  *   parity        0, 1, 0, 1, ... over the successive exchanges of a process (every rank the same sequence)
  * All ranks must call it the same number of times with the same n.  A rank whose peers do not arrive within the
  * poll limit (MSAQ_OPT_WAIT_POLLS) writes NaN and sets MSAQ_STATUS_PEER_TIMEOUT; it never hangs.
+ * partial == NULL: the partial sums are in the slots already -- msaq_wonly_gemv_fused_push put them there -- and the
+ * call only waits, adds and writes.
  */
 size_t msaq_peer_exchange_bytes(int world, int64_t n);
 int msaq_peer_exchange(const float* partial, const void* residual, void* out, void* const* peer_bufs, int rank, int world,
                        int64_t n, int parity, void* stream);
+
+/*
+ * msaq_wonly_gemv_fused with the exchange's push inside, for the row-parallel projections (O, down) of a
+ * tensor-parallel layer: the warp that finishes a tile of outputs stores them straight into this rank's slot of
+ * every rank's exchange buffer (its own included) instead of into local memory, so the partial sums cross NVLink
+ * tile by tile while the GEMV still runs; msaq_peer_exchange(partial = NULL, ...) with the same parity and
+ * n = M * OUT then completes the sum.  Same arguments as msaq_wonly_gemv_fused without y / y_f32, same peer buffers
+ * and parity rule as msaq_peer_exchange.  Built into the integer-MMA kernel only (u = 4, gs = 2, M <= 8, aligned
+ * column-major planes, M * OUT a multiple of 4): MSAQ_ERR_UNSUPPORTED otherwise, and the caller runs the two calls
+ * separately.
+ */
+int msaq_wonly_gemv_fused_push(const void* x, int prologue, const void* addend, int addend_is_f32, float eps,
+                               void* h_out, const int8_t* scale_exp, const uint8_t* upper_cm,
+                               const uint8_t* shared_cm, int64_t M, int64_t OUT, int64_t NB, int u, int gs,
+                               void* const* peer_bufs, int rank, int world, int parity,
+                               void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------- W+A decode, prefill vehicle -- */
 

@@ -77,19 +77,19 @@ MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB, int fmt = GF_MSAQ_U4) {
     return p;
 }
 
-template <int PASSES, int TC, int KB, bool INK, int FMT = GF_MSAQ_U4>
+template <int PASSES, int TC, int KB, bool INK, int FMT = GF_MSAQ_U4, bool PUSH = false>
 int launch_mma_ink(const GemvMmaArgs& a, cudaStream_t st) {
     static int configured[64] = {};                      // largest dynamic smem size set per device
     const int smem = a.sch.stages * KB * gm_stage_bytes(TC, PASSES, FMT) + a.table_bytes;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && configured[dev] < smem) {
-        if (cudaFuncSetAttribute(gemv_u4gs2_mma_kernel<PASSES, TC, KB, INK, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(gemv_u4gs2_mma_kernel<PASSES, TC, KB, INK, FMT, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  smem) != cudaSuccess)
             return fail(MSAQ_ERR_CUDA, "cannot reserve %d bytes of shared memory", smem);
         configured[dev] = smem;
     }
-    launch_chained(gemv_u4gs2_mma_kernel<PASSES, TC, KB, INK, FMT>, dim3(a.sch.grid), dim3(GM_THREADS), smem, st, a);
+    launch_chained(gemv_u4gs2_mma_kernel<PASSES, TC, KB, INK, FMT, PUSH>, dim3(a.sch.grid), dim3(GM_THREADS), smem, st, a);
     count_launch();
     return check_launch(FMT == GF_MXINT8 ? "gemv_mxint8_mma" : "gemv_u4gs2_mma");
 }
@@ -106,6 +106,15 @@ int launch_mma(const GemvMmaArgs& a, cudaStream_t st) {
     if constexpr (TC < GM_GROUP) {
         return fail(MSAQ_ERR_ARG, "tile narrower than a column group");
     } else {
+        if constexpr (PASSES <= 2) {                       // the push variant serves up to eight rows
+            if (a.push.world) {
+                if constexpr (PASSES == 1) {
+                    if (a.xmode >= 0) return launch_mma_ink<PASSES, TC, KB, true, GF_MSAQ_U4, true>(a, st);
+                }
+                return launch_mma_ink<PASSES, TC, KB, false, GF_MSAQ_U4, true>(a, st);
+            }
+        }
+        if (a.push.world) return fail(MSAQ_ERR_UNSUPPORTED, "the push variant serves up to eight rows");
         if constexpr (PASSES == 1) {
             if (a.xmode >= 0) return launch_mma_ink<PASSES, TC, KB, true>(a, st);
         }
@@ -224,7 +233,8 @@ int launch_xprep(const XprepArgs& xa, int mode, unsigned grid, cudaStream_t st) 
 }
 
 int run_mma(const __nv_bfloat16* X, const Prologue& pro, const int8_t* se, const uint8_t* up, const uint8_t* sh,
-            void* Y, float* Yf, int64_t M, int64_t OUT, int64_t NB, void* ws, cudaStream_t st, int fmt = GF_MSAQ_U4) {
+            void* Y, float* Yf, int64_t M, int64_t OUT, int64_t NB, void* ws, cudaStream_t st, int fmt = GF_MSAQ_U4,
+            const PeerPush* push = nullptr) {
     const MmaPlan p = plan_mma(M, OUT, NB, fmt);
     uint8_t* base = static_cast<uint8_t*>(ws);
     int* status = reinterpret_cast<int*>(base);
@@ -271,7 +281,7 @@ int run_mma(const __nv_bfloat16* X, const Prologue& pro, const int8_t* se, const
         GemvMmaArgs a{se, up, sh, xprep, partial, counters, status, sticky_status(), static_cast<__nv_bfloat16*>(Y), Yf,
                       (int)m0, rows, (int)OUT, (int)NB, sch, option_wait_polls(), option_test_skip_stage(),
                       in_kernel ? pro.mode : -1, xa.X, xa.R, xa.h_out, (int)ldx, pro.r_is_f32, pro.eps, tag,
-                      in_kernel ? (int)table : 0, 0, msaq_get_option(MSAQ_OPT_EARLY_WEIGHTS)};
+                      in_kernel ? (int)table : 0, 0, option_early_weights() ? 1 : 0, push ? *push : PeerPush{}};
         // the ring depth was planned for the first tile's pass count; a last, smaller tile may go deeper but need not
         int rc;
         if (fmt == GF_MXINT8) {
@@ -432,6 +442,42 @@ extern "C" int msaq_wonly_gemv_fused(const void* x, int prologue, const void* ad
     }
     if (rc) return rc;
     return gemv_dispatch(tmp, scale_exp, upper_cm, shared_cm, y, y_f32, M, OUT, NB, u, gs, true, workspace, g, stream);
+}
+
+// ---- GEMV of a row-parallel projection with the exchange's push inside --------------------
+extern "C" int msaq_wonly_gemv_fused_push(const void* x, int prologue, const void* addend, int addend_is_f32, float eps,
+                                          void* h_out, const int8_t* scale_exp, const uint8_t* upper_cm,
+                                          const uint8_t* shared_cm, int64_t M, int64_t OUT, int64_t NB, int u, int gs,
+                                          void* const* peer_bufs, int rank, int world, int parity, void* workspace,
+                                          size_t workspace_bytes, void* stream) {
+    if (prologue < MSAQ_PRO_NONE || prologue > MSAQ_PRO_ADD_RMSNORM) return fail(MSAQ_ERR_ARG, "unknown prologue %d", prologue);
+    if (!x || !scale_exp || !upper_cm || !shared_cm || !peer_bufs) return fail(MSAQ_ERR_ARG, "null pointer");
+    if (prologue == MSAQ_PRO_ADD_RMSNORM && (!addend || !h_out))
+        return fail(MSAQ_ERR_ARG, "the add+rmsnorm prologue needs an addend and h_out");
+    if (M <= 0 || OUT <= 0 || NB <= 0) return fail(MSAQ_ERR_ARG, "M, OUT and NB must be positive");
+    if (world < 2 || world > 8 || rank < 0 || rank >= world) return fail(MSAQ_ERR_ARG, "world must be 2..8 and rank inside it");
+    if (parity != 0 && parity != 1) return fail(MSAQ_ERR_ARG, "parity must be 0 or 1");
+    if (M > INT32_MAX || OUT > INT32_MAX || NB * BLOCK > INT32_MAX / 2) return fail(MSAQ_ERR_ARG, "size exceeds 2^31");
+    if (int rc = require_sm100()) return rc;
+    const bool vec_ok = !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(addend)) & 15);
+    if (M >= GU_MIN_M || (M * OUT) % 4 || !vec_ok || !workspace ||
+        !mma_usable(scale_exp, upper_cm, shared_cm, workspace, OUT, u, gs, true))
+        return fail(MSAQ_ERR_UNSUPPORTED, "the push is built into the integer-MMA GEMV only (u=4, gs=2, up to 8 rows, aligned "
+                                          "column-major planes): run the GEMV and msaq_peer_exchange separately");
+    const size_t need = msaq_wonly_gemv_fused_workspace(M, OUT, NB, u, gs);
+    if (workspace_bytes < need) return fail(MSAQ_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    PeerPush push{};
+    for (int r = 0; r < world; ++r) {
+        if (!peer_bufs[r] || (reinterpret_cast<uintptr_t>(peer_bufs[r]) & 15)) return fail(MSAQ_ERR_ARG, "bad peer buffer %d", r);
+        push.buf[r] = static_cast<float*>(peer_bufs[r]);
+    }
+    push.n = M * OUT;
+    push.world = world;
+    push.rank = rank;
+    push.parity = parity;
+    const Prologue pro{prologue, addend, addend_is_f32, h_out, eps};
+    return run_mma(static_cast<const __nv_bfloat16*>(x), pro, scale_exp, upper_cm, shared_cm, nullptr, nullptr, M, OUT, NB,
+                   workspace, static_cast<cudaStream_t>(stream), GF_MSAQ_U4, &push);
 }
 
 // ---- GEMV without any allocation ---------------------------------------------------------

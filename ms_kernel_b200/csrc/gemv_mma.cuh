@@ -252,6 +252,26 @@ gemv_xprep_kernel(const XprepArgs a) {
 }
 
 // ---- main kernel ------------------------------------------------------------------
+// Tensor-parallel row-parallel projections (O, down): instead of writing its finished outputs to local memory, the
+// warp that completes a tile stores them straight into this rank's slot of every rank's exchange buffer (its own
+// included), each float as an 8-byte word {x, seq} -- the layout and sequence number of peer_exchange.cu, whose
+// receiving kernel then only waits and adds.  The partial sums leave tile by tile while the GEMV still runs.
+struct PeerPush {
+    float* buf[8];           // buf[r]: rank r's exchange memory as mapped into this process
+    long long n;             // floats per slot (rows * OUT)
+    int world, rank, parity; // world == 0: no push, ordinary outputs
+};
+__device__ __forceinline__ uint32_t gemv_push_seq(const PeerPush& p) {
+    const unsigned int* ctl = reinterpret_cast<const unsigned int*>(p.buf[p.rank] + 4 * (long long)p.world * p.n);
+    return *reinterpret_cast<const volatile unsigned int*>(ctl + p.parity) + 1u;
+}
+__device__ __forceinline__ void gemv_push(const PeerPush& p, long long idx, float v, uint32_t seq) {
+    const long long off = (((long long)p.parity * p.world + p.rank) * p.n + idx) * 2;
+    for (int r = 0; r < p.world; ++r)
+        // weak stores: each 8-byte word validates itself, so their order does not matter
+        asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(p.buf[r] + off), "r"(__float_as_uint(v)), "r"(seq) : "memory");
+}
+
 struct GemvMmaArgs {
     const int8_t* scale_exp;
     const uint8_t* upper_cm;
@@ -282,6 +302,7 @@ struct GemvMmaArgs {
     int table_bytes;         // shared memory in front of the ring that holds the in-kernel record table
     int natural;             // in-kernel records in natural element order (see XprepArgs)
     int early;               // first ring-full of weights goes out before the wait on the kernel in front
+    PeerPush push;
 };
 
 // Sums of squares of the launch's rows (of X, or of bf16(X + R) for XP_ADD_NORM) by all threads of the
@@ -549,7 +570,9 @@ __device__ __forceinline__ void gemv_stage_start(const GemvMmaArgs& a, uint8_t* 
 // KB = K blocks per ring stage (per unit).  Two halve the barrier hand-offs per byte where the tile
 // cannot get wider (few column tiles, many K blocks).
 // INK = the activation records come from this CTA's own table (in-kernel staging, PASSES == 1 only).
-template <int PASSES, int TC, int KB, bool INK = false, int FMT = GF_MSAQ_U4>
+// PUSH = the finished outputs go into the ranks' exchange buffers (PeerPush) instead of local memory; a variant of
+// its own so that the ordinary kernel's registers stay as they are.
+template <int PASSES, int TC, int KB, bool INK = false, int FMT = GF_MSAQ_U4, bool PUSH = false>
 __global__ void __launch_bounds__(GM_THREADS, GM_CTAS_PER_SM)
 gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
     static_assert(!INK || PASSES == 1, "in-kernel staging serves launches of up to four rows");
@@ -768,6 +791,8 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
             }
             if (nq > 0) {
                 if (nslots == 1) {
+                    uint32_t seq = 0u;
+                    if constexpr (PUSH) seq = gemv_push_seq(a.push);
 #pragma unroll
                     for (int q = 0; q < GROUPS; ++q) {
                         if (q < nq) {
@@ -776,9 +801,14 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
                                 const int m = p * GM_MP + t;
                                 if (m < a.rows) {
                                     const int64_t o = (int64_t)(a.m0 + m) * a.OUT + o0 + q * GM_GROUP + r0;
-                                    a.y[o] = __float2bfloat16_rn(acc[q][p][0]);
-                                    a.y[o + 8] = __float2bfloat16_rn(acc[q][p][1]);
-                                    if (yf) { yf[o] = acc[q][p][0]; yf[o + 8] = acc[q][p][1]; }
+                                    if constexpr (PUSH) {
+                                        gemv_push(a.push, o, acc[q][p][0], seq);
+                                        gemv_push(a.push, o + 8, acc[q][p][1], seq);
+                                    } else {
+                                        a.y[o] = __float2bfloat16_rn(acc[q][p][0]);
+                                        a.y[o + 8] = __float2bfloat16_rn(acc[q][p][1]);
+                                        if (yf) { yf[o] = acc[q][p][0]; yf[o + 8] = acc[q][p][1]; }
+                                    }
                                 }
                             }
                         }
@@ -805,6 +835,8 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
                     if (arrived == (unsigned int)nslots) {
                         __threadfence();
                         const bool poison = __ldcg(a.status) == (int)a.tag;        // a wait gave up somewhere in this call
+                        uint32_t seq = 0u;
+                        if constexpr (PUSH) seq = gemv_push_seq(a.push);
                         const int ncol = nq * 16;
                         const int64_t sstride = (int64_t)a.rows * a.OUT;
                         const int total = a.rows * ncol;
@@ -839,11 +871,16 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
                             }
                             if (poison) sum0 = sum1 = __int_as_float(0x7FC00000);
                             const int64_t y0 = (int64_t)a.m0 * a.OUT + e0, y1 = (int64_t)a.m0 * a.OUT + e1;
-                            a.y[y0] = __float2bfloat16_rn(sum0);
-                            if (yf) yf[y0] = sum0;
-                            if (!single) {
-                                a.y[y1] = __float2bfloat16_rn(sum1);
-                                if (yf) yf[y1] = sum1;
+                            if constexpr (PUSH) {
+                                gemv_push(a.push, y0, sum0, seq);
+                                if (!single) gemv_push(a.push, y1, sum1, seq);
+                            } else {
+                                a.y[y0] = __float2bfloat16_rn(sum0);
+                                if (yf) yf[y0] = sum0;
+                                if (!single) {
+                                    a.y[y1] = __float2bfloat16_rn(sum1);
+                                    if (yf) yf[y1] = sum1;
+                                }
                             }
                         }
                         // back to zero at rest: the next call (or the next replay of this launch) counts from 0 again

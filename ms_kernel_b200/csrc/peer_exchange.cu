@@ -26,7 +26,8 @@ constexpr int PX_THREADS = 256;
 
 struct PeerArgs {
     float* buf[PX_MAX_WORLD];        // buf[r]: rank r's exchange memory as mapped into this process
-    const float* partial;            // this rank's contribution, [n]
+    const float* partial;            // this rank's contribution, [n]; null: it was pushed already (by the GEMV that
+                                     // produced it, msaq_wonly_gemv_fused_push), into this rank's own slot too
     const __nv_bfloat16* residual;   // optional: out = bf16(residual + sum)
     void* out;                       // fp32 [n], or bf16 [n] with a residual
     int* sticky;                     // the library's per-device status word
@@ -59,8 +60,9 @@ peer_exchange_kernel(const PeerArgs a) {
     const uint32_t seq = *reinterpret_cast<volatile unsigned int*>(ctl + a.parity) + 1u;
     const int64_t i0 = ((int64_t)blockIdx.x * PX_THREADS + threadIdx.x) * 4;
     if (i0 < a.n) {                                          // n is a multiple of 4
-        const float4 mine = *reinterpret_cast<const float4*>(a.partial + i0);
-        for (int r = 0; r < a.world; ++r) {                  // push: my slot in every peer's buffer of this parity
+        const bool pushed = a.partial == nullptr;
+        const float4 mine = pushed ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(a.partial + i0);
+        for (int r = 0; r < a.world && !pushed; ++r) {       // push: my slot in every peer's buffer of this parity
             if (r == a.rank) continue;
             float* dst = a.buf[r] + (((int64_t)a.parity * a.world + a.rank) * a.n + i0) * 2;
             px_store(dst, mine.x, mine.y, seq);
@@ -74,7 +76,7 @@ peer_exchange_kernel(const PeerArgs a) {
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int r = 0; r < a.world; ++r) {                  // rank order: the same sum on every rank
             float4 v = mine;
-            if (r != a.rank) {
+            if (r != a.rank || pushed) {
                 const float* src = a.buf[a.rank] + (((int64_t)a.parity * a.world + r) * a.n + i0) * 2;
                 bool got0 = false, got1 = false;
                 while (ok) {
@@ -125,13 +127,13 @@ extern "C" size_t msaq_peer_exchange_bytes(int world, int64_t n) {
 
 extern "C" int msaq_peer_exchange(const float* partial, const void* residual, void* out, void* const* peer_bufs, int rank,
                                   int world, int64_t n, int parity, void* stream) {
-    if (!partial || !out || !peer_bufs) return fail(MSAQ_ERR_ARG, "null pointer");
+    if (!out || !peer_bufs) return fail(MSAQ_ERR_ARG, "null pointer");
     if (world < 2 || world > PX_MAX_WORLD || rank < 0 || rank >= world)
         return fail(MSAQ_ERR_ARG, "world must be 2..%d and rank inside it", PX_MAX_WORLD);
     if (n <= 0 || n % 4) return fail(MSAQ_ERR_ARG, "n must be a positive multiple of 4");
     if (parity != 0 && parity != 1) return fail(MSAQ_ERR_ARG, "parity must be 0 or 1");
-    if ((reinterpret_cast<uintptr_t>(partial) | reinterpret_cast<uintptr_t>(out)) & 15)
-        return fail(MSAQ_ERR_ARG, "partial and out must be 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(partial) & 15) || (reinterpret_cast<uintptr_t>(out) & (residual ? 7 : 15)))
+        return fail(MSAQ_ERR_ARG, "partial and an fp32 out must be 16-byte aligned, a bf16 out 8-byte aligned");
     if (residual && (reinterpret_cast<uintptr_t>(residual) & 7)) return fail(MSAQ_ERR_ARG, "residual must be 8-byte aligned");
     PeerArgs a{};
     for (int r = 0; r < world; ++r) {

@@ -453,6 +453,54 @@ Tensor peer_exchange(const Tensor& partial, const c10::optional<Tensor>& residua
     return out;
 }
 
+// The row-parallel GEMV with the exchange's push inside (no output tensor: the partial sums land in the ranks'
+// exchange buffers), and the receiving half of the exchange: fp32 [M, OUT] sum, or bf16(residual + sum).
+void wonly_gemv_fused_push(const Tensor& x, int64_t prologue, double eps, const Tensor& s, const Tensor& up, const Tensor& sh,
+                           int64_t M, int64_t OUT, int64_t NB, int64_t u, int64_t gs, std::vector<int64_t> peer_ptrs,
+                           int64_t rank, int64_t parity) {
+    check_act(x, "x");
+    int64_t UB, SB;
+    fmt_sizes(u, gs, &UB, &SB);
+    TORCH_CHECK(M >= 1 && OUT >= 1 && NB >= 1, "M, OUT and NB must be positive");
+    TORCH_CHECK(prologue != MSAQ_PRO_ADD_RMSNORM, "the add+rmsnorm prologue belongs to column-parallel projections");
+    TORCH_CHECK(x.numel() == M * NB * 32 * (prologue == MSAQ_PRO_SILU_MUL ? 2 : 1), "x has ", x.numel(), " elements");
+    check_planes(s, up, sh, x, NB * OUT, UB, SB);
+    const int64_t world = (int64_t)peer_ptrs.size();
+    TORCH_CHECK(world >= 2 && world <= 8, "2 to 8 ranks");
+    void* bufs[8];
+    for (int64_t r = 0; r < world; ++r) bufs[r] = reinterpret_cast<void*>(peer_ptrs[r]);
+    c10::cuda::CUDAGuard guard(x.device());
+    const size_t wsb = msaq_wonly_gemv_fused_workspace(M, OUT, NB, (int)u, (int)gs);
+    Tensor ws = workspace(x, wsb);
+    check_rc(msaq_wonly_gemv_fused_push(x.data_ptr(), (int)prologue, nullptr, 0, (float)eps, nullptr, s.data_ptr<int8_t>(),
+                                        up.data_ptr<uint8_t>(), sh.data_ptr<uint8_t>(), M, OUT, NB, (int)u, (int)gs, bufs,
+                                        (int)rank, (int)world, (int)parity, ws.data_ptr(), wsb, stream_of(x)),
+             "wonly_gemv_fused_push");
+}
+
+Tensor peer_exchange_recv(const Tensor& like, const c10::optional<Tensor>& residual, std::vector<int64_t> peer_ptrs, int64_t rank,
+                          int64_t parity, int64_t M, int64_t OUT) {
+    TORCH_CHECK(like.is_cuda(), "like must be a CUDA tensor");
+    const int64_t world = (int64_t)peer_ptrs.size();
+    TORCH_CHECK(world >= 2 && world <= 8, "2 to 8 ranks");
+    void* bufs[8];
+    for (int64_t r = 0; r < world; ++r) bufs[r] = reinterpret_cast<void*>(peer_ptrs[r]);
+    c10::cuda::CUDAGuard guard(like.device());
+    Tensor out;
+    const void* res = nullptr;
+    if (residual.has_value()) {
+        check_act(*residual, "residual");
+        TORCH_CHECK(residual->numel() == M * OUT, "residual must have M * OUT elements");
+        out = at::empty_like(*residual);
+        res = residual->data_ptr();
+    } else {
+        out = at::empty({M, OUT}, like.options().dtype(at::kFloat));
+    }
+    check_rc(msaq_peer_exchange(nullptr, res, out.data_ptr(), bufs, (int)rank, (int)world, M * OUT, (int)parity, stream_of(like)),
+             "peer_exchange_recv");
+    return out;
+}
+
 // ---- W+A decode and the prefill vehicle (schemas of the reference, csrc/pybind.cpp:203-204,231-233,244-245) ----
 Tensor wa_gemv_impl(const Tensor& x, const Tensor& s, const Tensor& up, const Tensor& sh, int64_t M, int64_t OUT,
                     int64_t NB, int64_t u, int64_t gs, bool batched) {
@@ -738,6 +786,10 @@ TORCH_LIBRARY(msaq, m) {
     m.def("silu_mul(Tensor gate_up) -> Tensor", &silu_mul);
     m.def("add_residual(Tensor h, Tensor delta) -> Tensor", &add_residual);
     m.def("peer_exchange(Tensor partial, Tensor? residual, int[] peer_ptrs, int rank, int parity) -> Tensor", &peer_exchange);
+    m.def("wonly_gemv_fused_push(Tensor x, int prologue, float eps, Tensor scale_exp, Tensor upper_cm, Tensor shared_cm, int M, "
+          "int OUT, int NB, int u, int gs, int[] peer_ptrs, int rank, int parity) -> ()", &wonly_gemv_fused_push);
+    m.def("peer_exchange_recv(Tensor like, Tensor? residual, int[] peer_ptrs, int rank, int parity, int M, int OUT) -> Tensor",
+          &peer_exchange_recv);
     m.def("launch_count() -> int", &launch_count);
     m.def("set_option(int option, int value) -> ()", &set_option);
     m.def("get_option(int option) -> int", &get_option);

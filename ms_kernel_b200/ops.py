@@ -139,6 +139,20 @@ class PackedLinear:
                                     self.u, self.gs, bool(out_f32))
         return (out[0], out[1]) if prologue == PRO_ADD_RMSNORM else out[0]
 
+    def can_push(self, M):
+        """Whether fwd_push serves M rows of this linear (the integer-MMA GEMV's terms)."""
+        return self.u == 4 and self.gs == 2 and 1 <= M <= 8 and self.OUT % 16 == 0 and (M * self.OUT) % 4 == 0
+
+    def fwd_push(self, x, prologue, eps, peer_ptrs, rank, parity):
+        """The GEMV of a row-parallel (K-sharded) linear with the exchange's push inside: the fp32 partial sums
+        go straight from the kernel's finishing warps into every rank's exchange buffer (include/msaq_b200.h:
+        msaq_wonly_gemv_fused_push).  prologue: PRO_NONE, PRO_RMSNORM or PRO_SILU_MUL.  Returns nothing; the sum
+        comes out of the receiving half of the exchange (tp.PeerExchange.recv)."""
+        M = int(x.shape[0])
+        _OPS.wonly_gemv_fused_push(x.contiguous(), int(prologue), float(eps), self.scale_exp, self.upper_cm,
+                                   self.shared_cm, M, self.OUT, self.nb, self.u, self.gs, list(peer_ptrs), int(rank),
+                                   int(parity))
+
 
 class KVCache:
     """Packed K and V caches [B,Hkv,nb,Lcap,*] with append and attend.

@@ -127,6 +127,58 @@ def test_argument_checks():
     assert _lib.lib().msaq_peer_exchange_bytes(9, n) == 0
 
 
+@pytest.mark.parametrize("OUT,K,M,prologue", [(8192, 1024, 1, 0), (8192, 3584, 1, 2), (4096, 2048, 4, 0), (8192, 4096, 8, 2),
+                                              (1024, 256, 1, 0)])
+def test_gemv_with_the_push_inside(OUT, K, M, prologue):
+    """msaq_wonly_gemv_fused_push: the GEMV's finishing warps store the fp32 outputs as {x, seq} words into this rank's
+    slot of every rank's buffer.  One GPU, both "ranks'" buffers local; the other rank's push is played by the host,
+    then the receiving half adds up.  Bit-exact against the same GEMV's fp32 output."""
+    from ms_kernel_b200 import ops, pack
+    dev = torch.device("cuda", 0)
+    o = _ops()
+    g = torch.Generator(device="cuda").manual_seed(OUT + K + M)
+    W = (torch.randn((OUT, K), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    lin = ops.PackedLinear(pack.pack_weight(W, 4, 2, device=dev), dev)
+    assert lin.can_push(M) and not lin.can_push(9)
+    x = torch.randn((M, (2 if prologue == 2 else 1) * K), generator=g, device="cuda").to(torch.bfloat16)
+    want = lin.fwd_fused(x, prologue, None, 1e-5, True) if prologue else lin.fwd_f32(x)
+    world, rank, n = 2, 1, M * OUT
+    bufs = _bufs(world, n, dev)
+    ptrs = [b.data_ptr() for b in bufs]
+    other = torch.randn(n, generator=torch.Generator().manual_seed(5))
+    h = torch.randn((M, OUT), generator=g, device="cuda").to(torch.bfloat16)
+    for it, parity in enumerate((0, 1, 0)):
+        seq = it // 2 + 1
+        torch.cuda.synchronize()
+        lin.fwd_push(x, prologue, 1e-5, ptrs, rank, parity)
+        torch.cuda.synchronize()
+        for r in range(world):                               # landed in both buffers, every word with the sequence number
+            assert torch.equal(_slot(bufs[r], world, n, parity, rank).cpu(), _encode(want.reshape(-1).cpu(), seq))
+        _slot(bufs[rank], world, n, parity, 0).copy_(_encode(other, seq))       # the peer's push, played by the host
+        torch.cuda.synchronize()
+        res = h if it == 2 else None
+        got = o.peer_exchange_recv(x, res, ptrs, rank, parity, M, OUT)
+        torch.cuda.synchronize()
+        total = other.reshape(M, OUT) + want.cpu()           # rank order: rank 0 (the peer) first
+        if res is not None:
+            total = (h.float().cpu() + total).to(torch.bfloat16)
+        assert torch.equal(got.cpu(), total)
+        assert _ctl(bufs[rank], world, n).cpu()[parity] == seq
+    assert o.wait_status(True) == 0
+
+
+def test_push_refuses_what_the_mma_gemv_does_not_serve():
+    from ms_kernel_b200 import ops, pack
+    dev = torch.device("cuda", 0)
+    W = (torch.randn((256, 256), device="cuda") * 0.02).to(torch.bfloat16)
+    lin3 = ops.PackedLinear(pack.pack_weight(W, 3, 2, device=dev), dev)
+    assert not lin3.can_push(1)
+    bufs = _bufs(2, 256, dev)
+    x = torch.randn((1, 256), device="cuda").to(torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        lin3.fwd_push(x, 0, 1e-5, [b.data_ptr() for b in bufs], 0, 0)
+
+
 def _two_rank_worker(rank, world, port, q):
     try:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -150,6 +202,22 @@ def _two_rank_worker(rank, world, port, q):
             bad += int(not torch.equal(got.cpu(), want))
             got2 = ex.reduce_add(parts[rank].to(dev), h.to(dev))
             bad += int(not torch.equal(got2.cpu(), (h.float() + want).to(torch.bfloat16)))
+        # the two halves: a GEMV with the push inside, then the receiving half; against the partials all-gathered
+        from ms_kernel_b200 import ops, pack
+        gw = torch.Generator(device="cuda").manual_seed(100 + rank)
+        W = (torch.randn((n, 1024), generator=gw, device="cuda") * 0.02).to(torch.bfloat16)
+        lin = ops.PackedLinear(pack.pack_weight(W, 4, 2, device=dev), dev)
+        xa = torch.randn((1, 1024), generator=gw, device="cuda").to(torch.bfloat16)
+        mine = lin.fwd_f32(xa)
+        parts = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        want = parts[0].clone()
+        for r in range(1, world):
+            want += parts[r]
+        torch.cuda.synchronize()
+        for it in range(20):
+            got = ex.recv(ex.push_from(lin, xa))
+            bad += int(not torch.equal(got, want))
         # the same inside a CUDA graph, replayed
         x = torch.randn(n, generator=gens[rank]).to(dev)
         allx = [torch.zeros(n, device=dev) for _ in range(world)]
