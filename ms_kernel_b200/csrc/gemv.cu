@@ -335,7 +335,9 @@ int gemv_dispatch(const void* X, const int8_t* se, const uint8_t* up, const uint
                        !((reinterpret_cast<uintptr_t>(Y) | reinterpret_cast<uintptr_t>(Yf)) & 15);
     // u = 4 keeps up to eight rows on the integer-MMA kernel; the 5+3 and 6+2 bit formats have no such kernel
     if (tm_ok && (u != 4 || M >= GU_MIN_M)) return run_umma(x, se, up, sh, Y, Yf, M, OUT, NB, u, ws, st);
-    if (mma_usable(se, up, sh, ws, OUT, u, gs, cm))
+    // the integer-MMA kernel's finishing warps store four outputs at a time: 8-byte aligned bf16, 16-byte aligned fp32
+    const bool out_ok = !((reinterpret_cast<uintptr_t>(Y) & 7) | (reinterpret_cast<uintptr_t>(Yf) & 15));
+    if (mma_usable(se, up, sh, ws, OUT, u, gs, cm) && out_ok)
         return run_mma(x, Prologue{XP_PLAIN, nullptr, 0, nullptr, 0.0f}, se, up, sh, Y, Yf, M, OUT, NB, ws, st);
 
     return gemv_run_generic(x, se, up, sh, Y, Yf, M, OUT, NB, f, cm, static_cast<uint8_t*>(ws) + WS_CTL_BYTES, st);
@@ -422,7 +424,8 @@ extern "C" int msaq_wonly_gemv_fused(const void* x, int prologue, const void* ad
                     workspace ? workspace_bytes : (size_t)0);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int64_t K = NB * BLOCK;
-    const bool vec_ok = !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(addend)) & 15);
+    const bool vec_ok = !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(addend)) & 15) &&
+                        !((reinterpret_cast<uintptr_t>(y) & 7) | (reinterpret_cast<uintptr_t>(y_f32) & 15));
     // fused staging belongs to the integer-MMA kernel; batches the tensor-memory kernel takes run the glue separately
     const bool small = M < GU_MIN_M || !option_tensor_memory();
     if (mma_usable(scale_exp, upper_cm, shared_cm, workspace, OUT, u, gs, true) && vec_ok && small) {
@@ -538,8 +541,10 @@ extern "C" int msaq_mxint8_gemv_batched_wide(const void* X, const int8_t* scale_
     if (M <= 0 || OUT <= 0 || NB <= 0) return fail(MSAQ_ERR_ARG, "M, OUT and NB must be positive");
     if (M > INT32_MAX || OUT > INT32_MAX || NB * BLOCK > INT32_MAX) return fail(MSAQ_ERR_ARG, "size exceeds 2^31");
     if (OUT % 16) return fail(MSAQ_ERR_UNSUPPORTED, "the MXINT8 GEMV needs OUT to be a multiple of 16");
-    if ((reinterpret_cast<uintptr_t>(scale_exp) | reinterpret_cast<uintptr_t>(qweight_cm) | reinterpret_cast<uintptr_t>(workspace)) & 15)
-        return fail(MSAQ_ERR_ARG, "planes and workspace must be 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(scale_exp) | reinterpret_cast<uintptr_t>(qweight_cm) | reinterpret_cast<uintptr_t>(workspace) |
+         reinterpret_cast<uintptr_t>(Y_f32)) & 15)
+        return fail(MSAQ_ERR_ARG, "planes, workspace and Y_f32 must be 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(Y) & 7) return fail(MSAQ_ERR_ARG, "Y must be 8-byte aligned");
     if (int rc = require_sm100()) return rc;
     const size_t need = msaq_mxint8_gemv_workspace(M, OUT, NB);
     if (!workspace || workspace_bytes < need)

@@ -837,49 +837,54 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
                         const bool poison = __ldcg(a.status) == (int)a.tag;        // a wait gave up somewhere in this call
                         uint32_t seq = 0u;
                         if constexpr (PUSH) seq = gemv_push_seq(a.push);
-                        const int ncol = nq * 16;
-                        const int64_t sstride = (int64_t)a.rows * a.OUT;
-                        const int total = a.rows * ncol;
-                        // Sixteen loads in flight per lane, summed in slot order: two outputs x eight slots, or --
-                        // when this lane has a single output left -- sixteen slots of that one output.
-                        for (int i0 = lane; i0 < total; i0 += 64) {
-                            const bool single = i0 + 32 >= total;
-                            const int i1 = single ? i0 : i0 + 32;
-                            const int m0 = i0 / ncol, j0 = i0 % ncol, m1 = i1 / ncol, j1 = i1 % ncol;
-                            const int64_t e0 = (int64_t)m0 * a.OUT + o0 + (j0 >> 4) * GM_GROUP + warp * 16 + (j0 & 15);
-                            const int64_t e1 = (int64_t)m1 * a.OUT + o0 + (j1 >> 4) * GM_GROUP + warp * 16 + (j1 & 15);
-                            const float* s0 = a.partial + e0;
-                            const float* s1 = a.partial + e1 + (single ? 8 * sstride : 0);
-                            const int step = single ? 16 : 8, lim1 = single ? nslots - 8 : nslots;
-                            float sum0 = 0.0f, sum1 = 0.0f;
-                            for (int k0 = 0; k0 < nslots; k0 += step) {
-                                float v[8], w[8];
+                        // An item is four adjacent outputs (row m, group q, quad of the warp's 16 columns); 32 / S items are
+                        // in hand at a time, S lanes to an item, lane `part` adding the slots part, part + S, ... with eight
+                        // 16-byte loads in flight, then the S sums are added across lanes: one or two rounds of load latency
+                        // where one output per lane and eight scalar loads in flight took four to eight.  The order of the
+                        // additions depends on the shape alone, so the sum is the same bits on every run.
+                        const int64_t sstride4 = (int64_t)a.rows * a.OUT / 4;           // slot stride in float4 (OUT % 16 == 0)
+                        const int items = a.rows * nq * 4;
+                        int S = 1;
+                        while (S < 8 && items * S * 2 <= 32) S *= 2;
+                        const int per = 32 / S;
+                        for (int base = 0; base < items; base += per) {
+                            const int it = base + lane / S, part = lane % S;
+                            const bool live = it < items;
+                            const int m = live ? it / (nq * 4) : 0, rem = live ? it % (nq * 4) : 0;
+                            const int64_t e = (int64_t)m * a.OUT + o0 + (rem >> 2) * GM_GROUP + warp * 16 + (rem & 3) * 4;
+                            const float4* src = reinterpret_cast<const float4*>(a.partial + e);
+                            float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                            if (live) {
+                                for (int k0 = part; k0 < nslots; k0 += 8 * S) {
+                                    float4 v[8];
 #pragma unroll
-                                for (int k = 0; k < 8; ++k) {
-                                    v[k] = (k0 + k < nslots) ? __ldcg(s0 + (k0 + k) * sstride) : 0.0f;
-                                    w[k] = (k0 + k < lim1) ? __ldcg(s1 + (k0 + k) * sstride) : 0.0f;
-                                }
+                                    for (int k = 0; k < 8; ++k)
+                                        v[k] = (k0 + k * S < nslots) ? __ldcg(src + (k0 + k * S) * sstride4) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-                                for (int k = 0; k < 8; ++k) sum0 += v[k];
-                                if (single) {
-#pragma unroll
-                                    for (int k = 0; k < 8; ++k) sum0 += w[k];
-                                } else {
-#pragma unroll
-                                    for (int k = 0; k < 8; ++k) sum1 += w[k];
+                                    for (int k = 0; k < 8; ++k) { sum.x += v[k].x; sum.y += v[k].y; sum.z += v[k].z; sum.w += v[k].w; }
                                 }
                             }
-                            if (poison) sum0 = sum1 = __int_as_float(0x7FC00000);
-                            const int64_t y0 = (int64_t)a.m0 * a.OUT + e0, y1 = (int64_t)a.m0 * a.OUT + e1;
-                            if constexpr (PUSH) {
-                                gemv_push(a.push, y0, sum0, seq);
-                                if (!single) gemv_push(a.push, y1, sum1, seq);
-                            } else {
-                                a.y[y0] = __float2bfloat16_rn(sum0);
-                                if (yf) yf[y0] = sum0;
-                                if (!single) {
-                                    a.y[y1] = __float2bfloat16_rn(sum1);
-                                    if (yf) yf[y1] = sum1;
+                            for (int o = S >> 1; o; o >>= 1) {
+                                sum.x += __shfl_xor_sync(0xffffffffu, sum.x, o);
+                                sum.y += __shfl_xor_sync(0xffffffffu, sum.y, o);
+                                sum.z += __shfl_xor_sync(0xffffffffu, sum.z, o);
+                                sum.w += __shfl_xor_sync(0xffffffffu, sum.w, o);
+                            }
+                            if (live && part == 0) {
+                                if (poison) sum.x = sum.y = sum.z = sum.w = __int_as_float(0x7FC00000);
+                                const int64_t y0 = (int64_t)a.m0 * a.OUT + e;
+                                if constexpr (PUSH) {
+                                    gemv_push(a.push, y0, sum.x, seq);
+                                    gemv_push(a.push, y0 + 1, sum.y, seq);
+                                    gemv_push(a.push, y0 + 2, sum.z, seq);
+                                    gemv_push(a.push, y0 + 3, sum.w, seq);
+                                } else {
+                                    __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x, sum.y), hi = __floats2bfloat162_rn(sum.z, sum.w);
+                                    uint2 ob;
+                                    ob.x = *reinterpret_cast<uint32_t*>(&lo);
+                                    ob.y = *reinterpret_cast<uint32_t*>(&hi);
+                                    *reinterpret_cast<uint2*>(a.y + y0) = ob;
+                                    if (yf) *reinterpret_cast<float4*>(yf + y0) = sum;
                                 }
                             }
                         }
