@@ -1,6 +1,7 @@
 // Host side of the weight-only GEMV entry points: argument checks, the split-K
 // plan, kernel selection.  Replaces the launchers at csrc/w_gemv.cu:1410-1570
 // of the reference.
+#include <cstdlib>
 #include <mutex>
 
 #include "gemv_mma.cuh"
@@ -50,7 +51,7 @@ MmaPlan plan_mma(int64_t M, int64_t OUT, int64_t NB, int fmt = GF_MSAQ_U4) {
         s.col_tiles = (int)((OUT + tc - 1) / tc);
         const long long units = s.units();
         s.grid = (int)(units < slots ? units : slots);
-        if (tc == min_tc || (s.grid + s.col_tiles - 1) / s.col_tiles <= 32) break;
+        if (tc == min_tc || (s.grid + s.col_tiles - 1) / s.col_tiles <= 32) break;      // 8, 16 and 64 measured slower
     }
     // Launches of one or two passes (up to eight rows) on half- or quarter-width tiles: two or four K blocks per ring
     // stage, for the same cut in hand-offs per byte the wider tile gives (8192x28672: 44.5 -> 41.3 us at one row,
