@@ -349,6 +349,18 @@ int msaq_peer_exchange(const float* partial, const void* residual, void* out, vo
                        int64_t n, int parity, void* stream);
 
 /*
+ * y = bf16(residual + bf16(W . pro(x))): msaq_wonly_gemv_fused (prologue none, rmsnorm or SiLU*mul) with the
+ * residual add of a decoder layer's last projection done by the GEMV's finishing warps -- the same two roundings
+ * as the GEMV followed by msaq_add_residual, one launch fewer.  residual and y bf16 [M, OUT]; y may be the
+ * residual's own memory (every output is read before it is written, by the same thread).  Formats and sizes the
+ * integer-MMA kernel does not serve run the two steps as separate kernels.
+ */
+int msaq_wonly_gemv_fused_add(const void* x, int prologue, float eps, const int8_t* scale_exp,
+                              const uint8_t* upper_cm, const uint8_t* shared_cm, const void* residual, void* y,
+                              int64_t M, int64_t OUT, int64_t NB, int u, int gs,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * msaq_wonly_gemv_fused with the exchange's push inside, for the row-parallel projections (O, down) of a
  * tensor-parallel layer: the warp that finishes a tile of outputs stores them straight into this rank's slot of
  * every rank's exchange buffer (its own included) instead of into local memory, so the partial sums cross NVLink

@@ -235,7 +235,7 @@ int launch_xprep(const XprepArgs& xa, int mode, unsigned grid, cudaStream_t st) 
 
 int run_mma(const __nv_bfloat16* X, const Prologue& pro, const int8_t* se, const uint8_t* up, const uint8_t* sh,
             void* Y, float* Yf, int64_t M, int64_t OUT, int64_t NB, void* ws, cudaStream_t st, int fmt = GF_MSAQ_U4,
-            const PeerPush* push = nullptr) {
+            const PeerPush* push = nullptr, const void* res = nullptr) {
     const MmaPlan p = plan_mma(M, OUT, NB, fmt);
     uint8_t* base = static_cast<uint8_t*>(ws);
     int* status = reinterpret_cast<int*>(base);
@@ -282,7 +282,8 @@ int run_mma(const __nv_bfloat16* X, const Prologue& pro, const int8_t* se, const
         GemvMmaArgs a{se, up, sh, xprep, partial, counters, status, sticky_status(), static_cast<__nv_bfloat16*>(Y), Yf,
                       (int)m0, rows, (int)OUT, (int)NB, sch, option_wait_polls(), option_test_skip_stage(),
                       in_kernel ? pro.mode : -1, xa.X, xa.R, xa.h_out, (int)ldx, pro.r_is_f32, pro.eps, tag,
-                      in_kernel ? (int)table : 0, 0, option_early_weights() ? 1 : 0, push ? *push : PeerPush{}};
+                      in_kernel ? (int)table : 0, 0, option_early_weights() ? 1 : 0, push ? *push : PeerPush{},
+                      static_cast<const __nv_bfloat16*>(res)};
         // the ring depth was planned for the first tile's pass count; a last, smaller tile may go deeper but need not
         int rc;
         if (fmt == GF_MXINT8) {
@@ -446,6 +447,35 @@ extern "C" int msaq_wonly_gemv_fused(const void* x, int prologue, const void* ad
     }
     if (rc) return rc;
     return gemv_dispatch(tmp, scale_exp, upper_cm, shared_cm, y, y_f32, M, OUT, NB, u, gs, true, workspace, g, stream);
+}
+
+// ---- fused GEMV with the residual add behind it ------------------------------------------------
+extern "C" int msaq_wonly_gemv_fused_add(const void* x, int prologue, float eps, const int8_t* scale_exp,
+                                         const uint8_t* upper_cm, const uint8_t* shared_cm, const void* residual, void* y,
+                                         int64_t M, int64_t OUT, int64_t NB, int u, int gs, void* workspace,
+                                         size_t workspace_bytes, void* stream) {
+    if (prologue != MSAQ_PRO_NONE && prologue != MSAQ_PRO_RMSNORM && prologue != MSAQ_PRO_SILU_MUL)
+        return fail(MSAQ_ERR_ARG, "prologue %d: none, rmsnorm or SiLU*mul", prologue);
+    if (!x || !scale_exp || !upper_cm || !shared_cm || !residual || !y) return fail(MSAQ_ERR_ARG, "null pointer");
+    if (M <= 0 || OUT <= 0 || NB <= 0) return fail(MSAQ_ERR_ARG, "M, OUT and NB must be positive");
+    if (M > INT32_MAX || OUT > INT32_MAX || NB * BLOCK > INT32_MAX / 2) return fail(MSAQ_ERR_ARG, "size exceeds 2^31");
+    if (int rc = require_sm100()) return rc;
+    const size_t need = msaq_wonly_gemv_fused_workspace(M, OUT, NB, u, gs);
+    if (!workspace || workspace_bytes < need)
+        return fail(MSAQ_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", need, workspace ? workspace_bytes : (size_t)0);
+    const bool ok = !((reinterpret_cast<uintptr_t>(x) & 15) | (reinterpret_cast<uintptr_t>(y) & 7) |
+                      (reinterpret_cast<uintptr_t>(residual) & 7)) && M < GU_MIN_M &&
+                    mma_usable(scale_exp, upper_cm, shared_cm, workspace, OUT, u, gs, true);
+    if (ok) {
+        const Prologue pro{prologue, nullptr, 0, nullptr, eps};
+        return run_mma(static_cast<const __nv_bfloat16*>(x), pro, scale_exp, upper_cm, shared_cm, y, nullptr, M, OUT, NB,
+                       workspace, static_cast<cudaStream_t>(stream), GF_MSAQ_U4, nullptr, residual);
+    }
+    // every other format and size: the same two steps as separate kernels (identical roundings)
+    if (int rc = msaq_wonly_gemv_fused(x, prologue, nullptr, 0, eps, nullptr, scale_exp, upper_cm, shared_cm, y, nullptr, M, OUT,
+                                       NB, u, gs, workspace, workspace_bytes, stream))
+        return rc;
+    return msaq_add_residual(residual, y, 0, y, M * OUT, stream);
 }
 
 // ---- GEMV of a row-parallel projection with the exchange's push inside --------------------

@@ -303,6 +303,7 @@ struct GemvMmaArgs {
     int natural;             // in-kernel records in natural element order (see XprepArgs)
     int early;               // first ring-full of weights goes out before the wait on the kernel in front
     PeerPush push;
+    const __nv_bfloat16* res;   // optional [M][OUT]: y = bf16(res + W x), the residual add behind a layer's last projection
 };
 
 // Sums of squares of the launch's rows (of X, or of bf16(X + R) for XP_ADD_NORM) by all threads of the
@@ -805,8 +806,13 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
                                         gemv_push(a.push, o, acc[q][p][0], seq);
                                         gemv_push(a.push, o + 8, acc[q][p][1], seq);
                                     } else {
-                                        a.y[o] = __float2bfloat16_rn(acc[q][p][0]);
-                                        a.y[o + 8] = __float2bfloat16_rn(acc[q][p][1]);
+                                        __nv_bfloat16 b0 = __float2bfloat16_rn(acc[q][p][0]), b1 = __float2bfloat16_rn(acc[q][p][1]);
+                                        if (a.res) {       // the projection rounds to bf16 first, as the unfused add sees it
+                                            b0 = __float2bfloat16_rn(__bfloat162float(a.res[o]) + __bfloat162float(b0));
+                                            b1 = __float2bfloat16_rn(__bfloat162float(a.res[o + 8]) + __bfloat162float(b1));
+                                        }
+                                        a.y[o] = b0;
+                                        a.y[o + 8] = b1;
                                         if (yf) { yf[o] = acc[q][p][0]; yf[o + 8] = acc[q][p][1]; }
                                     }
                                 }
@@ -879,12 +885,19 @@ gemv_u4gs2_mma_kernel(const GemvMmaArgs a) {
                                     gemv_push(a.push, y0 + 2, sum.z, seq);
                                     gemv_push(a.push, y0 + 3, sum.w, seq);
                                 } else {
+                                    if (yf) *reinterpret_cast<float4*>(yf + y0) = sum;
+                                    if (a.res) {           // the projection rounds to bf16 first, as the unfused add sees it
+                                        const uint2 rb = *reinterpret_cast<const uint2*>(a.res + y0);
+                                        sum.x = bf16_lo(rb.x) + __bfloat162float(__float2bfloat16_rn(sum.x));
+                                        sum.y = bf16_hi(rb.x) + __bfloat162float(__float2bfloat16_rn(sum.y));
+                                        sum.z = bf16_lo(rb.y) + __bfloat162float(__float2bfloat16_rn(sum.z));
+                                        sum.w = bf16_hi(rb.y) + __bfloat162float(__float2bfloat16_rn(sum.w));
+                                    }
                                     __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x, sum.y), hi = __floats2bfloat162_rn(sum.z, sum.w);
                                     uint2 ob;
                                     ob.x = *reinterpret_cast<uint32_t*>(&lo);
                                     ob.y = *reinterpret_cast<uint32_t*>(&hi);
                                     *reinterpret_cast<uint2*>(a.y + y0) = ob;
-                                    if (yf) *reinterpret_cast<float4*>(yf + y0) = sum;
                                 }
                             }
                         }

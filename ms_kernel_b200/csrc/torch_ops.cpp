@@ -453,6 +453,28 @@ Tensor peer_exchange(const Tensor& partial, const c10::optional<Tensor>& residua
     return out;
 }
 
+// residual + GEMV(pro(x)), the last projection of a decoder layer with its residual add inside.
+Tensor wonly_gemv_fused_add(const Tensor& x, int64_t prologue, double eps, const Tensor& s, const Tensor& up, const Tensor& sh,
+                            const Tensor& residual, int64_t M, int64_t OUT, int64_t NB, int64_t u, int64_t gs) {
+    check_act(x, "x");
+    check_act(residual, "residual");
+    int64_t UB, SB;
+    fmt_sizes(u, gs, &UB, &SB);
+    TORCH_CHECK(M >= 1 && OUT >= 1 && NB >= 1, "M, OUT and NB must be positive");
+    TORCH_CHECK(x.numel() == M * NB * 32 * (prologue == MSAQ_PRO_SILU_MUL ? 2 : 1), "x has ", x.numel(), " elements");
+    TORCH_CHECK(residual.numel() == M * OUT, "residual must be [M, OUT]");
+    check_planes(s, up, sh, x, NB * OUT, UB, SB);
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor y = at::empty({M, OUT}, x.options());
+    const size_t wsb = msaq_wonly_gemv_fused_workspace(M, OUT, NB, (int)u, (int)gs);
+    Tensor ws = workspace(x, wsb);
+    check_rc(msaq_wonly_gemv_fused_add(x.data_ptr(), (int)prologue, (float)eps, s.data_ptr<int8_t>(), up.data_ptr<uint8_t>(),
+                                       sh.data_ptr<uint8_t>(), residual.data_ptr(), y.data_ptr(), M, OUT, NB, (int)u, (int)gs,
+                                       ws.data_ptr(), wsb, stream_of(x)),
+             "wonly_gemv_fused_add");
+    return y;
+}
+
 // The row-parallel GEMV with the exchange's push inside (no output tensor: the partial sums land in the ranks'
 // exchange buffers), and the receiving half of the exchange: fp32 [M, OUT] sum, or bf16(residual + sum).
 void wonly_gemv_fused_push(const Tensor& x, int64_t prologue, double eps, const Tensor& s, const Tensor& up, const Tensor& sh,
@@ -786,6 +808,8 @@ TORCH_LIBRARY(msaq, m) {
     m.def("silu_mul(Tensor gate_up) -> Tensor", &silu_mul);
     m.def("add_residual(Tensor h, Tensor delta) -> Tensor", &add_residual);
     m.def("peer_exchange(Tensor partial, Tensor? residual, int[] peer_ptrs, int rank, int parity) -> Tensor", &peer_exchange);
+    m.def("wonly_gemv_fused_add(Tensor x, int prologue, float eps, Tensor scale_exp, Tensor upper_cm, Tensor shared_cm, "
+          "Tensor residual, int M, int OUT, int NB, int u, int gs) -> Tensor", &wonly_gemv_fused_add);
     m.def("wonly_gemv_fused_push(Tensor x, int prologue, float eps, Tensor scale_exp, Tensor upper_cm, Tensor shared_cm, int M, "
           "int OUT, int NB, int u, int gs, int[] peer_ptrs, int rank, int parity) -> ()", &wonly_gemv_fused_push);
     m.def("peer_exchange_recv(Tensor like, Tensor? residual, int[] peer_ptrs, int rank, int parity, int M, int OUT) -> Tensor",

@@ -139,6 +139,13 @@ class PackedLinear:
                                     self.u, self.gs, bool(out_f32))
         return (out[0], out[1]) if prologue == PRO_ADD_RMSNORM else out[0]
 
+    def fwd_fused_add(self, x, prologue, residual, eps=1e-5):
+        """residual + GEMV(prologue(x)) in bf16, the residual add done by the GEMV's finishing warps (same
+        roundings as fwd_fused followed by the add).  prologue: PRO_NONE, PRO_RMSNORM or PRO_SILU_MUL."""
+        M = int(x.shape[0])
+        return _OPS.wonly_gemv_fused_add(x.contiguous(), int(prologue), float(eps), self.scale_exp, self.upper_cm,
+                                         self.shared_cm, residual.contiguous(), M, self.OUT, self.nb, self.u, self.gs)
+
     def can_push(self, M):
         """Whether fwd_push serves M rows of this linear (the integer-MMA GEMV's terms)."""
         return self.u == 4 and self.gs == 2 and 1 <= M <= 8 and self.OUT % 16 == 0 and (M * self.OUT) % 4 == 0

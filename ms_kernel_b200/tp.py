@@ -323,6 +323,8 @@ class DecoderLayerTP:
         o = self.all_reduce(o) if self.world > 1 else o
         if fused:
             gu, h = self.lin["gate_up"].fwd_fused(h, 3, o, self.eps)   # h + o, rmsnorm inside
+            if self.world == 1 and hasattr(self.lin["down"], "fwd_fused_add"):
+                return self.lin["down"].fwd_fused_add(gu, 2, h, self.eps)      # SiLU(gate) * up in front, h + ... behind
             dn = self.lin["down"].fwd_fused(gu, 2, None, self.eps, self.world > 1)   # SiLU(gate) * up inside; fp32 partial for the all-reduce
         else:
             h = self._add(h, o)

@@ -242,3 +242,22 @@ def test_early_weights_option_changes_no_bit(rng, OUT, K, M):
     for a, b in zip(outs[0], outs[1]):
         assert torch.equal(a, b)
     assert L.msaq_get_option(6) == 0
+
+
+@pytest.mark.parametrize("OUT,K,M,u,prologue", [(8192, 28672 // 4, 1, 4, 2), (4096, 4096, 1, 4, 0), (8192, 1024, 4, 4, 1),
+                                               (1024, 512, 8, 4, 2), (8192, 2048, 16, 4, 2), (1024, 512, 2, 3, 0)])
+def test_residual_add_behind_the_gemv_is_bit_equal_to_the_two_steps(rng, OUT, K, M, u, prologue):
+    """msaq_wonly_gemv_fused_add: the residual add of a layer's last projection done by the GEMV's finishing warps
+    rounds exactly as the GEMV followed by msaq_add_residual (16 rows and u = 3 take the two-kernel route inside)."""
+    from ms_kernel_b200 import ops, pack
+    dev = torch.device("cuda")
+    g = torch.Generator(device="cuda").manual_seed(OUT + K + M + u)
+    W = (torch.randn((OUT, K), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    lin = ops.PackedLinear(pack.pack_weight(W, u, 2, device=dev), dev)
+    x = torch.randn((M, (2 if prologue == 2 else 1) * K), generator=g, device="cuda").to(torch.bfloat16)
+    h = torch.randn((M, OUT), generator=g, device="cuda").to(torch.bfloat16)
+    y = lin.fwd_fused(x, prologue) if prologue else lin.fwd(x)
+    want = torch.ops.msaq.add_residual(h, y.reshape(M, OUT).contiguous())
+    got = lin.fwd_fused_add(x, prologue, h)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want.reshape(M, OUT))
