@@ -33,7 +33,7 @@ bool mma_eligible(int64_t H, int64_t Hkv, int64_t D, int u, int gs, int64_t Lcap
 }
 
 struct KvMmaPlan {
-    int S, key_tile;
+    int S, key_tile, cps;
     size_t status_off, total;
 };
 
@@ -44,7 +44,9 @@ KvMmaPlan plan_mma(int64_t B, int64_t H, int64_t Hkv, int64_t Lk) {
     // the pipeline fill and the tail of one CTA overlap with the steady state of others -- but no
     // tile shorter than 1024 keys (query staging, pipeline fill and merge are fixed costs per tile),
     // except to fill one wave when the whole problem is small.
-    const int64_t slots = (int64_t)KVM_CTAS_PER_SM * sm_count();
+    // thread blocks per SM: three (two-stage ring) from 64 MB of cache on, two (three-stage ring) below
+    p.cps = B * Hkv * Lk * 200 >= (64LL << 20) ? 3 : 2;
+    const int64_t slots = (int64_t)p.cps * sm_count();
     int64_t want = (4 * slots + pairs - 1) / pairs;
     const int64_t by_size = Lk / 1024;
     int64_t one_wave = slots / pairs;
@@ -62,21 +64,26 @@ KvMmaPlan plan_mma(int64_t B, int64_t H, int64_t Hkv, int64_t Lk) {
     return p;
 }
 
-template <int G, int FMT = KVF_MSAQ_U4>
-int launch_kv_mma(const KvMmaArgs& a, int S, int Hkv, int B, cudaStream_t st) {
+template <int G, int FMT, int CPS>
+int launch_kv_mma_cps(const KvMmaArgs& a, int S, int Hkv, int B, cudaStream_t st) {
     static bool configured[64] = {};
-    constexpr int smem = kvm_smem_bytes(FMT);
+    constexpr int smem = kvm_smem_bytes(FMT, CPS);
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(kv_decode_u4gs2_kernel<G, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        if (cudaFuncSetAttribute(kv_decode_u4gs2_kernel<G, FMT, CPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
             cudaSuccess)
             return fail(MSAQ_ERR_CUDA, "cannot reserve %d bytes of shared memory", smem);
         configured[dev] = true;
     }
-    launch_chained(kv_decode_u4gs2_kernel<G, FMT>, dim3((unsigned)S, (unsigned)Hkv, (unsigned)B), dim3(KVM_THREADS), smem, st, a);
+    launch_chained(kv_decode_u4gs2_kernel<G, FMT, CPS>, dim3((unsigned)S, (unsigned)Hkv, (unsigned)B), dim3(KVM_THREADS), smem, st, a);
     count_launch();
     return check_launch(FMT == KVF_MXINT8 ? "kv_decode_mxint8" : "kv_decode_u4gs2");
+}
+
+template <int G, int FMT = KVF_MSAQ_U4>
+int launch_kv_mma(const KvMmaArgs& a, int S, int Hkv, int B, int cps, cudaStream_t st) {
+    return cps == 3 ? launch_kv_mma_cps<G, FMT, 3>(a, S, Hkv, B, st) : launch_kv_mma_cps<G, FMT, 2>(a, S, Hkv, B, st);
 }
 
 struct QRope {
@@ -97,17 +104,17 @@ int run_mma(const __nv_bfloat16* q, KvPlanes kp, KvPlanes vp, void* out, float* 
     int rc;
     if (fmt == KVF_MXINT8) {
         switch (H / Hkv) {
-            case 1: rc = launch_kv_mma<1, KVF_MXINT8>(a, p.S, (int)Hkv, (int)B, st); break;
-            case 2: rc = launch_kv_mma<2, KVF_MXINT8>(a, p.S, (int)Hkv, (int)B, st); break;
-            case 4: rc = launch_kv_mma<4, KVF_MXINT8>(a, p.S, (int)Hkv, (int)B, st); break;
-            default: rc = launch_kv_mma<8, KVF_MXINT8>(a, p.S, (int)Hkv, (int)B, st); break;
+            case 1: rc = launch_kv_mma<1, KVF_MXINT8>(a, p.S, (int)Hkv, (int)B, p.cps, st); break;
+            case 2: rc = launch_kv_mma<2, KVF_MXINT8>(a, p.S, (int)Hkv, (int)B, p.cps, st); break;
+            case 4: rc = launch_kv_mma<4, KVF_MXINT8>(a, p.S, (int)Hkv, (int)B, p.cps, st); break;
+            default: rc = launch_kv_mma<8, KVF_MXINT8>(a, p.S, (int)Hkv, (int)B, p.cps, st); break;
         }
     } else
     switch (H / Hkv) {
-        case 1: rc = launch_kv_mma<1>(a, p.S, (int)Hkv, (int)B, st); break;
-        case 2: rc = launch_kv_mma<2>(a, p.S, (int)Hkv, (int)B, st); break;
-        case 4: rc = launch_kv_mma<4>(a, p.S, (int)Hkv, (int)B, st); break;
-        default: rc = launch_kv_mma<8>(a, p.S, (int)Hkv, (int)B, st); break;
+        case 1: rc = launch_kv_mma<1>(a, p.S, (int)Hkv, (int)B, p.cps, st); break;
+        case 2: rc = launch_kv_mma<2>(a, p.S, (int)Hkv, (int)B, p.cps, st); break;
+        case 4: rc = launch_kv_mma<4>(a, p.S, (int)Hkv, (int)B, p.cps, st); break;
+        default: rc = launch_kv_mma<8>(a, p.S, (int)Hkv, (int)B, p.cps, st); break;
     }
     if (rc) return rc;
     launch_chained(kv_decode_combine2_kernel, dim3((unsigned)H, (unsigned)B), dim3(128), 0, st,

@@ -30,8 +30,11 @@ constexpr int KVM_WARPS = 4;
 constexpr int KVM_THREADS = (KVM_WARPS + 1) * 32;
 constexpr int KVM_TK = 128;                 // keys per stage
 constexpr int KVM_CHUNK = 32;               // keys per warp per stage
-constexpr int KVM_STAGES = 3;
-constexpr int KVM_CTAS_PER_SM = 2;
+// Two builds of the kernel: CPS = 2 thread blocks per SM with a three-stage ring (up to 204 registers), for small
+// problems where each block's own latency counts (B = 1, Lk = 16384: 17.6 against 19.3 us), and CPS = 3 with a
+// two-stage ring (136 registers, no spills), for large ones where twelve consumer warps per SM hide more of the
+// softmax / P.V issue latency than eight (GQA 32/8, Lk = 32768, B = 64: 630 -> 595 us; B = 16: 186 -> 170 us).
+constexpr int kvm_stages(int cps) { return cps == 3 ? 2 : 3; }
 constexpr int KVM_UP = KVM_TK * 16, KVM_SH = KVM_TK * 8, KVM_SC = KVM_TK;
 constexpr int KVM_K_UP = 0, KVM_K_SH = 4 * KVM_UP, KVM_K_SC = KVM_K_SH + 4 * KVM_SH;
 constexpr int KVM_V_UP = KVM_K_SC + 4 * KVM_SC, KVM_V_SH = KVM_V_UP + 4 * KVM_UP, KVM_V_SC = KVM_V_SH + 4 * KVM_SH;
@@ -44,16 +47,12 @@ constexpr int KVX_Q = KVM_TK * 32;                                // code bytes 
 constexpr int KVX_K_Q = 0, KVX_K_SC = 4 * KVX_Q, KVX_V_Q = KVX_K_SC + 4 * KVM_SC, KVX_V_SC = KVX_V_Q + 4 * KVX_Q;
 constexpr int KVX_STAGE_BYTES = KVX_V_SC + 4 * KVM_SC;            // 33792
 __host__ __device__ constexpr int kvm_stage_bytes(int fmt) { return fmt == KVF_MXINT8 ? KVX_STAGE_BYTES : KVM_STAGE_BYTES; }
-__host__ __device__ constexpr int kvm_smem_bytes(int fmt) {      // ring + query records + probability exchange + scale table
-    return KVM_STAGES * kvm_stage_bytes(fmt) + 4 * 2 * 320 + KVM_WARPS * 8 * 40 * 4 + KVM_WARPS * 4 * 32 * 4;
+__host__ __device__ constexpr int kvm_smem_bytes(int fmt, int cps) {      // ring + query records + probability exchange + scale table
+    return kvm_stages(cps) * kvm_stage_bytes(fmt) + 4 * 2 * 320 + KVM_WARPS * 8 * 40 * 4 + KVM_WARPS * 4 * 32 * 4;
 }
 constexpr int KVM_QREC = 320;               // staged query record per (block, pass); layout as in gemv_mma.cuh
 constexpr float KVM_SPLIT_TAU = 0.001953125f;  // 2^-9: a chunk is split when all keys but its maximum sum to less than this
 constexpr int KVM_PSTRIDE = 40;             // floats per head row of the probability exchange buffer
-constexpr int KVM_OFF_Q = KVM_STAGES * KVM_STAGE_BYTES;
-constexpr int KVM_OFF_P = KVM_OFF_Q + 4 * 2 * KVM_QREC;
-constexpr int KVM_OFF_R = KVM_OFF_P + KVM_WARPS * 8 * KVM_PSTRIDE * 4;      // per-warp 2^-shift table [4][32] floats
-constexpr int KVM_SMEM = KVM_OFF_R + KVM_WARPS * 4 * 32 * 4;
 
 struct KvMmaArgs {
     const __nv_bfloat16* q;     // [B][Hq][128]
@@ -72,16 +71,17 @@ struct KvMmaArgs {
     int skip_stage;             // test hook: the producer of CTA (0,0,0) stops before this stage (-1: never)
 };
 
-template <int G, int FMT = KVF_MSAQ_U4>
-__global__ void __launch_bounds__(KVM_THREADS, KVM_CTAS_PER_SM)
+template <int G, int FMT = KVF_MSAQ_U4, int CPS = 2>
+__global__ void __launch_bounds__(KVM_THREADS, CPS)
 kv_decode_u4gs2_kernel(const KvMmaArgs a) {
+    constexpr int KVM_STAGES = kvm_stages(CPS);
     chain_wait();
     constexpr int PASSES = (G + 3) / 4;
     constexpr bool MX = FMT == KVF_MXINT8;
     constexpr int KVM_STAGE_BYTES = kvm_stage_bytes(FMT);        // shadows the MSAQ constants below
     constexpr int KVM_OFF_Q = KVM_STAGES * KVM_STAGE_BYTES;
     constexpr int KVM_OFF_P = KVM_OFF_Q + 4 * 2 * KVM_QREC;
-    constexpr int KVM_OFF_R = KVM_OFF_P + KVM_WARPS * 8 * KVM_PSTRIDE * 4;
+    constexpr int KVM_OFF_R = KVM_OFF_P + KVM_WARPS * 8 * KVM_PSTRIDE * 4;      // per-warp 2^-shift table [4][32] floats
     extern __shared__ __align__(128) uint8_t kvm_smem[];
     uint8_t* const smem = kvm_smem;
     __shared__ __align__(8) uint64_t bar_full[KVM_STAGES];
