@@ -133,6 +133,113 @@ def _run_rank(rank, world, port, seed, q, shape_args=None):
         dist.destroy_process_group()
 
 
+class _FusedOracleLinear(_OracleLinear):
+    """The fused entry points of ops.PackedLinear restated on the CPU (same argument meaning), so that the branches of
+    DecoderLayerTP.step that use them -- glue fused into the GEMVs, the residual add behind the last one, the exchange
+    started inside the row-parallel GEMVs -- run in the CPU suite."""
+    glue = _TorchGlue()
+
+    def _pro(self, x, prologue, addend, eps):
+        h = None
+        if prologue == 1:
+            x = self.glue.rmsnorm(x, eps)
+        elif prologue == 2:
+            x = self.glue.silu_mul(x)
+        elif prologue == 3:
+            h = self.glue.add(x, addend)
+            x = self.glue.rmsnorm(h, eps)
+        return x, h
+
+    def fwd_f32(self, x):
+        return (x.double() @ self.W.T).float()
+
+    def fwd_fused(self, x, prologue, addend=None, eps=1e-5, out_f32=False):
+        x, h = self._pro(x, prologue, addend, eps)
+        y = self.fwd_f32(x) if out_f32 else self.fwd(x)
+        return (y, h) if prologue == 3 else y
+
+    def fwd_fused_add(self, x, prologue, residual, eps=1e-5):
+        return self.glue.add(residual, self.fwd_fused(x, prologue, None, eps))
+
+    def can_push(self, M):
+        return M <= 8
+
+
+class _GlooExchange:
+    """tp.PeerExchange's interface over a gloo all-reduce: push_from runs the GEMV and keeps the partial sums,
+    recv completes the sum (and adds the residual)."""
+    fused = True
+
+    def __init__(self):
+        self.calls = 0
+
+    def push_from(self, lin, x, prologue=0, eps=1e-5):
+        self.calls += 1
+        return lin.fwd_fused(x, prologue, None, eps, True) if prologue else lin.fwd_f32(x)
+
+    def recv(self, token, residual=None):
+        import torch.distributed as dist
+        dist.all_reduce(token)
+        return token if residual is None else (residual.float() + token).to(residual.dtype)
+
+    def __call__(self, t):                      # the unfused route must not be taken
+        raise AssertionError("the step did not take the fused exchange")
+
+
+def _run_rank_fused(rank, world, port, seed, q):
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    rng = np.random.default_rng(seed)
+    W, P = _weights(rng, SHAPE)
+    B, L = 2, 12
+    sh = tp.shard_layer(P, SHAPE, world, rank)
+    lin = {k: _FusedOracleLinear(v) for k, v in sh.items()}
+    _, kv, _ = SHAPE.local(world)
+    cache = _OracleCache(B, kv, SHAPE.head_dim, L)
+    full_K = torch.from_numpy(rng.standard_normal((B, SHAPE.n_kv, L, SHAPE.head_dim)))
+    full_V = torch.from_numpy(rng.standard_normal((B, SHAPE.n_kv, L, SHAPE.head_dim)))
+    cache.K[:] = full_K[:, rank * kv:(rank + 1) * kv]
+    cache.V[:] = full_V[:, rank * kv:(rank + 1) * kv]
+    ex = _GlooExchange() if world > 1 else None
+    layer = tp.DecoderLayerTP(SHAPE, world, lin, cache, ex, glue=_TorchGlue())
+    h = torch.from_numpy(rng.standard_normal((B, SHAPE.hidden)).astype(np.float32)).to(torch.bfloat16)
+    cos, sin = orc.rope_tables(np.array([L - 1]), SHAPE.head_dim)
+    out = layer.step(h, L - 1, L, rope=(torch.from_numpy(cos), torch.from_numpy(sin)))
+    if rank == 0:
+        q.put((out.float().numpy(), ex.calls if ex else 0))
+        q.close()
+        q.join_thread()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def test_fused_step_and_exchange_inside_the_gemvs_match_the_plain_step():
+    """One rank: glue fused into the GEMVs and the residual add behind the last one; two ranks: both exchanges
+    started inside the row-parallel GEMVs (push_from / recv).  Both against the unfused single-rank step."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q0 = ctx.Queue()
+    p0 = ctx.Process(target=_run_rank, args=(0, 1, 0, 123, q0, None))
+    p0.start()
+    plain = q0.get(timeout=120)
+    p0.join(timeout=120)
+    for world in (1, 2):
+        q = ctx.Queue()
+        port = _free_port()
+        procs = [ctx.Process(target=_run_rank_fused, args=(r, world, port, 123, q)) for r in range(world)]
+        for p in procs:
+            p.start()
+        got, calls = q.get(timeout=120)
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+        assert calls == (2 if world > 1 else 0)
+        assert np.isfinite(got).all()
+        assert orc.rel_fro(got, plain) < 2e-2
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
