@@ -595,15 +595,14 @@ def single_gpu_detail(dev, peak, peak_kind):
         pos = (sl - 1).to(torch.int32)
 
         def step(c):
-            c.append(kn, kn, pos)          # one new token per sequence, then attend
-            return c.attend(q, Lk, sl)
+            return c.append_attend(q, kn, kn, pos, Lk, sl)      # one new token per sequence, packed by the attention kernel
 
         usec = graph_time([(lambda c=c: step(c)) for c in caches], 10, dev)
         b = nbytes + 4 * B * Hq * D
         out["detail"]["kv_decode"].append({"case": tag, "B": B, "Hq": Hq, "Hkv": Hkv, "Lk": Lk, "varlen": varlen,
                                            "us": round(usec, 2), "GBps": round(b / usec / 1e3, 1),
                                            "frac_8TBs": round(b / usec / 1e3 / NOMINAL_PEAK_GBS, 3),
-                                           "includes": "K/V append of one token + flash-decode"})
+                                           "includes": "K/V append of one token (inside the attention kernel) + flash-decode"})
         del caches
         torch.cuda.empty_cache()
 

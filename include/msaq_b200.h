@@ -315,6 +315,25 @@ int msaq_kv_decode_attention_batched(const void* q,
                                      int64_t NB, int u, int gs, int64_t Lcap, int qrot,
                                      void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * One decode step's cache update and attention in one call: msaq_kv_append_pair_rope(k_new, v_new, ..., pos) followed
+ * by msaq_kv_decode_attention_rope(q, ..., q_pos = pos), with the same bytes in the cache and the same output.  On
+ * the tuned path (u = 4, gs = 2, D = 128, Hq/Hkv in {1,2,4,8}, Lcap % 16 == 0) the new token is packed by the
+ * attention kernel itself -- the thread block that owns the key tile of the token's slot writes the K and V rows of
+ * its (sequence, kv head) before it streams them -- so the append costs no launch; otherwise the two kernels run one
+ * after the other.  k_new, v_new bf16 [B, Hkv, D]; pos (pos_per_seq[b] when given) is the token's slot and its
+ * position for RoPE (query and K rows alike: the token attends from where it is stored); rotate_k applies the
+ * Hadamard rotation to the K row; rope_cos == NULL: no RoPE.
+ */
+int msaq_kv_decode_attention_append(const void* q, const void* k_new, const void* v_new,
+                                    int8_t* ks, uint8_t* ku, uint8_t* kh, int8_t* vs, uint8_t* vu, uint8_t* vh,
+                                    void* out, float* out_f32, const int32_t* seq_lens,
+                                    int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D, int64_t NB,
+                                    int u, int gs, int64_t Lcap, int rotate_k, int qrot,
+                                    const float* rope_cos, const float* rope_sin, int64_t rope_rows,
+                                    int64_t pos, const int32_t* pos_per_seq,
+                                    void* workspace, size_t workspace_bytes, void* stream);
+
 /* The batched decode with the rotary embedding of the query rows in the prologue (see msaq_rope above). */
 int msaq_kv_decode_attention_rope(const void* q,
                                   const int8_t* ks, const uint8_t* ku, const uint8_t* kh,

@@ -49,6 +49,8 @@ SIGNATURES = {
     "msaq_kv_decode_attention_batched": (_int, [_p] * 7 + [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64,
                                                              _int, _int, _i64, _int, _p, _sz, _p]),
     "msaq_peer_exchange_bytes": (_sz, [_int, _i64]),
+    "msaq_kv_decode_attention_append": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64,
+                                               _i64, _int, _int, _i64, _int, _int, _p, _p, _i64, _i64, _p, _p, _sz, _p]),
     "msaq_wonly_gemv_fused_add": (_int, [_p, _int, C.c_float, _p, _p, _p, _p, _p, _i64, _i64, _i64, _int, _int, _p, _sz, _p]),
     "msaq_wonly_gemv_fused_push": (_int, [_p, _int, _p, _int, C.c_float, _p, _p, _p, _p, _i64, _i64, _i64, _int, _int,
                                           C.POINTER(_p), _int, _int, _int, _p, _sz, _p]),

@@ -92,15 +92,29 @@ struct QRope {
     const int32_t* q_pos_per_seq;
 };
 
+// The step's new token, to be appended by the decode kernel itself (see KvMmaArgs).
+struct KvAppend {
+    const void* k_new;
+    const void* v_new;
+    int64_t pos;
+    const int32_t* pos_per_seq;
+    int rotate_k;
+};
+
 int run_mma(const __nv_bfloat16* q, KvPlanes kp, KvPlanes vp, void* out, float* out_f32, const int32_t* seq_lens,
             int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t Lcap, int qrot, const QRope& qr, void* ws,
-            cudaStream_t st, int fmt = KVF_MSAQ_U4) {
+            cudaStream_t st, int fmt = KVF_MSAQ_U4, const KvAppend* app = nullptr) {
     const KvMmaPlan p = plan_mma(B, H, Hkv, Lk);
+    Fmt f4{};
+    make_fmt(4, 2, &f4);
     uint8_t* base = static_cast<uint8_t*>(ws) + WS_CTL_BYTES;
     int* status = reinterpret_cast<int*>(base + p.status_off);
     KvMmaArgs a{q, kp, vp, reinterpret_cast<float*>(base), seq_lens, status, sticky_status(), (int)H, (int)Hkv, (int)Lk,
                 (int)Lcap, p.key_tile, p.S, qrot, (float)(1.4426950408889634 / sqrt(128.0)), qr.rope, qr.q_pos,
-                qr.q_pos_per_seq, KVM_SPLIT_TAU, option_wait_polls(), option_test_skip_stage()};
+                qr.q_pos_per_seq, KVM_SPLIT_TAU, option_wait_polls(), option_test_skip_stage(),
+                app ? static_cast<const __nv_bfloat16*>(app->k_new) : nullptr,
+                app ? static_cast<const __nv_bfloat16*>(app->v_new) : nullptr, app ? app->pos : 0,
+                app ? app->pos_per_seq : nullptr, app ? app->rotate_k : 0, f4};
     int rc;
     if (fmt == KVF_MXINT8) {
         switch (H / Hkv) {
@@ -125,7 +139,8 @@ int run_mma(const __nv_bfloat16* q, KvPlanes kp, KvPlanes vp, void* out, float* 
 
 int decode_dispatch(const void* q, KvPlanes kp, KvPlanes vp, void* out, float* out_f32, const int32_t* seq_lens,
                     int64_t B, int64_t H, int64_t Hkv, int64_t Lk, int64_t D, int64_t NB, int u, int gs,
-                    int64_t Lcap, int qrot, const QRope& qr, void* ws, size_t ws_bytes, void* stream) {
+                    int64_t Lcap, int qrot, const QRope& qr, void* ws, size_t ws_bytes, void* stream,
+                    const KvAppend* app = nullptr) {
     Fmt f;
     if (qr.rope.cos) {
         if (!qr.rope.sin || qr.rope.rows < 1) return fail(MSAQ_ERR_ARG, "bad RoPE tables");
@@ -156,7 +171,14 @@ int decode_dispatch(const void* q, KvPlanes kp, KvPlanes vp, void* out, float* o
         !((reinterpret_cast<uintptr_t>(kp.s) | reinterpret_cast<uintptr_t>(kp.u) | reinterpret_cast<uintptr_t>(kp.h) |
            reinterpret_cast<uintptr_t>(vp.s) | reinterpret_cast<uintptr_t>(vp.u) | reinterpret_cast<uintptr_t>(vp.h)) & 15))
         return run_mma(static_cast<const __nv_bfloat16*>(q), kp, vp, out, out_f32, seq_lens, B, H, Hkv, Lk, Lcap, qrot,
-                       qr, ws, st);
+                       qr, ws, st, KVF_MSAQ_U4, app);
+    if (app) {           // the generic kernels take the token from the cache: append it with the kernel of its own first
+        if (int rc = msaq_kv_append_pair_rope(app->k_new, app->v_new, const_cast<int8_t*>(kp.s), const_cast<uint8_t*>(kp.u),
+                                              const_cast<uint8_t*>(kp.h), const_cast<int8_t*>(vp.s), const_cast<uint8_t*>(vp.u),
+                                              const_cast<uint8_t*>(vp.h), B, Hkv, D, NB, app->pos, app->pos_per_seq, Lcap, u, gs,
+                                              app->rotate_k, qr.rope.cos, qr.rope.sin, qr.rope.rows, stream))
+            return rc;
+    }
     const KvPlan p = plan_generic(B, H, Lk);
     const float sm_scale = (float)(1.0 / sqrt((double)D));
     float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + WS_CTL_BYTES);
@@ -222,6 +244,27 @@ extern "C" int msaq_kv_decode_attention_rope(const void* q, const int8_t* ks, co
     return decode_dispatch(q, KvPlanes{ks, ku, kh}, KvPlanes{vs, vu, vh}, out, out_f32, seq_lens, B, H, Hkv, Lk, D, NB,
                            u, gs, Lcap, qrot, QRope{Rope{rope_cos, rope_sin, rope_rows}, q_pos, q_pos_per_seq}, workspace,
                            workspace_bytes, stream);
+}
+
+extern "C" int msaq_kv_decode_attention_append(const void* q, const void* k_new, const void* v_new, int8_t* ks, uint8_t* ku,
+                                               uint8_t* kh, int8_t* vs, uint8_t* vu, uint8_t* vh, void* out, float* out_f32,
+                                               const int32_t* seq_lens, int64_t B, int64_t H, int64_t Hkv, int64_t Lk,
+                                               int64_t D, int64_t NB, int u, int gs, int64_t Lcap, int rotate_k, int qrot,
+                                               const float* rope_cos, const float* rope_sin, int64_t rope_rows,
+                                               int64_t pos, const int32_t* pos_per_seq, void* workspace,
+                                               size_t workspace_bytes, void* stream) {
+    if (!k_new || !v_new) return fail(MSAQ_ERR_ARG, "null pointer");
+    if ((reinterpret_cast<uintptr_t>(k_new) | reinterpret_cast<uintptr_t>(v_new)) & 7)
+        return fail(MSAQ_ERR_ARG, "k_new and v_new must be 8-byte aligned");
+    const int64_t cap = Lcap < 0 ? Lk : Lcap;
+    if (!pos_per_seq && (pos < 0 || pos >= cap))
+        return fail(MSAQ_ERR_ARG, "pos %lld outside the capacity %lld", (long long)pos, (long long)cap);
+    if (rope_cos && !pos_per_seq && rope_rows != 1 && pos >= rope_rows)
+        return fail(MSAQ_ERR_ARG, "pos %lld outside the %lld RoPE table rows", (long long)pos, (long long)rope_rows);
+    const KvAppend app{k_new, v_new, pos, pos_per_seq, rotate_k};
+    return decode_dispatch(q, KvPlanes{ks, ku, kh}, KvPlanes{vs, vu, vh}, out, out_f32, seq_lens, B, H, Hkv, Lk, D, NB,
+                           u, gs, Lcap, qrot, QRope{Rope{rope_cos, rope_sin, rope_rows}, pos, pos_per_seq}, workspace,
+                           workspace_bytes, stream, &app);
 }
 
 // ---- plain MXINT8 caches (the reference's matched baseline, csrc/mxint8.cu:750-912) ---------------------

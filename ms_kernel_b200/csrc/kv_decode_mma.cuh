@@ -21,6 +21,7 @@
 // reference, including its fused query rotation (:485-498).
 #pragma once
 
+#include "kv_quant_row.cuh"
 #include "kv_decode_generic.cuh"
 #include "sm100_ptx.cuh"
 
@@ -69,6 +70,16 @@ struct KvMmaArgs {
     float split_limit;          // a chunk whose small keys sum to less than this (relative to its maximum) may split
     uint32_t max_polls;         // limit of every mbarrier wait (see mbar_wait_bounded)
     int skip_stage;             // test hook: the producer of CTA (0,0,0) stops before this stage (-1: never)
+    // The step's new token, appended by this kernel (k_new == nullptr: the cache is taken as it is): the thread block
+    // that owns the key tile of the token's slot packs the K row (RoPE with the query's tables at the slot, then the
+    // Hadamard rotation when app_rot) and the V row of its (sequence, kv head) into the planes before it streams
+    // them, exactly as msaq_kv_append_pair_rope would have.
+    const __nv_bfloat16* k_new;   // [B][Hkv][128]
+    const __nv_bfloat16* v_new;
+    int64_t app_pos;              // slot of the new token, or per sequence:
+    const int32_t* app_pos_per_seq;
+    int app_rot;
+    Fmt fmt;
 };
 
 template <int G, int FMT = KVF_MSAQ_U4, int CPS = 2>
@@ -102,6 +113,34 @@ kv_decode_u4gs2_kernel(const KvMmaArgs a) {
         mbar_init_fence();
     }
     for (int i = tid; i < 4 * 2 * KVM_QREC / 4; i += KVM_THREADS) reinterpret_cast<uint32_t*>(smem + KVM_OFF_Q)[i] = 0u;
+    if (a.k_new) {
+        // The new token: written by the thread block whose tile holds its slot (the last tile for a slot beyond the
+        // attended keys), warp 0 the K row, warp 1 the V row, through the ring memory that is still free.  The
+        // proxy fence and the barrier below put the bytes in front of this block's own bulk copies; no other
+        // block reads that slot.
+        const int64_t p = a.app_pos_per_seq ? (int64_t)a.app_pos_per_seq[b] : a.app_pos;
+        const bool valid = p >= 0 && p < a.Lcap;
+        const int owner = valid ? min((int)(p / a.key_tile), (int)gridDim.x - 1) : 0;
+        if (tile == owner) {
+            if (!valid) {
+                if (tid == 0 && hk == 0 && a.sticky) atomicOr(a.sticky, BAD_APPEND_POS);
+            } else if (warp < 2) {
+                const KvPlanes& pl = warp == 0 ? a.k : a.v;
+                QuantJob job;
+                job.X = warp == 0 ? a.k_new : a.v_new;
+                job.scale_exp = const_cast<int8_t*>(pl.s);
+                job.upper = const_cast<uint8_t*>(pl.u);
+                job.shared = const_cast<uint8_t*>(pl.h);
+                job.rot = warp == 0 ? a.app_rot : 0;
+                job.rope = warp == 0 ? 1 : 0;
+                job.mx = MX ? 1 : 0;
+                const int64_t head = (int64_t)b * a.Hkv + hk;
+                quantize_row_warp<4>(job, a.rope, head, head, p, a.Lcap, a.fmt, reinterpret_cast<float*>(smem + warp * 1024),
+                                     reinterpret_cast<uint32_t*>(smem + 2048 + warp * 256), lane);
+                asm volatile("fence.proxy.async;" ::: "memory");
+            }
+        }
+    }
     __syncthreads();
 
     if (warp == KVM_WARPS) {

@@ -406,6 +406,55 @@ Tensor kv_decode_attention_rope(const Tensor& q, const Tensor& ks, const Tensor&
                          &cos, &sin, q_pos_t, q_pos);
 }
 
+// One decode step's cache update and attention in one op (the planes are written in place).
+Tensor kv_decode_attention_append(const Tensor& q, const Tensor& k_new, const Tensor& v_new, Tensor ks, Tensor ku, Tensor kh,
+                                  Tensor vs, Tensor vu, Tensor vh, const c10::optional<Tensor>& seq_lens, int64_t B, int64_t H,
+                                  int64_t Hkv, int64_t Lk, int64_t D, int64_t NB, int64_t u, int64_t gs, int64_t Lcap,
+                                  bool rotate_k, bool qrot, const c10::optional<Tensor>& cos, const c10::optional<Tensor>& sin,
+                                  const c10::optional<Tensor>& pos_t, int64_t pos) {
+    check_act(q, "q");
+    check_act(k_new, "k_new");
+    check_act(v_new, "v_new");
+    TORCH_CHECK(cos.has_value() == sin.has_value(), "cos and sin come together");
+    if (cos.has_value()) check_rope(*cos, *sin, q, D);
+    const int32_t* pp = nullptr;
+    if (pos_t.has_value()) {
+        const Tensor& p = *pos_t;
+        TORCH_CHECK(p.is_cuda() && p.scalar_type() == at::kInt && p.is_contiguous() && p.numel() == B,
+                    "pos must be a contiguous CUDA int32 tensor of B elements");
+        pp = p.data_ptr<int32_t>();
+    }
+    reject_numeric_toggles();
+    int64_t UB, SB;
+    fmt_sizes(u, gs, &UB, &SB);
+    if (Lcap < 0) Lcap = Lk;
+    TORCH_CHECK(B >= 1 && H >= 1 && Hkv >= 1 && Lk >= 1, "B, H, Hkv and Lk must be positive");
+    TORCH_CHECK(q.numel() == B * H * D, "q must hold B*H*D elements");
+    TORCH_CHECK(k_new.numel() == B * Hkv * D && v_new.numel() == B * Hkv * D, "k_new and v_new must hold B*Hkv*D elements");
+    check_planes(ks, ku, kh, q, B * Hkv * NB * Lcap, UB, SB);
+    check_planes(vs, vu, vh, q, B * Hkv * NB * Lcap, UB, SB);
+    const int32_t* lens = nullptr;
+    if (seq_lens.has_value()) {
+        const Tensor& sl = *seq_lens;
+        TORCH_CHECK(sl.is_cuda() && sl.scalar_type() == at::kInt && sl.is_contiguous() && sl.numel() == B,
+                    "seq_lens must be a contiguous CUDA int32 tensor of B elements");
+        lens = sl.data_ptr<int32_t>();
+    }
+    c10::cuda::CUDAGuard guard(q.device());
+    Tensor out = at::empty({B, H, D}, q.options());
+    const size_t wsb = msaq_kv_decode_workspace(B, H, Hkv, Lk, D);
+    Tensor ws = workspace(q, wsb);
+    check_rc(msaq_kv_decode_attention_append(q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), ks.data_ptr<int8_t>(),
+                                             ku.data_ptr<uint8_t>(), kh.data_ptr<uint8_t>(), vs.data_ptr<int8_t>(),
+                                             vu.data_ptr<uint8_t>(), vh.data_ptr<uint8_t>(), out.data_ptr(), nullptr, lens, B, H,
+                                             Hkv, Lk, D, NB, (int)u, (int)gs, Lcap, rotate_k ? 1 : 0, qrot ? 1 : 0,
+                                             cos.has_value() ? cos->data_ptr<float>() : nullptr,
+                                             sin.has_value() ? sin->data_ptr<float>() : nullptr,
+                                             cos.has_value() ? cos->size(0) : 0, pos, pp, ws.data_ptr(), wsb, stream_of(q)),
+             "kv_decode_attention_append");
+    return out;
+}
+
 // x [B, heads, D] bf16 -> RoPE at position pos (pos_t[b] per sequence when given).
 Tensor rope(const Tensor& x, const Tensor& cos, const Tensor& sin, const c10::optional<Tensor>& pos_t, int64_t pos) {
     check_act(x, "x");
@@ -807,6 +856,10 @@ TORCH_LIBRARY(msaq, m) {
     m.def("rmsnorm(Tensor x, float eps) -> Tensor", &rmsnorm);
     m.def("silu_mul(Tensor gate_up) -> Tensor", &silu_mul);
     m.def("add_residual(Tensor h, Tensor delta) -> Tensor", &add_residual);
+    m.def("kv_decode_attention_append(Tensor q, Tensor k_new, Tensor v_new, Tensor(a!) k_scale_exp, Tensor(b!) k_upper, "
+          "Tensor(c!) k_shared, Tensor(d!) v_scale_exp, Tensor(e!) v_upper, Tensor(f!) v_shared, Tensor? seq_lens, int B, int H, "
+          "int Hkv, int Lk, int D, int NB, int u, int gs, int Lcap, bool rotate_k, bool qrot, Tensor? cos, Tensor? sin, "
+          "Tensor? pos_t, int pos) -> Tensor", &kv_decode_attention_append);
     m.def("peer_exchange(Tensor partial, Tensor? residual, int[] peer_ptrs, int rank, int parity) -> Tensor", &peer_exchange);
     m.def("wonly_gemv_fused_add(Tensor x, int prologue, float eps, Tensor scale_exp, Tensor upper_cm, Tensor shared_cm, "
           "Tensor residual, int M, int OUT, int NB, int u, int gs) -> Tensor", &wonly_gemv_fused_add);

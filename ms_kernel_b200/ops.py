@@ -231,6 +231,22 @@ class KVCache:
         return _OPS.kv_decode_attention_rope(q, *self.k, *self.v, seq_lens, self.B, Hq, self.Hkv, Lk, self.D, self.nb,
                                              self.u, self.gs, self.Lcap, self.rotate, rope[0], rope[1], pos_t, pos_i)
 
+    def append_attend(self, q, k_new, v_new, pos, Lk, seq_lens=None, rope=None):
+        """append(k_new, v_new, pos, rope) followed by attend(q, Lk, seq_lens, rope, pos) in one call: the same bytes
+        in the cache, the same output; on the tuned path the attention kernel packs the new token itself and the
+        append costs no launch (include/msaq_b200.h: msaq_kv_decode_attention_append)."""
+        Hq = int(q.shape[1])
+        if seq_lens is None:
+            seq_lens = self._full_lens.get(Lk)
+            if seq_lens is None:
+                seq_lens = self._full_lens[Lk] = torch.full((self.B,), Lk, dtype=torch.int32, device=q.device)
+        H = self.B * self.Hkv
+        pos_t, pos_i = (None, int(pos)) if isinstance(pos, int) else (pos, 0)
+        cos, sin = (None, None) if rope is None else (rope[0], rope[1])
+        return _OPS.kv_decode_attention_append(q, k_new.reshape(H, self.D).contiguous(), v_new.reshape(H, self.D).contiguous(),
+                                               *self.k, *self.v, seq_lens, self.B, Hq, self.Hkv, Lk, self.D, self.nb, self.u,
+                                               self.gs, self.Lcap, self.rotate, self.rotate, cos, sin, pos_t, pos_i)
+
 
 # --------------------------------------------------------------------------
 # plain MXINT8 twins (the reference's matched baseline format, ms_lib/pack.py:530-594)

@@ -304,7 +304,9 @@ class DecoderLayerTP:
         q = qkv[:, : self.q_heads * d].reshape(B, self.q_heads, d)
         k = qkv[:, self.q_heads * d:(self.q_heads + self.kv_heads) * d].reshape(B, self.kv_heads, d)
         v = qkv[:, (self.q_heads + self.kv_heads) * d:].reshape(B, self.kv_heads, d)
-        if rope is None:
+        if hasattr(self.cache, "append_attend"):
+            a = self.cache.append_attend(q.contiguous(), k, v, pos, Lk, seq_lens, rope)    # the append inside the attention kernel
+        elif rope is None:
             self.cache.append(k, v, pos)
             a = self.cache.attend(q.contiguous(), Lk, seq_lens)        # [B, q, d], heads local
         else:
