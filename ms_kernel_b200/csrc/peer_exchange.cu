@@ -69,25 +69,54 @@ peer_exchange_kernel(const PeerArgs a) {
             px_store(dst + 4, mine.z, mine.w, seq);
         }
         // ranks start a step up to a host jitter apart, so the limit is generous: 4 x the poll option, with
-        // 2 us naps once the first thousand polls have passed (seconds at the default, milliseconds in the tests)
+        // 2 us naps once the first thousand polls have passed (seconds at the default, milliseconds in the tests).
+        // All slots are polled together: the loads of a round go out back to back and only then are their sequence
+        // numbers looked at, so a round costs one load latency whatever the number of ranks (polling rank after rank
+        // made the wait grow by two dependent loads per rank: 11 us per exchange at eight ranks).
         const uint64_t limit = 4ull * a.max_polls;
         uint64_t polls = 0;
         bool ok = true;
-        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < a.world; ++r) {                  // rank order: the same sum on every rank
-            float4 v = mine;
-            if (r != a.rank || pushed) {
-                const float* src = a.buf[a.rank] + (((int64_t)a.parity * a.world + r) * a.n + i0) * 2;
-                bool got0 = false, got1 = false;
-                while (ok) {
-                    if (!got0) got0 = px_load(src, seq, v.x, v.y);
-                    if (!got1) got1 = px_load(src + 4, seq, v.z, v.w);
-                    if (got0 && got1) break;
-                    if (++polls >= limit) ok = false;
-                    else if (polls > 64) __nanosleep(polls < 1024 ? 100 : 2000);
+        float x[PX_MAX_WORLD][4];
+        uint32_t pending = 0;                                // bit 2r + k: half k of rank r's slot not seen yet
+#pragma unroll
+        for (int r = 0; r < PX_MAX_WORLD; ++r)
+            if (r < a.world && (r != a.rank || pushed)) pending |= 3u << (2 * r);
+        const float* base = a.buf[a.rank] + ((int64_t)a.parity * a.world * a.n + i0) * 2;
+        while (pending) {
+            uint32_t w[PX_MAX_WORLD][2][4];
+#pragma unroll
+            for (int r = 0; r < PX_MAX_WORLD; ++r) {
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    if (pending >> (2 * r + k) & 1u) {
+                        const float* src = base + (int64_t)r * a.n * 2 + 4 * k;
+                        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(w[r][k][0]), "=r"(w[r][k][1]), "=r"(w[r][k][2]), "=r"(w[r][k][3]) : "l"(src) : "memory");
+                    }
                 }
             }
-            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+#pragma unroll
+            for (int r = 0; r < PX_MAX_WORLD; ++r) {
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    if ((pending >> (2 * r + k) & 1u) && w[r][k][1] == seq && w[r][k][3] == seq) {
+                        x[r][2 * k] = __uint_as_float(w[r][k][0]);
+                        x[r][2 * k + 1] = __uint_as_float(w[r][k][2]);
+                        pending &= ~(1u << (2 * r + k));
+                    }
+                }
+            }
+            if (!pending) break;
+            if (++polls >= limit) { ok = false; break; }
+            if (polls > 64) __nanosleep(polls < 1024 ? 100 : 2000);
+        }
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int r = 0; r < PX_MAX_WORLD; ++r) {             // rank order: the same sum on every rank
+            if (r < a.world) {
+                if (r == a.rank && !pushed) { s.x += mine.x; s.y += mine.y; s.z += mine.z; s.w += mine.w; }
+                else { s.x += x[r][0]; s.y += x[r][1]; s.z += x[r][2]; s.w += x[r][3]; }
+            }
         }
         if (!ok) {
             if (a.sticky) atomicOr(a.sticky, PEER_EXCHANGE_TIMEOUT);
