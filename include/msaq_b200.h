@@ -57,7 +57,7 @@ unsigned long long msaq_launch_count(void);
  *   cores with accumulators in tensor memory; 0 keeps them on the warp-level integer MMA path (the two paths
  *   agree to the output tolerance, not bit for bit).
  * MSAQ_OPT_INKERNEL_STAGING (default 1): small integer-MMA GEMVs (up to four rows, no fused prologue, at most
- *   nine K blocks per thread block) convert their activations inside the main kernel, one launch per GEMV; 0
+ *   eighteen K blocks per thread block) convert their activations inside the main kernel, one launch per GEMV; 0
  *   runs the separate staging kernel in front, as all other launches do.  Same staged values either way.
  * MSAQ_OPT_WAIT_POLLS (default 2^20): poll limit of every wait on a shared-memory barrier inside the pipelined
  *   kernels.  A wait that reaches it gives up: the kernel finishes by itself, the outputs the wait fed become

@@ -260,9 +260,9 @@ int run_mma(const __nv_bfloat16* X, const Prologue& pro, const int8_t* se, const
         xa.r_is_f32 = pro.r_is_f32;
         xa.eps = pro.eps;
         xa.natural = fmt == GF_MXINT8 ? 1 : 0;
-        // Up to four rows, no prologue, and no CTA streams more than nine K blocks (the small problems, where fixed
+        // Up to four rows, no prologue, and no CTA streams more than eighteen K blocks (the small problems, where fixed
         // costs are most of the time): the main kernel stages the activations itself -- each of its nine warps writes
-        // one record into a table in shared memory while the first copies are in flight -- and no launch runs in
+        // one or two records into a table in shared memory while the first copies are in flight -- and no launch runs in
         // front (4096x4096, one row: 11.8 -> 10.3 us).  With a prologue in front, or more blocks per CTA, the
         // separate staging kernel is the faster arrangement: it runs under the tail of the kernel before it, while
         // staging inside delays the consumers' start (measured on the 70B layer's GEMVs, one and eight GPUs).

@@ -48,7 +48,9 @@ constexpr int GM_MP = 4;             // activation rows per MMA pass
 constexpr int GM_MAX_PASSES = 4;     // -> at most 16 rows per launch
 constexpr int GM_XREC = 320;         // bytes of staged activations per (block, pass)
 constexpr int GM_CTAS_PER_SM = MSAQ_GM_CTAS;
-constexpr int GM_MAX_TABLE = (GM_WARPS + 1) * GM_XREC;   // largest in-kernel record table: one record per warp of the CTA
+// Largest in-kernel record table: two records per warp of the CTA.  (One per warp was the first rule; a second
+// round costs less than the staging launch it replaces: 8192x8192, one row, 19.85 -> 19.2 us.)
+constexpr int GM_MAX_TABLE = 2 * (GM_WARPS + 1) * GM_XREC;
 
 // Stage layout for a tile of TC columns x one K block:
 //   upper [TC][16] | shared [TC][8] | scale [TC] | activations [passes][GM_XREC]
@@ -544,9 +546,9 @@ __device__ __forceinline__ void gemv_stage_records(const GemvMmaArgs& a, uint8_t
     }
 }
 
-// The start of a CTA: all nine warps take the row norms (where the prologue has one) and then one record
-// each, while the first copies are in flight.  The host uses this path only where a CTA streams at most nine
-// K blocks, i.e. where one round covers the table: staging more than that in the kernel delays the
+// The start of a CTA: all nine warps take the row norms (where the prologue has one) and then one or two records
+// each, while the first copies are in flight.  The host uses this path only where a CTA streams at most eighteen
+// K blocks, i.e. where two rounds cover the table: staging much more than that in the kernel delays the
 // consumers' start by more than the separate staging kernel costs (it overlaps the tail of the kernel before
 // it), and records written by the producer warp one unit ahead of its copies slow a two-stage ring down
 // (both measured: 57344x8192 70.5 and 77.0 us against 69.1 us behind the staging kernel).
