@@ -163,7 +163,7 @@ def test_gemv_in_kernel_staging_equals_staging_kernel(rng, M, OUT, K):
     assert L.msaq_get_option(5) == 1
     n0 = L.msaq_launch_count()
     got, gotf = cabi.gemv("batched", cabi.bf16_dev(X), pd, M=M)
-    # where no thread block streams more than nine K blocks the staging kernel in front is gone
+    # where no thread block streams more than eighteen K blocks the staging kernel in front is gone
     launches = L.msaq_launch_count() - n0
     assert launches in (1, 2)
     if (OUT, K) in ((384, 512), (4096, 4096)):
