@@ -133,6 +133,17 @@ gemv_xprep_kernel(const XprepArgs a) {
     const bool live = blk < a.NB;                  // uniform over the CTA
 
     float inv_rms = 1.0f;
+    // this warp's own 32 elements, asked for before the row norm so that they do not cost a second round of
+    // load latency behind it
+    float hv_own = 0.0f, d_own = 0.0f;
+    if ((MODE == XP_RMSNORM || MODE == XP_ADD_NORM) && live && m < a.M) {
+        const int k = blk * BLOCK + lane;
+        hv_own = __bfloat162float(a.X[(int64_t)m * a.ldx + k]);
+        if (MODE == XP_ADD_NORM) {
+            const int64_t o = (int64_t)m * K + k;
+            d_own = a.r_is_f32 ? static_cast<const float*>(a.R)[o] : __bfloat162float(static_cast<const __nv_bfloat16*>(a.R)[o]);
+        }
+    }
     if (MODE == XP_RMSNORM || MODE == XP_ADD_NORM) {
         // Sum of squares of each of this pass's rows, by the whole CTA, in an order that does not
         // depend on the CTA: every CTA arrives at the same bits.
@@ -209,11 +220,10 @@ gemv_xprep_kernel(const XprepArgs a) {
             const float g = __bfloat162float(xr[k]), u = __bfloat162float(xr[K + k]);
             x = __bfloat162float(__float2bfloat16_rn(g / (1.0f + __expf(-g)) * u));
         } else {
-            float hv = __bfloat162float(xr[k]);
+            float hv = hv_own;
             if (MODE == XP_ADD_NORM) {
                 const int64_t o = (int64_t)m * K + k;
-                const float d = a.r_is_f32 ? static_cast<const float*>(a.R)[o]
-                                           : __bfloat162float(static_cast<const __nv_bfloat16*>(a.R)[o]);
+                const float d = d_own;
                 const __nv_bfloat16 hb = __float2bfloat16_rn(hv + d);
                 a.h_out[o] = hb;
                 hv = __bfloat162float(hb);
