@@ -44,13 +44,6 @@ __device__ __forceinline__ void px_store(float* dst, float x0, float x1, uint32_
     asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(dst), "r"(__float_as_uint(x0)), "r"(seq),
                  "r"(__float_as_uint(x1)) : "memory");
 }
-__device__ __forceinline__ bool px_load(const float* src, uint32_t seq, float& x0, float& x1) {
-    uint32_t a, fa, b, fb;
-    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(fa), "=r"(b), "=r"(fb) : "l"(src) : "memory");
-    x0 = __uint_as_float(a);
-    x1 = __uint_as_float(b);
-    return fa == seq && fb == seq;
-}
 
 __global__ void __launch_bounds__(PX_THREADS)
 peer_exchange_kernel(const PeerArgs a) {

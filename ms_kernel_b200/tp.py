@@ -163,11 +163,12 @@ def peer_all_reduce(group, numel, dtype, device, slots=2):
 
 class PeerExchange:
     """The same exchange on this library's own kernel (msaq_peer_exchange): every rank stores its partial
-    sums straight into its slot of every peer's buffer, counts itself on the peer's flag and waits once
-    for the others -- one kernel, one wait, and the residual add of the step's end inside it
-    (`reduce_add`).  The buffers are torch symmetric memory (peer-mapped by its rendezvous); the kernel
-    uses plain peer stores and loads only.  Successive calls alternate between two halves of the buffer;
-    every rank must make the same calls in the same order."""
+    sums straight into its slot of every peer's buffer as words that carry the exchange's sequence number
+    beside the data, and every thread waits on its own words -- one kernel, no fence, no flag, and the
+    residual add of the step's end inside it (`reduce_add`).  The buffers are torch symmetric memory
+    (peer-mapped by its rendezvous); the kernel uses plain peer stores and local loads only.  Successive
+    calls alternate between two halves of the buffer; every rank must make the same calls in the same
+    order."""
 
     def __init__(self, group, numel, device, fused=True):
         import torch
