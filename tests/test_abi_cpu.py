@@ -46,6 +46,39 @@ def test_argument_validation_needs_no_device():
     assert L.msaq_pack_weight(one, 1, one, one, one, one, one, 8, 40, 4, 2, None) == -1  # K % 32
 
 
+def test_new_entry_points_validate_before_the_device():
+    """The tensor-parallel exchange, the GEMV with the push inside, the GEMV with the residual add behind it and the
+    decode with the append inside: sizes and arguments are checked before anything touches a device."""
+    import ctypes as C
+    from ms_kernel_b200 import _lib
+    L = _lib.lib()
+    one = 16
+    assert L.msaq_peer_exchange_bytes(2, 8192) == 4 * 2 * 8192 * 4 + 256
+    assert L.msaq_peer_exchange_bytes(8, 4) == 4 * 8 * 4 * 4 + 256
+    assert L.msaq_peer_exchange_bytes(1, 8192) == 0 and L.msaq_peer_exchange_bytes(9, 8192) == 0
+    assert L.msaq_peer_exchange_bytes(2, 0) == 0
+    bufs = (C.c_void_p * 8)(*([one] * 8))
+    assert L.msaq_peer_exchange(one, None, None, bufs, 0, 2, 8192, 0, None) == -1          # no output
+    assert L.msaq_peer_exchange(one, None, one, bufs, 2, 2, 8192, 0, None) == -1           # rank outside the world
+    assert L.msaq_peer_exchange(one, None, one, bufs, 0, 9, 8192, 0, None) == -1           # more than eight ranks
+    assert L.msaq_peer_exchange(one, None, one, bufs, 0, 2, 8190, 0, None) == -1           # n not a multiple of 4
+    assert L.msaq_peer_exchange(one, None, one, bufs, 0, 2, 8192, 2, None) == -1           # parity
+    assert L.msaq_peer_exchange(one + 4, None, one, bufs, 0, 2, 8192, 0, None) == -1       # misaligned partial
+    bad = (C.c_void_p * 8)(one, None)
+    assert L.msaq_peer_exchange(one, None, one, bad, 0, 2, 8192, 0, None) == -1            # a peer buffer is missing
+    args = [one, 0, None, 0, 1e-5, None, one, one, one, 1, 256, 8, 4, 2]
+    assert L.msaq_wonly_gemv_fused_push(*args, bufs, 0, 1, 0, one, 1 << 20, None) == -1    # one rank is no exchange
+    assert L.msaq_wonly_gemv_fused_push(*args, bufs, 0, 2, 3, one, 1 << 20, None) == -1    # parity
+    assert L.msaq_wonly_gemv_fused_push(*args, None, 0, 2, 0, one, 1 << 20, None) == -1    # no buffers
+    assert L.msaq_wonly_gemv_fused_add(one, 3, 1e-5, one, one, one, one, one, 1, 256, 8, 4, 2, one, 1 << 20, None) == -1   # add+rmsnorm is not a prologue here
+    assert L.msaq_wonly_gemv_fused_add(one, 0, 1e-5, one, one, one, None, one, 1, 256, 8, 4, 2, one, 1 << 20, None) == -1  # no residual
+    dec = [one] * 3 + [one] * 6 + [one, None, None, 2, 8, 8, 64, 128, 4, 4, 2, 64, 1, 1, None, None, 0]
+    assert L.msaq_kv_decode_attention_append(*dec, 64, None, one, 1 << 20, None) == -1     # slot beyond the capacity
+    assert L.msaq_kv_decode_attention_append(*dec, -1, None, one, 1 << 20, None) == -1     # negative slot
+    dec[1] = None
+    assert L.msaq_kv_decode_attention_append(*dec, 3, None, one, 1 << 20, None) == -1      # no new K row
+
+
 def test_no_fallback_without_gpu():
     import torch
     if torch.cuda.is_available():
